@@ -1,0 +1,89 @@
+"""Builds ``lingua_b200/lib/liblingua_b200.so`` from ``lingua_b200/csrc/*.cu`` with nvcc for sm_100a.
+
+The library has a plain C ABI (no torch headers), so a full rebuild takes well under a
+minute and needs no GPU. Objects are cached by a hash of the source, the headers and the
+flags. ``python -m lingua_b200.build [--verbose] [--force]``.
+"""
+from __future__ import annotations
+
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+CSRC = PKG / "csrc"
+LIBDIR = PKG / "lib"
+OBJDIR = LIBDIR / "obj"
+LIB = LIBDIR / "liblingua_b200.so"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-O3", "-std=c++17", "-lineinfo",
+    "--use_fast_math",
+    "-Xcompiler", "-fPIC",
+    "--expt-relaxed-constexpr",
+    "-Xptxas", "-v",
+]
+
+
+def nvcc_path() -> str:
+    cand = os.environ.get("NVCC") or shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not Path(cand).exists():
+        raise RuntimeError("nvcc not found; set NVCC or put /usr/local/cuda/bin on PATH")
+    return cand
+
+
+def _digest(src: Path, headers: list[Path]) -> str:
+    h = hashlib.sha256()
+    h.update(" ".join(NVCC_FLAGS).encode())
+    for f in [src, *headers]:
+        h.update(f.read_bytes())
+    return h.hexdigest()[:16]
+
+
+def build(force: bool = False, verbose: bool = False) -> Path:
+    """Compile every kernel source and link the shared library. Returns its path."""
+    nvcc = nvcc_path()
+    OBJDIR.mkdir(parents=True, exist_ok=True)
+    sources = sorted(CSRC.glob("*.cu"))
+    headers = sorted(list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")))
+    jobs = []
+    objs = []
+    for src in sources:
+        obj = OBJDIR / f"{src.stem}.{_digest(src, headers)}.o"
+        objs.append(obj)
+        if force or not obj.exists():
+            for old in OBJDIR.glob(f"{src.stem}.*.o"):
+                old.unlink()
+            jobs.append((src, obj))
+
+    def compile_one(job):
+        src, obj = job
+        cmd = [nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        log = OBJDIR / f"{src.stem}.ptxas.log"
+        log.write_text(r.stdout + r.stderr)
+        if r.returncode != 0:
+            raise RuntimeError(f"nvcc failed for {src.name}:\n{r.stdout}\n{r.stderr}")
+        if verbose:
+            print(f"[build] {src.name}\n{r.stderr}")
+        return obj
+
+    if jobs:
+        with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
+            list(ex.map(compile_one, jobs))
+    if jobs or not LIB.exists() or force:
+        cmd = [nvcc, "-shared", "-o", str(LIB), *map(str, objs), "-lcudart"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    return LIB
+
+
+if __name__ == "__main__":
+    p = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
+    print(p)

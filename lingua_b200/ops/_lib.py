@@ -1,0 +1,111 @@
+"""ctypes binding of ``liblingua_b200.so`` (the sm_100a kernels).
+
+The library is loaded from ``lingua_b200/lib`` in this source tree. On a machine with a
+GPU a missing library is an error (no silent PyTorch fallback); on a CPU-only machine
+``available()`` is False and the callers use their PyTorch reference implementations.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from pathlib import Path
+
+import torch
+
+_LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "liblingua_b200.so"
+_lib = None
+_status = {}
+
+LB_BF16, LB_F32, LB_E4M3, LB_E5M2 = 0, 1, 2, 3
+
+
+class GemmArgs(C.Structure):
+    _fields_ = [
+        ("A", C.c_void_p), ("B", C.c_void_p), ("C", C.c_void_p), ("status", C.c_void_p),
+        ("M", C.c_int), ("N", C.c_int), ("K", C.c_int),
+        ("a_major", C.c_int), ("b_major", C.c_int),
+        ("in_dtype", C.c_int), ("out_dtype", C.c_int),
+        ("accumulate", C.c_int),
+        ("nb0", C.c_int), ("nb1", C.c_int),
+        ("force_bn", C.c_int),
+        ("alpha", C.c_float),
+        ("lda", C.c_longlong), ("ldb", C.c_longlong), ("ldc", C.c_longlong),
+        ("a_bs0", C.c_longlong), ("a_bs1", C.c_longlong),
+        ("b_bs0", C.c_longlong), ("b_bs1", C.c_longlong),
+        ("c_bs0", C.c_longlong), ("c_bs1", C.c_longlong),
+    ]
+
+
+def lib_path() -> Path:
+    return _LIB_PATH
+
+
+def available() -> bool:
+    """True when the native kernels can run: a CUDA device is visible and the library loads."""
+    if not torch.cuda.is_available():
+        return False
+    return load() is not None
+
+
+def load():
+    """dlopen the kernel library (building it first if the .so is missing and nvcc exists)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not _LIB_PATH.exists():
+        if os.environ.get("LINGUA_B200_NO_BUILD") == "1":
+            raise RuntimeError(f"{_LIB_PATH} is missing; run `python -m lingua_b200.build`")
+        from lingua_b200 import build as _build
+
+        _build.build()
+    lib = C.CDLL(str(_LIB_PATH))
+    lib.lb_gemm.argtypes = [C.POINTER(GemmArgs), C.c_void_p]
+    lib.lb_gemm.restype = C.c_int
+    lib.lb_launch_count.restype = C.c_longlong
+    lib.lb_launch_count_add.argtypes = [C.c_longlong]
+    _declare(lib)
+    _lib = lib
+    return lib
+
+
+def _declare(lib) -> None:
+    """Signatures of the remaining entry points; a symbol that is absent is left undeclared."""
+    vp, i, ll, f = C.c_void_p, C.c_int, C.c_longlong, C.c_float
+    sigs = {}
+    for name, args in sigs.items():
+        if hasattr(lib, name):
+            fn = getattr(lib, name)
+            fn.argtypes = args
+            fn.restype = C.c_int
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def status_word(device=None) -> torch.Tensor:
+    """One uint32 status word per device, shared by every kernel that can time out."""
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index
+    t = _status.get(dev)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=f"cuda:{dev}")
+        _status[dev] = t
+    return t
+
+
+def check_status() -> None:
+    """Synchronises and raises if any kernel recorded a timed-out wait since the last check."""
+    for dev, t in _status.items():
+        v = int(t.item())
+        if v != 0:
+            t.zero_()
+            raise RuntimeError(f"lingua_b200 kernel reported status 0x{v & 0xFFFFFFFF:x} on cuda:{dev}")
+
+
+def launch_count() -> int:
+    return int(load().lb_launch_count())
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"{what} failed with code {rc}")

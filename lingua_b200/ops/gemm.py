@@ -1,0 +1,106 @@
+"""bf16 GEMM on the tcgen05 kernel (``csrc/gemm.cu``), with a PyTorch reference for CPU.
+
+``gemm(a, b)`` computes ``a @ b.transpose(-1, -2)`` for ``a: [..., M, K]`` and
+``b: [..., N, K]``. Either operand may be a transposed view: the kernel reads K-contiguous
+and M/N-contiguous operands directly, so the dgrad and wgrad GEMMs of a linear layer
+(lingua/transformer.py:357-359) need no transposed copies.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+
+def _major_and_ld(t: torch.Tensor):
+    """(major, leading stride) of the last two dims: 0 = last dim contiguous, 1 = second-to-last."""
+    if t.stride(-1) == 1:
+        return 0, t.stride(-2)
+    if t.stride(-2) == 1:
+        return 1, t.stride(-1)
+    raise ValueError("operand needs a unit stride in one of its last two dims")
+
+
+def gemm_ref(a, b, out_dtype=torch.bfloat16, out=None, accumulate=False, alpha=1.0):
+    r = torch.matmul(a.float(), b.float().transpose(-1, -2)) * alpha
+    if out is not None:
+        if accumulate:
+            out.add_(r.to(out.dtype))
+        else:
+            out.copy_(r.to(out.dtype))
+        return out
+    return r.to(out_dtype)
+
+
+def gemm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    out_dtype: torch.dtype = torch.bfloat16,
+    out: Optional[torch.Tensor] = None,
+    accumulate: bool = False,
+    alpha: float = 1.0,
+    force_bn: int = 0,
+) -> torch.Tensor:
+    """``out (+)= alpha * a @ b^T``; a: [*batch, M, K], b: [*batch, N, K], up to two batch dims."""
+    if not a.is_cuda:
+        return gemm_ref(a, b, out_dtype, out, accumulate, alpha)
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, "bf16 operands expected"
+    assert a.dim() == b.dim() and 2 <= a.dim() <= 4
+    M, K = a.shape[-2:]
+    N, Kb = b.shape[-2:]
+    assert K == Kb, f"reduction dims differ: {K} vs {Kb}"
+    batch = list(a.shape[:-2])
+    assert list(b.shape[:-2]) == batch
+    if out is None:
+        out = torch.empty(*batch, M, N, dtype=out_dtype, device=a.device)
+    else:
+        assert out.shape[-2:] == (M, N) and out.stride(-1) == 1
+    a_major, lda = _major_and_ld(a)
+    b_major, ldb = _major_and_ld(b)
+    # A unit-extent dim can report any stride; normalise so the TMA stride rule holds.
+    if M == 1 and a_major == 0:
+        lda = K
+    if N == 1 and b_major == 0:
+        ldb = K
+    args = _lib.GemmArgs()
+    args.A, args.B, args.C = a.data_ptr(), b.data_ptr(), out.data_ptr()
+    args.status = _lib.status_word(a.device).data_ptr()
+    args.M, args.N, args.K = M, N, K
+    args.a_major, args.b_major = a_major, b_major
+    args.in_dtype = _lib.LB_BF16
+    args.out_dtype = _lib.LB_BF16 if out.dtype == torch.bfloat16 else _lib.LB_F32
+    assert out.dtype in (torch.bfloat16, torch.float32)
+    args.accumulate = int(accumulate)
+    args.alpha = float(alpha)
+    args.force_bn = force_bn
+    args.lda, args.ldb, args.ldc = lda, ldb, out.stride(-2)
+    # kernel batch index 0 is the fastest-varying (last) batch dim
+    nb = batch[::-1] + [1] * (2 - len(batch))
+    sa = list(a.stride()[:-2])[::-1] + [0] * (2 - len(batch))
+    sb = list(b.stride()[:-2])[::-1] + [0] * (2 - len(batch))
+    sc = list(out.stride()[:-2])[::-1] + [0] * (2 - len(batch))
+    args.nb0, args.nb1 = nb
+    args.a_bs0, args.a_bs1 = sa
+    args.b_bs0, args.b_bs1 = sb
+    args.c_bs0, args.c_bs1 = sc
+    rc = _lib.load().lb_gemm(C.byref(args), _lib.stream_ptr())
+    _lib.check(rc, f"lb_gemm(M={M},N={N},K={K},majors={a_major}{b_major})")
+    return out
+
+
+def mm_nt(x: torch.Tensor, w: torch.Tensor, **kw) -> torch.Tensor:
+    """x[M,K] @ w[N,K]^T -> [M,N] (linear forward)."""
+    return gemm(x, w, **kw)
+
+
+def mm_nn(dy: torch.Tensor, w: torch.Tensor, **kw) -> torch.Tensor:
+    """dy[M,N] @ w[N,K] -> [M,K] (linear dgrad)."""
+    return gemm(dy, w.transpose(-1, -2), **kw)
+
+
+def mm_tn(dy: torch.Tensor, x: torch.Tensor, **kw) -> torch.Tensor:
+    """dy[M,N]^T @ x[M,K] -> [N,K] (linear wgrad)."""
+    return gemm(dy.transpose(-1, -2), x.transpose(-1, -2), **kw)

@@ -1,0 +1,73 @@
+"""tcgen05 GEMM vs an fp32 PyTorch matmul of the same bf16 inputs."""
+import pytest
+import torch
+
+from lingua_b200.ops import gemm as G
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(a, b, alpha=1.0):
+    return alpha * (a.float() @ b.float().transpose(-1, -2))
+
+
+def _check(out, ref, k):
+    tol = 2e-2 * max(1.0, (k / 256) ** 0.5)
+    err = (out.float() - ref).abs().max().item()
+    scale = ref.abs().max().item() + 1e-6
+    assert err / scale < tol, f"rel err {err / scale:.4g} (abs {err:.4g})"
+
+
+SHAPES = [(128, 256, 64), (256, 512, 512), (384, 128, 192), (200, 136, 72), (1024, 2048, 1024), (130, 72, 1032)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+@pytest.mark.parametrize("a_t,b_t", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_all_majors(M, N, K, a_t, b_t, out_dtype):
+    torch.manual_seed(0)
+    dev = "cuda"
+    # transposed operands need their contiguous dim (M or N) to be a multiple of 8 for TMA
+    if (a_t and M % 8) or (b_t and N % 8):
+        pytest.skip("TMA stride alignment")
+    a = torch.randn(K, M, device=dev, dtype=torch.bfloat16).t() if a_t else torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+    b = torch.randn(K, N, device=dev, dtype=torch.bfloat16).t() if b_t else torch.randn(N, K, device=dev, dtype=torch.bfloat16)
+    out = G.gemm(a, b, out_dtype=out_dtype)
+    torch.cuda.synchronize()
+    _check(out, _ref(a, b), K)
+
+
+def test_gemm_accumulate_and_alpha():
+    torch.manual_seed(1)
+    a = torch.randn(256, 320, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(384, 320, device="cuda", dtype=torch.bfloat16)
+    c0 = torch.randn(256, 384, device="cuda", dtype=torch.float32)
+    c = c0.clone()
+    G.gemm(a, b, out=c, accumulate=True, alpha=0.5)
+    _check(c, c0 + _ref(a, b, 0.5), 320)
+
+
+def test_gemm_batched_strided():
+    torch.manual_seed(2)
+    B, S, H, D = 2, 256, 3, 128
+    q = torch.randn(B, S, H, D, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(B, S, H, D, device="cuda", dtype=torch.bfloat16)
+    s = G.gemm(q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), out_dtype=torch.float32)
+    ref = torch.einsum("bshd,bthd->bhst", q.float(), k.float())
+    _check(s, ref, D)
+    # P @ V with V as the MN-major operand: out[b,h,s,d] = sum_t p[b,h,s,t] v[b,t,h,d]
+    p = torch.randn(B, H, S, S, device="cuda", dtype=torch.bfloat16)
+    o = G.gemm(p, k.permute(0, 2, 3, 1), out_dtype=torch.bfloat16)
+    ref = torch.einsum("bhst,bthd->bhsd", p.float(), k.float())
+    _check(o, ref, S)
+
+
+def test_linear_three_gemms():
+    torch.manual_seed(3)
+    M, K, N = 512, 256, 384
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    dy = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    _check(G.mm_nt(x, w), x.float() @ w.float().t(), K)
+    _check(G.mm_nn(dy, w), dy.float() @ w.float(), N)
+    _check(G.mm_tn(dy, x, out_dtype=torch.float32), dy.float().t() @ x.float(), M)
