@@ -1,0 +1,720 @@
+// Flash attention forward / backward for head_dim 128 on tcgen05 (sm_100a).
+//
+// Causal, block-causal (documents packed in one sequence, given as doc_start[token]) and
+// sliding-window masks; grouped-query attention without materialising repeated K/V heads.
+// Replaces the SDPA / xformers / flex_attention calls of lingua/transformer.py:374-404 and
+// the mask builders of lingua/transformer.py:142-217.
+//
+// Forward, one CTA per (128-query block, head, batch): warp 0 streams K/V tiles with TMA
+// through a 2-stage ring, one thread of warp 1 issues S = Q K^T into one of two TMEM
+// buffers and O += P V, warps 2-5 (one thread per query row) run the online softmax on S
+// straight out of TMEM, write P as bf16 into a swizzled shared-memory tile for the second
+// MMA, and rescale the TMEM-resident O only when a row maximum grew by more than 2^8.
+//
+// Backward, one CTA per (128-key block, kv head, batch), looping over the query blocks that
+// can see it: S and dP are recomputed on the tensor cores, dV and dK accumulate in TMEM for
+// the whole loop, and dQ tiles are reduced into an fp32 scratch buffer with vector atomics.
+#include "common.cuh"
+#include "lingua_b200.h"
+
+namespace lb {
+
+constexpr int AT_THREADS = 192;
+constexpr int AT_TILE = 128 * 128 * 2;  // one 128 x 128 bf16 tile: two 16 KB halves of 64 columns
+constexpr int AT_HALF = 128 * 64 * 2;
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float LN2 = 0.6931471805599453f;
+
+constexpr uint32_t IDESC_KK = make_idesc(128, 128, 1, 1, 0, 0);
+constexpr uint32_t IDESC_KM = make_idesc(128, 128, 1, 1, 0, 1);
+constexpr uint32_t IDESC_MM = make_idesc(128, 128, 1, 1, 1, 1);
+
+// k-th 16-wide reduction slice of a tile whose 128-byte rows run along the reduction dim
+__device__ __forceinline__ uint64_t desc_k(uint32_t tile, int k) {
+  return make_smem_desc(tile + (k >> 2) * AT_HALF + (k & 3) * 32, 16, 1024);
+}
+// k-th 16-row reduction slice of a tile whose 128-byte rows run along M/N (one row per k)
+__device__ __forceinline__ uint64_t desc_mn(uint32_t tile, int k) {
+  return make_smem_desc(tile + k * 2048, AT_HALF, 1024);
+}
+// 32 bf16 of row r, columns [32c, 32c+32) into a 128 x 128 tile in the TMA 128-byte swizzle
+__device__ __forceinline__ void st_tile_row32(uint32_t tile, int r, int c, const uint32_t (&pk)[16]) {
+  const uint32_t base = tile + (c >> 1) * AT_HALF + r * 128;
+  const int unit0 = (c & 1) * 4;
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const uint32_t addr = base + (((unit0 + u) ^ (r & 7)) << 4);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk[4 * u]), "r"(pk[4 * u + 1]),
+                 "r"(pk[4 * u + 2]), "r"(pk[4 * u + 3])
+                 : "memory");
+  }
+}
+
+struct AttnParams {
+  int B, S, H, Hkv;
+  int causal, window;
+  float scale;
+  const int* doc_start;  // [B*S]: first token of the document of each token, or null
+  const int* doc_end;    // [B*S]: one past the last token of that document, or null
+  __nv_bfloat16* O;      // [B,S,H,128] contiguous
+  float* lse;            // [B,H,S] natural log
+  const float* delta;    // [B,H,S]
+  float* dq_acc;         // [B,S,H,128] fp32
+  __nv_bfloat16 *dk, *dv;
+  long long k_sb, k_ss, k_sh, v_sb, v_ss, v_sh;  // strides of dk / dv (same as k / v)
+  uint32_t* status;
+};
+
+// ============================================================================ forward
+constexpr int FWD_SMEM = AT_TILE /*Q*/ + 4 * AT_TILE /*K,V x 2 stages*/ + AT_TILE /*P*/ + 1024 + 256;
+
+__global__ void __launch_bounds__(AT_THREADS, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
+                const __grid_constant__ CUtensorMap tv, const AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ int abort_flag;
+  __shared__ uint32_t tmem_slot;
+  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sQ = sbase;
+  auto sK = [&](int s) { return sbase + AT_TILE + s * 2 * AT_TILE; };
+  auto sV = [&](int s) { return sbase + 2 * AT_TILE + s * 2 * AT_TILE; };
+  const uint32_t sP = sbase + 5 * AT_TILE;
+  const uint32_t bars = sbase + 6 * AT_TILE;
+  const uint32_t q_full = bars;
+  auto k_full = [&](int s) { return bars + 8 + 8 * s; };
+  auto v_full = [&](int s) { return bars + 24 + 8 * s; };
+  auto kv_empty = [&](int s) { return bars + 40 + 8 * s; };
+  auto s_full = [&](int s) { return bars + 56 + 8 * s; };
+  auto s_empty = [&](int s) { return bars + 72 + 8 * s; };
+  const uint32_t p_full = bars + 88;
+  const uint32_t o_done = bars + 96;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nqb = (p.S + 127) / 128;
+  const int qb = nqb - 1 - blockIdx.x;  // longest rows first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.H / p.Hkv);
+
+  // kv block range [j0, j1]
+  const int row_first = qb * 128;
+  const int row_last = min(qb * 128 + 127, p.S - 1);
+  int lo_first = p.doc_start ? p.doc_start[(long long)b * p.S + row_first] : 0;
+  int lo_last = p.doc_start ? p.doc_start[(long long)b * p.S + row_last] : 0;
+  if (p.window > 0) {
+    lo_first = max(lo_first, row_first - p.window + 1);
+    lo_last = max(lo_last, row_last - p.window + 1);
+  }
+  const int j0 = lo_first / 128;
+  const int j1 = p.causal ? qb : nqb - 1;
+  const int n = j1 - j0 + 1;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(k_full(s), 1);
+      mbar_init(v_full(s), 1);
+      mbar_init(kv_empty(s), 1);
+      mbar_init(s_full(s), 1);
+      mbar_init(s_empty(s), 4);
+    }
+    mbar_init(p_full, 4);
+    mbar_init(o_done, 1);
+    fence_mbar_init();
+    tma_prefetch_desc(&tq);
+    tma_prefetch_desc(&tk);
+    tma_prefetch_desc(&tv);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  const uint32_t tS0 = tmem, tO = tmem + 256;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(q_full, AT_TILE);
+      tma_load_4d(sQ, &tq, q_full, 0, row_first, h, b);
+      tma_load_4d(sQ + AT_HALF, &tq, q_full, 64, row_first, h, b);
+      for (int it = 0; it < n; ++it) {
+        const int s = it & 1, kv0 = (j0 + it) * 128;
+        if (!mbar_wait(kv_empty(s), ((it >> 1) & 1) ^ 1, &abort_flag, p.status, 0x11)) break;
+        mbar_arrive_expect_tx(k_full(s), AT_TILE);
+        tma_load_4d(sK(s), &tk, k_full(s), 0, kv0, hk, b);
+        tma_load_4d(sK(s) + AT_HALF, &tk, k_full(s), 64, kv0, hk, b);
+        mbar_arrive_expect_tx(v_full(s), AT_TILE);
+        tma_load_4d(sV(s), &tv, v_full(s), 0, kv0, hk, b);
+        tma_load_4d(sV(s) + AT_HALF, &tv, v_full(s), 64, kv0, hk, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = mbar_wait(q_full, 0, &abort_flag, p.status, 0x12) &&
+                mbar_wait(k_full(0), 0, &abort_flag, p.status, 0x13);
+      if (ok) {
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_f16(tS0, desc_k(sQ, k), desc_k(sK(0), k), IDESC_KK, k != 0);
+        umma_commit(s_full(0));
+      }
+      for (int it = 0; ok && it < n; ++it) {
+        if (it + 1 < n) {
+          const int b1 = (it + 1) & 1;
+          const uint32_t ph = ((it + 1) >> 1) & 1;
+          ok = mbar_wait(k_full(b1), ph, &abort_flag, p.status, 0x14) &&
+               mbar_wait(s_empty(b1), ph ^ 1, &abort_flag, p.status, 0x15);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            umma_f16(tS0 + b1 * 128, desc_k(sQ, k), desc_k(sK(b1), k), IDESC_KK, k != 0);
+          umma_commit(s_full(b1));
+        }
+        const int s = it & 1;
+        ok = mbar_wait(v_full(s), (it >> 1) & 1, &abort_flag, p.status, 0x16) &&
+             mbar_wait(p_full, it & 1, &abort_flag, p.status, 0x17);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_f16(tO, desc_k(sP, k), desc_mn(sV(s), k), IDESC_KM, (it | k) != 0);
+        umma_commit(kv_empty(s));
+        umma_commit(o_done);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax warps
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const int q_idx = qb * 128 + r;
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    const float sl2 = p.scale * LOG2E;
+    int lo = 0;
+    if (p.doc_start) lo = p.doc_start[(long long)b * p.S + min(q_idx, p.S - 1)];
+    if (p.window > 0) lo = max(lo, q_idx - p.window + 1);
+    const int hi = p.causal ? min(q_idx, p.S - 1) : p.S - 1;  // last visible key
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int it = 0; it < n; ++it) {
+      const int j = j0 + it, buf = it & 1;
+      const int kv0 = j * 128;
+      ok = mbar_wait(s_full(buf), (it >> 1) & 1, &abort_flag, p.status, 0x18);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t tS = tS0 + buf * 128 + lane_off;
+      const bool need_mask = (p.causal && j == qb) || (kv0 < lo_last) || (kv0 + 128 > p.S);
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t rr[32];
+        tmem_ld32(tS + c * 32, rr);
+        tmem_wait_ld();
+        if (need_mask) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const int kv = kv0 + c * 32 + e;
+            if (kv >= lo && kv <= hi) mx = fmaxf(mx, __uint_as_float(rr[e]));
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(rr[e]));
+        }
+      }
+      mx *= sl2;
+      const float m_new = fmaxf(m_used, mx);
+      if (it == 0) {
+        m_used = m_new;
+      } else {
+        const bool need = m_new > m_used + 8.f;
+        // P's buffer and O are both free once the previous P V product has completed.
+        ok = mbar_wait(o_done, (it - 1) & 1, &abort_flag, p.status, 0x19);
+        if (!ok) break;
+        if (__any_sync(0xFFFFFFFFu, need)) {
+          tc_fence_after();
+          const float f = need ? exp2f(m_used - m_new) : 1.f;
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t rr[32];
+            tmem_ld32(tO + lane_off + c * 32, rr);
+            tmem_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) rr[e] = __float_as_uint(__uint_as_float(rr[e]) * f);
+            tmem_st32(tO + lane_off + c * 32, rr);
+          }
+          tmem_wait_st();
+          l *= f;
+          if (need) m_used = m_new;
+        }
+      }
+      const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t rr[32], pk[16];
+        tmem_ld32(tS + c * 32, rr);
+        tmem_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float p0 = exp2f(__uint_as_float(rr[e]) * sl2 - m_eff);
+          float p1 = exp2f(__uint_as_float(rr[e + 1]) * sl2 - m_eff);
+          if (need_mask) {
+            const int kv = kv0 + c * 32 + e;
+            if (kv < lo || kv > hi) p0 = 0.f;
+            if (kv + 1 < lo || kv + 1 > hi) p1 = 0.f;
+          }
+          l += p0 + p1;
+          pk[e >> 1] = pack_bf16(p0, p1);
+        }
+        st_tile_row32(sP, r, c, pk);
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(s_empty(buf));
+        mbar_arrive(p_full);
+      }
+    }
+    if (ok && n > 0) ok = mbar_wait(o_done, (n - 1) & 1, &abort_flag, p.status, 0x1A);
+    if (ok) {
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* orow = p.O + (((long long)b * p.S + q_idx) * p.H + h) * 128;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t rr[32];
+        if (n > 0) {
+          tmem_ld32(tO + lane_off + c * 32, rr);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) rr[e] = 0u;
+        }
+        if (q_idx < p.S) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 v;
+            v.x = pack_bf16(__uint_as_float(rr[g * 8 + 0]) * inv, __uint_as_float(rr[g * 8 + 1]) * inv);
+            v.y = pack_bf16(__uint_as_float(rr[g * 8 + 2]) * inv, __uint_as_float(rr[g * 8 + 3]) * inv);
+            v.z = pack_bf16(__uint_as_float(rr[g * 8 + 4]) * inv, __uint_as_float(rr[g * 8 + 5]) * inv);
+            v.w = pack_bf16(__uint_as_float(rr[g * 8 + 6]) * inv, __uint_as_float(rr[g * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = v;
+          }
+        }
+      }
+      if (q_idx < p.S && p.lse) {
+        const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
+        p.lse[((long long)b * p.H + h) * p.S + q_idx] = l > 0.f ? (m_eff + log2f(l)) * LN2 : INFINITY;
+      }
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// ============================================================================ backward
+// delta[b,h,s] = sum_d O[b,s,h,d] * dO[b,s,h,d]; one warp per (b,s,h)
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ O, const __nv_bfloat16* __restrict__ dO,
+                                  float* __restrict__ delta, int B, int S, int H) {
+  const long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long total = (long long)B * S * H;
+  if (w >= total) return;
+  const uint2 a = reinterpret_cast<const uint2*>(O + w * 128)[lane];
+  const uint2 g = reinterpret_cast<const uint2*>(dO + w * 128)[lane];
+  const float2 a0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.x));
+  const float2 a1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a.y));
+  const float2 g0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&g.x));
+  const float2 g1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&g.y));
+  float s = a0.x * g0.x + a0.y * g0.y + a1.x * g1.x + a1.y * g1.y;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
+  if (lane == 0) {
+    const int hh = w % H;
+    const long long bs = w / H;
+    const int s_i = bs % S;
+    const int bb = bs / S;
+    delta[((long long)bb * H + hh) * S + s_i] = s;
+  }
+}
+
+// dq[b,s,h,:] (bf16, strided) = dq_acc[b,s,h,:] (fp32 contiguous)
+__global__ void attn_dq_store_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, int B, int S,
+                                     int H, long long sb, long long ss, long long sh) {
+  const long long total = (long long)B * S * H * 16;  // 8-element vectors
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int v = i & 15;
+    const long long row = i >> 4;
+    const int hh = row % H;
+    const long long bs = row / H;
+    const int s_i = bs % S;
+    const int bb = bs / S;
+    const float4 x = reinterpret_cast<const float4*>(acc + row * 128)[2 * v];
+    const float4 y = reinterpret_cast<const float4*>(acc + row * 128)[2 * v + 1];
+    uint4 o;
+    o.x = pack_bf16(x.x, x.y);
+    o.y = pack_bf16(x.z, x.w);
+    o.z = pack_bf16(y.x, y.y);
+    o.w = pack_bf16(y.z, y.w);
+    *reinterpret_cast<uint4*>(dq + bb * sb + s_i * ss + hh * sh + v * 8) = o;
+  }
+}
+
+constexpr int BWD_SMEM = 2 * AT_TILE /*K,V*/ + 4 * AT_TILE /*Q,dO x 2*/ + AT_TILE /*P|dS*/ + 1024 + 256;
+
+__global__ void __launch_bounds__(AT_THREADS, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
+                const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo,
+                const AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ int abort_flag;
+  __shared__ uint32_t tmem_slot;
+  const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sK = sbase, sV = sbase + AT_TILE;
+  auto sQ = [&](int s) { return sbase + 2 * AT_TILE + s * 2 * AT_TILE; };
+  auto sdO = [&](int s) { return sbase + 3 * AT_TILE + s * 2 * AT_TILE; };
+  const uint32_t sP = sbase + 6 * AT_TILE;
+  const uint32_t bars = sbase + 7 * AT_TILE;
+  const uint32_t kv_full = bars;
+  auto qd_full = [&](int s) { return bars + 8 + 8 * s; };
+  auto qd_empty = [&](int s) { return bars + 24 + 8 * s; };
+  const uint32_t s_full = bars + 40, p_full = bars + 48, dv_done = bars + 56, ds_full = bars + 64;
+  const uint32_t dq_full = bars + 72, dq_drained = bars + 80;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nqb = (p.S + 127) / 128;
+  const int jb = blockIdx.x;  // kv block
+  const int hk = blockIdx.y, b = blockIdx.z;
+  const int group = p.H / p.Hkv;
+  const int kv0 = jb * 128;
+  const int kv_last = min(kv0 + 127, p.S - 1);
+
+  // query blocks that can see this key block: [i0, i1]
+  const int i0 = p.causal ? jb : 0;
+  int i1 = nqb - 1;
+  if (p.doc_end) i1 = min(i1, (p.doc_end[(long long)b * p.S + kv_last] - 1) / 128);
+  if (p.window > 0) i1 = min(i1, (kv_last + p.window - 1) / 128);
+  const int nq = max(i1 - i0 + 1, 0);
+  const int n = nq * group;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(qd_full(s), 1);
+      mbar_init(qd_empty(s), 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 4);
+    mbar_init(dv_done, 1);
+    mbar_init(ds_full, 4);
+    mbar_init(dq_full, 1);
+    mbar_init(dq_drained, 4);
+    fence_mbar_init();
+    tma_prefetch_desc(&tq);
+    tma_prefetch_desc(&tk);
+    tma_prefetch_desc(&tv);
+    tma_prefetch_desc(&tdo);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  const uint32_t tS = tmem, tdP = tmem + 128, tdV = tmem + 256, tdK = tmem + 384;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(kv_full, 2 * AT_TILE);
+      tma_load_4d(sK, &tk, kv_full, 0, kv0, hk, b);
+      tma_load_4d(sK + AT_HALF, &tk, kv_full, 64, kv0, hk, b);
+      tma_load_4d(sV, &tv, kv_full, 0, kv0, hk, b);
+      tma_load_4d(sV + AT_HALF, &tv, kv_full, 64, kv0, hk, b);
+      for (int it = 0; it < n; ++it) {
+        const int s = it & 1;
+        const int h = hk * group + it / nq;
+        const int q0 = (i0 + it % nq) * 128;
+        if (!mbar_wait(qd_empty(s), ((it >> 1) & 1) ^ 1, &abort_flag, p.status, 0x21)) break;
+        mbar_arrive_expect_tx(qd_full(s), 2 * AT_TILE);
+        tma_load_4d(sQ(s), &tq, qd_full(s), 0, q0, h, b);
+        tma_load_4d(sQ(s) + AT_HALF, &tq, qd_full(s), 64, q0, h, b);
+        tma_load_4d(sdO(s), &tdo, qd_full(s), 0, q0, h, b);
+        tma_load_4d(sdO(s) + AT_HALF, &tdo, qd_full(s), 64, q0, h, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = mbar_wait(kv_full, 0, &abort_flag, p.status, 0x22);
+      for (int it = 0; ok && it < n; ++it) {
+        const int s = it & 1;
+        ok = mbar_wait(qd_full(s), (it >> 1) & 1, &abort_flag, p.status, 0x23);
+        if (ok && it > 0) ok = mbar_wait(dq_drained, (it - 1) & 1, &abort_flag, p.status, 0x24);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_f16(tS, desc_k(sQ(s), k), desc_k(sK, k), IDESC_KK, k != 0);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_f16(tdP, desc_k(sdO(s), k), desc_k(sV, k), IDESC_KK, k != 0);
+        umma_commit(s_full);
+        ok = mbar_wait(p_full, it & 1, &abort_flag, p.status, 0x25);
+        if (!ok) break;
+        tc_fence_after();
+        // dV[kv, d] += P^T dO : both operands read with one 128-byte row per query
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_f16(tdV, desc_mn(sP, k), desc_mn(sdO(s), k), IDESC_MM, (it | k) != 0);
+        umma_commit(dv_done);
+        ok = mbar_wait(ds_full, it & 1, &abort_flag, p.status, 0x26);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_f16(tdK, desc_mn(sP, k), desc_mn(sQ(s), k), IDESC_MM, (it | k) != 0);
+        // dQ[q, d] = dS K, into the columns that held S
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_f16(tS, desc_k(sP, k), desc_mn(sK, k), IDESC_KM, k != 0);
+        umma_commit(qd_empty(s));
+        umma_commit(dq_full);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    const float sl2 = p.scale * LOG2E;
+    bool ok = true;
+    for (int it = 0; it < n; ++it) {
+      const int h = hk * group + it / nq;
+      const int ib = i0 + it % nq;
+      const int q_idx = ib * 128 + r;
+      const bool row_ok = q_idx < p.S;
+      const long long stat_i = ((long long)b * p.H + h) * p.S + min(q_idx, p.S - 1);
+      const float lse2 = row_ok ? p.lse[stat_i] * LOG2E : INFINITY;
+      const float dlt = row_ok ? p.delta[stat_i] : 0.f;
+      int lo = 0;
+      if (p.doc_start) lo = p.doc_start[(long long)b * p.S + min(q_idx, p.S - 1)];
+      if (p.window > 0) lo = max(lo, q_idx - p.window + 1);
+      const int hi = p.causal ? min(q_idx, p.S - 1) : p.S - 1;
+      int lo_blk = 0;
+      {
+        const int rl = min(ib * 128 + 127, p.S - 1);
+        if (p.doc_start) lo_blk = p.doc_start[(long long)b * p.S + rl];
+        if (p.window > 0) lo_blk = max(lo_blk, rl - p.window + 1);
+      }
+      const bool need_mask = (p.causal && ib == jb) || (kv0 < lo_blk) || (kv0 + 128 > p.S) || (ib * 128 + 128 > p.S);
+
+      ok = mbar_wait(s_full, it & 1, &abort_flag, p.status, 0x27);
+      if (!ok) break;
+      tc_fence_after();
+      // pass A: P = exp(S - lse) -> shared memory (bf16)
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t rr[32], pk[16];
+        tmem_ld32(tS + lane_off + c * 32, rr);
+        tmem_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float p0 = exp2f(__uint_as_float(rr[e]) * sl2 - lse2);
+          float p1 = exp2f(__uint_as_float(rr[e + 1]) * sl2 - lse2);
+          if (need_mask) {
+            const int kv = kv0 + c * 32 + e;
+            if (!row_ok || kv < lo || kv > hi) p0 = 0.f;
+            if (!row_ok || kv + 1 < lo || kv + 1 > hi) p1 = 0.f;
+          }
+          pk[e >> 1] = pack_bf16(p0, p1);
+        }
+        st_tile_row32(sP, r, c, pk);
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+
+      ok = mbar_wait(dv_done, it & 1, &abort_flag, p.status, 0x28);
+      if (!ok) break;
+      tc_fence_after();
+      // pass B: dS = P * (dP - delta) * scale -> the same shared-memory tile
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t rr[32], dd[32], pk[16];
+        tmem_ld32(tS + lane_off + c * 32, rr);
+        tmem_ld32(tdP + lane_off + c * 32, dd);
+        tmem_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          float p0 = exp2f(__uint_as_float(rr[e]) * sl2 - lse2);
+          float p1 = exp2f(__uint_as_float(rr[e + 1]) * sl2 - lse2);
+          if (need_mask) {
+            const int kv = kv0 + c * 32 + e;
+            if (!row_ok || kv < lo || kv > hi) p0 = 0.f;
+            if (!row_ok || kv + 1 < lo || kv + 1 > hi) p1 = 0.f;
+          }
+          const float d0 = p0 * (__uint_as_float(dd[e]) - dlt) * p.scale;
+          const float d1 = p1 * (__uint_as_float(dd[e + 1]) - dlt) * p.scale;
+          pk[e >> 1] = pack_bf16(d0, d1);
+        }
+        st_tile_row32(sP, r, c, pk);
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ds_full);
+
+      ok = mbar_wait(dq_full, it & 1, &abort_flag, p.status, 0x29);
+      if (!ok) break;
+      tc_fence_after();
+      float* dqrow = p.dq_acc + (((long long)b * p.S + q_idx) * p.H + h) * 128;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t rr[32];
+        tmem_ld32(tS + lane_off + c * 32, rr);
+        tmem_wait_ld();
+        if (row_ok) {
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            float4 v = make_float4(__uint_as_float(rr[4 * g]), __uint_as_float(rr[4 * g + 1]),
+                                   __uint_as_float(rr[4 * g + 2]), __uint_as_float(rr[4 * g + 3]));
+            atomicAdd(reinterpret_cast<float4*>(dqrow + c * 32 + g * 4), v);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dq_drained);
+    }
+    // epilogue: dK, dV rows of this key block (every MMA has completed: dq_full was the last commit)
+    if (ok) {
+      tc_fence_after();
+      const int kv_idx = kv0 + r;
+      __nv_bfloat16* dkrow = p.dk + b * p.k_sb + (long long)kv_idx * p.k_ss + hk * p.k_sh;
+      __nv_bfloat16* dvrow = p.dv + b * p.v_sb + (long long)kv_idx * p.v_ss + hk * p.v_sh;
+#pragma unroll 1
+      for (int c = 0; c < 8; ++c) {
+        uint32_t rr[32];
+        if (n > 0) {
+          tmem_ld32((c < 4 ? tdK : tdV) + lane_off + (c & 3) * 32, rr);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) rr[e] = 0u;
+        }
+        if (kv_idx < p.S) {
+          __nv_bfloat16* dst = (c < 4 ? dkrow : dvrow) + (c & 3) * 32;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 v;
+            v.x = pack_bf16(__uint_as_float(rr[g * 8 + 0]), __uint_as_float(rr[g * 8 + 1]));
+            v.y = pack_bf16(__uint_as_float(rr[g * 8 + 2]), __uint_as_float(rr[g * 8 + 3]));
+            v.z = pack_bf16(__uint_as_float(rr[g * 8 + 4]), __uint_as_float(rr[g * 8 + 5]));
+            v.w = pack_bf16(__uint_as_float(rr[g * 8 + 6]), __uint_as_float(rr[g * 8 + 7]));
+            *reinterpret_cast<uint4*>(dst + g * 8) = v;
+          }
+        }
+      }
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+static int make_qkv_map(CUtensorMap* m, const void* ptr, int B, int S, int H, long long sb, long long ss,
+                        long long sh) {
+  return make_tmap_4d(m, ptr, 2, 128, S, ss, H, sh, B, sb, 64, 128);
+}
+
+}  // namespace lb
+
+using namespace lb;
+
+extern "C" int lb_attn_fwd(const LbAttnArgs* a, void* stream) {
+  if (a->D != 128) return 1;
+  if (a->H % a->Hkv) return 2;
+  if (a->doc_start && !a->causal) return 3;
+  if (a->B <= 0 || a->S <= 0) return 0;
+  CUtensorMap tq, tk, tv;
+  if (make_qkv_map(&tq, a->q, a->B, a->S, a->H, a->q_sb, a->q_ss, a->q_sh)) return 10;
+  if (make_qkv_map(&tk, a->k, a->B, a->S, a->Hkv, a->k_sb, a->k_ss, a->k_sh)) return 11;
+  if (make_qkv_map(&tv, a->v, a->B, a->S, a->Hkv, a->v_sb, a->v_ss, a->v_sh)) return 12;
+  AttnParams p = {};
+  p.B = a->B; p.S = a->S; p.H = a->H; p.Hkv = a->Hkv;
+  p.causal = a->causal; p.window = a->window; p.scale = a->scale;
+  p.doc_start = a->doc_start; p.doc_end = a->doc_end;
+  p.O = (__nv_bfloat16*)a->o; p.lse = a->lse; p.status = a->status;
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM) != cudaSuccess)
+      return 20;
+    attr = true;
+  }
+  dim3 grid((a->S + 127) / 128, a->H, a->B);
+  attn_fwd_kernel<<<grid, AT_THREADS, FWD_SMEM, (cudaStream_t)stream>>>(tq, tk, tv, p);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}
+
+// Needs a->delta ([B,H,S] fp32) and a->dq_acc ([B,S,H,128] fp32) as scratch; dq_acc is cleared here.
+extern "C" int lb_attn_bwd(const LbAttnArgs* a, void* stream) {
+  if (a->D != 128) return 1;
+  if (a->H % a->Hkv) return 2;
+  if (a->doc_start && !a->causal) return 3;
+  if (!a->delta || !a->dq_acc || !a->lse) return 4;
+  if (a->B <= 0 || a->S <= 0) return 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  CUtensorMap tq, tk, tv, tdo;
+  if (make_qkv_map(&tq, a->q, a->B, a->S, a->H, a->q_sb, a->q_ss, a->q_sh)) return 10;
+  if (make_qkv_map(&tk, a->k, a->B, a->S, a->Hkv, a->k_sb, a->k_ss, a->k_sh)) return 11;
+  if (make_qkv_map(&tv, a->v, a->B, a->S, a->Hkv, a->v_sb, a->v_ss, a->v_sh)) return 12;
+  if (make_qkv_map(&tdo, a->dout, a->B, a->S, a->H, (long long)a->S * a->H * 128, (long long)a->H * 128, 128)) return 13;
+  const long long rows = (long long)a->B * a->S * a->H;
+  attn_delta_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, st>>>(
+      (const __nv_bfloat16*)a->o, (const __nv_bfloat16*)a->dout, a->delta, a->B, a->S, a->H);
+  if (cudaMemsetAsync(a->dq_acc, 0, rows * 128 * sizeof(float), st) != cudaSuccess) return 21;
+  AttnParams p = {};
+  p.B = a->B; p.S = a->S; p.H = a->H; p.Hkv = a->Hkv;
+  p.causal = a->causal; p.window = a->window; p.scale = a->scale;
+  p.doc_start = a->doc_start; p.doc_end = a->doc_end;
+  p.lse = a->lse; p.delta = a->delta; p.dq_acc = a->dq_acc;
+  p.dk = (__nv_bfloat16*)a->dk; p.dv = (__nv_bfloat16*)a->dv;
+  p.k_sb = a->k_sb; p.k_ss = a->k_ss; p.k_sh = a->k_sh;
+  p.v_sb = a->v_sb; p.v_ss = a->v_ss; p.v_sh = a->v_sh;
+  p.status = a->status;
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM) != cudaSuccess)
+      return 20;
+    attr = true;
+  }
+  dim3 grid((a->S + 127) / 128, a->Hkv, a->B);
+  attn_bwd_kernel<<<grid, AT_THREADS, BWD_SMEM, st>>>(tq, tk, tv, tdo, p);
+  long long total = rows * 16;
+  int blocks = (int)((total + 255) / 256 < (long long)num_sms() * 8 ? (total + 255) / 256 : (long long)num_sms() * 8);
+  attn_dq_store_kernel<<<blocks, 256, 0, st>>>(a->dq_acc, (__nv_bfloat16*)a->dq, a->B, a->S, a->H, a->q_sb, a->q_ss, a->q_sh);
+  g_launches.fetch_add(4, std::memory_order_relaxed);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}

@@ -1,0 +1,642 @@
+// Memory-bound kernels of the transformer path: RMSNorm (+ residual add), RoPE, SwiGLU /
+// squared-ReLU, embedding gather / scatter-add, softmax cross-entropy over a logits chunk,
+// AdamW on flat shards, gradient sum of squares. All take bf16 activations, do their math
+// in fp32 (as lingua/transformer.py:51-56,126-139,283-289 do) and move 16 bytes per access.
+#include "common.cuh"
+#include "lingua_b200.h"
+
+namespace lb {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+  return v;
+}
+// Block-wide sum; `red` holds >= 33 floats. Every thread gets the result.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  if (w == 0) {
+    float t = lane < nw ? red[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  if (w == 0) {
+    float t = lane < nw ? red[lane] : -INFINITY;
+    t = warp_max(t);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+
+struct bf16x8 {
+  uint4 raw;
+  __device__ __forceinline__ void unpack(float (&f)[8]) const {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 t = __bfloat1622float2(h[i]);
+      f[2 * i] = t.x;
+      f[2 * i + 1] = t.y;
+    }
+  }
+  __device__ __forceinline__ void pack(const float (&f)[8]) {
+    raw.x = pack_bf16(f[0], f[1]);
+    raw.y = pack_bf16(f[2], f[3]);
+    raw.z = pack_bf16(f[4], f[5]);
+    raw.w = pack_bf16(f[6], f[7]);
+  }
+};
+__device__ __forceinline__ bf16x8 ld8(const __nv_bfloat16* p) {
+  bf16x8 v;
+  v.raw = *reinterpret_cast<const uint4*>(p);
+  return v;
+}
+__device__ __forceinline__ void st8(__nv_bfloat16* p, const bf16x8& v) {
+  *reinterpret_cast<uint4*>(p) = v.raw;
+}
+
+// ------------------------------------------------------------------ RMSNorm
+// One block per row. h = x (+ res); y = h * rsqrt(mean(h^2) + eps) * w.
+// If res != null the sum h is also written to h_out (the new residual stream).
+constexpr int NORM_MAX_VEC = 4;  // per-thread 8-element vectors kept in registers: D <= 256*8*4
+
+__global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(
+    const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
+    __nv_bfloat16* __restrict__ h_out, float* __restrict__ rstd_out, int D, float eps) {
+  __shared__ float red[33];
+  const long long row = blockIdx.x;
+  const __nv_bfloat16* xr = x + row * D;
+  const int nvec = D / 8;
+  float vals[NORM_MAX_VEC][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NORM_MAX_VEC; ++i) {
+    const int v = threadIdx.x + i * blockDim.x;
+    if (v < nvec) {
+      ld8(xr + v * 8).unpack(vals[i]);
+      if (res) {
+        float r[8];
+        ld8(res + row * D + v * 8).unpack(r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) vals[i][j] += r[j];
+        bf16x8 o;
+        o.pack(vals[i]);
+        st8(h_out + row * D + v * 8, o);
+        o.unpack(vals[i]);  // the normalised value uses the rounded residual, as a reload would
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += vals[i][j] * vals[i][j];
+    }
+  }
+  ss = block_sum(ss, red);
+  const float rstd = rsqrtf(ss / D + eps);
+  if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
+#pragma unroll
+  for (int i = 0; i < NORM_MAX_VEC; ++i) {
+    const int v = threadIdx.x + i * blockDim.x;
+    if (v < nvec) {
+      float wv[8], o[8];
+      ld8(w + v * 8).unpack(wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = vals[i][j] * rstd * wv[j];
+      bf16x8 ov;
+      ov.pack(o);
+      st8(y + row * D + v * 8, ov);
+    }
+  }
+}
+
+// dx = rstd * (dy*w - xhat * mean(dy*w*xhat)) (+ dres); dw += sum_rows dy * xhat (fp32 atomics).
+// Persistent over rows so that each block issues one set of atomics.
+__global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(
+    const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
+    const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
+    float* __restrict__ dw, int M, int D) {
+  __shared__ float red[33];
+  const int nvec = D / 8;
+  float dwacc[NORM_MAX_VEC][8];
+  float wv[NORM_MAX_VEC][8];
+#pragma unroll
+  for (int i = 0; i < NORM_MAX_VEC; ++i) {
+    const int v = threadIdx.x + i * blockDim.x;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
+    if (v < nvec) ld8(w + v * 8).unpack(wv[i]);
+  }
+  for (long long row = blockIdx.x; row < M; row += gridDim.x) {
+    const float rs = rstd[row];
+    float xh[NORM_MAX_VEC][8], g[NORM_MAX_VEC][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NORM_MAX_VEC; ++i) {
+      const int v = threadIdx.x + i * blockDim.x;
+      if (v < nvec) {
+        float xv[8], dv[8];
+        ld8(x + row * D + v * 8).unpack(xv);
+        ld8(dy + row * D + v * 8).unpack(dv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[i][j] = xv[j] * rs;
+          g[i][j] = dv[j] * wv[i][j];
+          dot += g[i][j] * xh[i][j];
+          dwacc[i][j] += dv[j] * xh[i][j];
+        }
+      }
+    }
+    dot = block_sum(dot, red) / D;
+#pragma unroll
+    for (int i = 0; i < NORM_MAX_VEC; ++i) {
+      const int v = threadIdx.x + i * blockDim.x;
+      if (v < nvec) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rs * (g[i][j] - xh[i][j] * dot);
+        if (dres) {
+          float r[8];
+          ld8(dres + row * D + v * 8).unpack(r);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += r[j];
+        }
+        bf16x8 ov;
+        ov.pack(o);
+        st8(dx + row * D + v * 8, ov);
+      }
+    }
+  }
+  if (dw) {
+#pragma unroll
+    for (int i = 0; i < NORM_MAX_VEC; ++i) {
+      const int v = threadIdx.x + i * blockDim.x;
+      if (v < nvec) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) atomicAdd(dw + v * 8 + j, dwacc[i][j]);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ RoPE
+// In-place rotation of interleaved pairs of the first n_rot_heads heads of every token row
+// (row stride `ld` elements). cs[pos][i] = (cos, sin) of pos * theta^(-2i/Dh).
+// sign = +1 forward, -1 backward (the transpose of a rotation is the opposite rotation).
+__global__ void rope_kernel(__nv_bfloat16* __restrict__ qk, const float2* __restrict__ cs,
+                            const int* __restrict__ pos_idx, long long n_tok, int seq_len, int ld,
+                            int n_rot_heads, int head_dim, float sign) {
+  const int vec_per_head = head_dim / 8;
+  const long long total = n_tok * n_rot_heads * vec_per_head;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int v = i % vec_per_head;
+    const long long th = i / vec_per_head;
+    const int h = th % n_rot_heads;
+    const long long tok = th / n_rot_heads;
+    const int pos = pos_idx ? pos_idx[tok] : (int)(tok % seq_len);
+    __nv_bfloat16* p = qk + tok * ld + h * head_dim + v * 8;
+    float f[8], o[8];
+    ld8(p).unpack(f);
+    const float4* c4 = reinterpret_cast<const float4*>(cs + (long long)pos * (head_dim / 2) + v * 4);
+    const float4 c01 = c4[0], c23 = c4[1];
+    const float cc[4] = {c01.x, c01.z, c23.x, c23.z};
+    const float sn[4] = {c01.y * sign, c01.w * sign, c23.y * sign, c23.w * sign};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      o[2 * j] = f[2 * j] * cc[j] - f[2 * j + 1] * sn[j];
+      o[2 * j + 1] = f[2 * j] * sn[j] + f[2 * j + 1] * cc[j];
+    }
+    bf16x8 ov;
+    ov.pack(o);
+    st8(p, ov);
+  }
+}
+
+// ------------------------------------------------------------------ gated activations
+// gu: [M, 2H] with the gate in columns [0,H) and the linear branch in [H,2H).
+// mode 0: silu(g) * u (SwiGLU).  mode 1: relu(g)^2 * u.
+__device__ __forceinline__ float act_f(float g, int mode) {
+  if (mode == 0) return g / (1.f + __expf(-g));
+  const float r = fmaxf(g, 0.f);
+  return r * r;
+}
+__device__ __forceinline__ float act_df(float g, int mode) {
+  if (mode == 0) {
+    const float s = 1.f / (1.f + __expf(-g));
+    return s * (1.f + g * (1.f - s));
+  }
+  return 2.f * fmaxf(g, 0.f);
+}
+__global__ void glu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
+                               long long M, int H, int mode) {
+  const int hv = H / 8;
+  const long long total = M * hv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / hv;
+    const int c = (i % hv) * 8;
+    float g[8], u[8], o[8];
+    ld8(gu + r * 2 * H + c).unpack(g);
+    ld8(gu + r * 2 * H + H + c).unpack(u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = act_f(g[j], mode) * u[j];
+    bf16x8 ov;
+    ov.pack(o);
+    st8(out + r * H + c, ov);
+  }
+}
+// dgu[:, :H] = dout * u * act'(g); dgu[:, H:] = dout * act(g). dgu may alias gu.
+__global__ void glu_bwd_kernel(const __nv_bfloat16* gu, const __nv_bfloat16* __restrict__ dout,
+                               __nv_bfloat16* dgu, long long M, int H, int mode) {
+  const int hv = H / 8;
+  const long long total = M * hv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / hv;
+    const int c = (i % hv) * 8;
+    float g[8], u[8], d[8], dg[8], du[8];
+    ld8(gu + r * 2 * H + c).unpack(g);
+    ld8(gu + r * 2 * H + H + c).unpack(u);
+    ld8(dout + r * H + c).unpack(d);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      dg[j] = d[j] * u[j] * act_df(g[j], mode);
+      du[j] = d[j] * act_f(g[j], mode);
+    }
+    bf16x8 a, b;
+    a.pack(dg);
+    b.pack(du);
+    st8(dgu + r * 2 * H + c, a);
+    st8(dgu + r * 2 * H + H + c, b);
+  }
+}
+// Ungated activation on [n]: mode 0 silu, 1 relu^2. bwd: dx = dy * act'(x).
+__global__ void act_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
+                               long long n8, int mode) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n8;
+       i += (long long)gridDim.x * blockDim.x) {
+    float f[8];
+    ld8(x + i * 8).unpack(f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = act_f(f[j], mode);
+    bf16x8 o;
+    o.pack(f);
+    st8(y + i * 8, o);
+  }
+}
+__global__ void act_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy,
+                               __nv_bfloat16* __restrict__ dx, long long n8, int mode) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n8;
+       i += (long long)gridDim.x * blockDim.x) {
+    float f[8], d[8];
+    ld8(x + i * 8).unpack(f);
+    ld8(dy + i * 8).unpack(d);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = d[j] * act_df(f[j], mode);
+    bf16x8 o;
+    o.pack(f);
+    st8(dx + i * 8, o);
+  }
+}
+
+// out = a + b (bf16, fp32 math)
+__global__ void add_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
+                           __nv_bfloat16* __restrict__ out, long long n8) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n8;
+       i += (long long)gridDim.x * blockDim.x) {
+    float x[8], y[8];
+    ld8(a + i * 8).unpack(x);
+    ld8(b + i * 8).unpack(y);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] += y[j];
+    bf16x8 o;
+    o.pack(x);
+    st8(out + i * 8, o);
+  }
+}
+
+// ------------------------------------------------------------------ embedding
+__global__ void embed_fwd_kernel(const long long* __restrict__ tok, const __nv_bfloat16* __restrict__ table,
+                                 __nv_bfloat16* __restrict__ out, long long n_tok, int D, int V) {
+  const int dv = D / 8;
+  const long long total = n_tok * dv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / dv;
+    const int c = (i % dv) * 8;
+    long long id = tok[t];
+    id = id < 0 ? 0 : (id >= V ? V - 1 : id);
+    st8(out + t * D + c, ld8(table + id * D + c));
+  }
+}
+// dtable[tok] += dy  (fp32 accumulation buffer)
+__global__ void embed_bwd_kernel(const long long* __restrict__ tok, const __nv_bfloat16* __restrict__ dy,
+                                 float* __restrict__ dtable, long long n_tok, int D, int V) {
+  const int dv = D / 8;
+  const long long total = n_tok * dv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / dv;
+    const int c = (i % dv) * 8;
+    long long id = tok[t];
+    if (id < 0 || id >= V) continue;
+    float f[8];
+    ld8(dy + t * D + c).unpack(f);
+    float* dst = dtable + id * D + c;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) atomicAdd(dst + j, f[j]);
+  }
+}
+
+// ------------------------------------------------------------------ cross-entropy
+// One block per row of fp32 logits [rows, V]. Writes loss[row] = lse - logit[target] and
+// lse[row]; rows whose target is ignore_index (< 0) get loss 0.
+__global__ void __launch_bounds__(512) ce_fwd_kernel(const float* __restrict__ logits,
+                                                     const long long* __restrict__ target,
+                                                     float* __restrict__ loss, float* __restrict__ lse,
+                                                     int V, long long ld) {
+  __shared__ float red[33];
+  const long long row = blockIdx.x;
+  const float* lr = logits + row * ld;
+  const int nv = V / 4;
+  float mx = -INFINITY;
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    const float4 v = reinterpret_cast<const float4*>(lr)[i];
+    mx = fmaxf(mx, fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)));
+  }
+  mx = block_max(mx, red);
+  float s = 0.f;
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    const float4 v = reinterpret_cast<const float4*>(lr)[i];
+    s += __expf(v.x - mx) + __expf(v.y - mx) + __expf(v.z - mx) + __expf(v.w - mx);
+  }
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) {
+    const float l = mx + logf(s);
+    lse[row] = l;
+    const long long t = target[row];
+    loss[row] = (t >= 0 && t < V) ? l - lr[t] : 0.f;
+  }
+}
+// dlogits[row] = (softmax(logits[row]) - onehot(target)) * scale[0] * gscale, as bf16.
+__global__ void __launch_bounds__(512) ce_bwd_kernel(const float* __restrict__ logits,
+                                                     const long long* __restrict__ target,
+                                                     const float* __restrict__ lse,
+                                                     const float* __restrict__ gscale_ptr, float scale,
+                                                     __nv_bfloat16* __restrict__ dlogits, int V,
+                                                     long long ld, long long ldd) {
+  const long long row = blockIdx.x;
+  const float* lr = logits + row * ld;
+  __nv_bfloat16* dr = dlogits + row * ldd;
+  const long long t = target[row];
+  const bool valid = t >= 0 && t < V;
+  const float sc = valid ? scale * (gscale_ptr ? gscale_ptr[0] : 1.f) : 0.f;
+  const float l = lse[row];
+  const int nv = V / 8;
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    const float4 a = reinterpret_cast<const float4*>(lr)[2 * i];
+    const float4 b = reinterpret_cast<const float4*>(lr)[2 * i + 1];
+    float f[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float p = __expf(f[j] - l);
+      if (i * 8 + j == t) p -= 1.f;
+      f[j] = p * sc;
+    }
+    bf16x8 o;
+    o.pack(f);
+    st8(dr + i * 8, o);
+  }
+}
+
+// ------------------------------------------------------------------ optimiser
+// sum of squares of a flat fp32 buffer, accumulated into out[0] (fp32 atomics of per-block
+// partials that were reduced in double).
+__global__ void __launch_bounds__(512) sumsq_kernel(const float* __restrict__ g, long long n,
+                                                    float* __restrict__ out) {
+  __shared__ float red[33];
+  float s = 0.f;
+  const long long n4 = n / 4;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float4 v = reinterpret_cast<const float4*>(g)[i];
+    s += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  if (blockIdx.x == 0)
+    for (long long i = n4 * 4 + threadIdx.x; i < n; i += blockDim.x) s += g[i] * g[i];
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) atomicAdd(out, s);
+}
+
+// AdamW on a flat fp32 shard (torch.optim.AdamW semantics: decoupled weight decay, bias
+// correction), with the clip coefficient min(1, max_norm / (sqrt(sumsq) + 1e-6)) taken from
+// a device scalar so that no host synchronisation is needed, and the updated weights
+// written back both as fp32 master and as bf16 compute copy.
+__global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ p, float* __restrict__ m,
+                                                    float* __restrict__ v, const float* __restrict__ g,
+                                                    __nv_bfloat16* __restrict__ p16, long long n,
+                                                    const float* __restrict__ sumsq, float max_norm,
+                                                    float grad_mul, float lr, float beta1, float beta2,
+                                                    float eps, float wd, float bc1, float bc2_sqrt) {
+  float clip = grad_mul;
+  if (sumsq && max_norm > 0.f) {
+    const float nrm = sqrtf(sumsq[0]) * grad_mul;
+    clip *= fminf(1.f, max_norm / (nrm + 1e-6f));
+  }
+  const long long n4 = n / 4;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4;
+       i += (long long)gridDim.x * blockDim.x) {
+    float4 pv = reinterpret_cast<float4*>(p)[i];
+    float4 mv = reinterpret_cast<float4*>(m)[i];
+    float4 vv = reinterpret_cast<float4*>(v)[i];
+    const float4 gv = reinterpret_cast<const float4*>(g)[i];
+    float pa[4] = {pv.x, pv.y, pv.z, pv.w}, ma[4] = {mv.x, mv.y, mv.z, mv.w};
+    float va[4] = {vv.x, vv.y, vv.z, vv.w};
+    const float ga[4] = {gv.x * clip, gv.y * clip, gv.z * clip, gv.w * clip};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      pa[j] *= (1.f - lr * wd);
+      ma[j] = beta1 * ma[j] + (1.f - beta1) * ga[j];
+      va[j] = beta2 * va[j] + (1.f - beta2) * ga[j] * ga[j];
+      const float denom = sqrtf(va[j]) / bc2_sqrt + eps;
+      pa[j] -= (lr / bc1) * ma[j] / denom;
+    }
+    reinterpret_cast<float4*>(p)[i] = make_float4(pa[0], pa[1], pa[2], pa[3]);
+    reinterpret_cast<float4*>(m)[i] = make_float4(ma[0], ma[1], ma[2], ma[3]);
+    reinterpret_cast<float4*>(v)[i] = make_float4(va[0], va[1], va[2], va[3]);
+    if (p16) {
+      uint2 o;
+      o.x = pack_bf16(pa[0], pa[1]);
+      o.y = pack_bf16(pa[2], pa[3]);
+      reinterpret_cast<uint2*>(p16)[i] = o;
+    }
+  }
+  if (blockIdx.x == 0) {
+    for (long long i = n4 * 4 + threadIdx.x; i < n; i += blockDim.x) {
+      float pa = p[i] * (1.f - lr * wd);
+      const float ga = g[i] * clip;
+      const float ma = beta1 * m[i] + (1.f - beta1) * ga;
+      const float va = beta2 * v[i] + (1.f - beta2) * ga * ga;
+      pa -= (lr / bc1) * ma / (sqrtf(va) / bc2_sqrt + eps);
+      p[i] = pa; m[i] = ma; v[i] = va;
+      if (p16) p16[i] = __float2bfloat16(pa);
+    }
+  }
+}
+
+__global__ void cast_f32_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst,
+                                     long long n) {
+  const long long n4 = n / 4;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float4 v = reinterpret_cast<const float4*>(src)[i];
+    uint2 o;
+    o.x = pack_bf16(v.x, v.y);
+    o.y = pack_bf16(v.z, v.w);
+    reinterpret_cast<uint2*>(dst)[i] = o;
+  }
+  if (blockIdx.x == 0)
+    for (long long i = n4 * 4 + threadIdx.x; i < n; i += blockDim.x) dst[i] = __float2bfloat16(src[i]);
+}
+
+static inline int grid_for(long long work_items, int threads, int per_sm = 8) {
+  long long b = (work_items + threads - 1) / threads;
+  const long long cap = (long long)num_sms() * per_sm;
+  if (b > cap) b = cap;
+  if (b < 1) b = 1;
+  return (int)b;
+}
+#define LB_LAUNCH_END()                                  \
+  g_launches.fetch_add(1, std::memory_order_relaxed);    \
+  {                                                      \
+    cudaError_t e__ = cudaGetLastError();                \
+    return e__ == cudaSuccess ? 0 : 400 + (int)e__;      \
+  }
+
+}  // namespace lb
+
+using namespace lb;
+typedef __nv_bfloat16 bf16;
+#define S_(s) reinterpret_cast<cudaStream_t>(s)
+
+extern "C" int lb_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* h_out,
+                              float* rstd, long long M, int D, float eps, void* stream) {
+  if (D % 8 || D > 256 * 8 * NORM_MAX_VEC) return 1;
+  if (M == 0) return 0;
+  rmsnorm_fwd_kernel<<<(unsigned)M, 256, 0, S_(stream)>>>((const bf16*)x, (const bf16*)res, (const bf16*)w,
+                                                          (bf16*)y, (bf16*)h_out, rstd, D, eps);
+  LB_LAUNCH_END();
+}
+extern "C" int lb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd,
+                              const void* dres, void* dx, float* dw, long long M, int D, void* stream) {
+  if (D % 8 || D > 256 * 8 * NORM_MAX_VEC) return 1;
+  if (M == 0) return 0;
+  long long grid = M < num_sms() * 4 ? M : num_sms() * 4;
+  rmsnorm_bwd_kernel<<<(unsigned)grid, 256, 0, S_(stream)>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w,
+                                                             rstd, (const bf16*)dres, (bf16*)dx, dw, (int)M, D);
+  LB_LAUNCH_END();
+}
+extern "C" int lb_rope(void* qk, const void* cs, const int* pos_idx, long long n_tok, int seq_len, int ld,
+                       int n_rot_heads, int head_dim, int backward, void* stream) {
+  if (head_dim % 8 || ld % 8) return 1;
+  const long long total = n_tok * n_rot_heads * (head_dim / 8);
+  if (total == 0) return 0;
+  rope_kernel<<<grid_for(total, 256), 256, 0, S_(stream)>>>((bf16*)qk, (const float2*)cs, pos_idx, n_tok, seq_len,
+                                                            ld, n_rot_heads, head_dim, backward ? -1.f : 1.f);
+  LB_LAUNCH_END();
+}
+extern "C" int lb_glu_fwd(const void* gu, void* out, long long M, int H, int mode, void* stream) {
+  if (H % 8) return 1;
+  glu_fwd_kernel<<<grid_for(M * (H / 8), 256), 256, 0, S_(stream)>>>((const bf16*)gu, (bf16*)out, M, H, mode);
+  LB_LAUNCH_END();
+}
+extern "C" int lb_glu_bwd(const void* gu, const void* dout, void* dgu, long long M, int H, int mode, void* stream) {
+  if (H % 8) return 1;
+  glu_bwd_kernel<<<grid_for(M * (H / 8), 256), 256, 0, S_(stream)>>>((const bf16*)gu, (const bf16*)dout, (bf16*)dgu, M, H, mode);
+  LB_LAUNCH_END();
+}
+extern "C" int lb_act_fwd(const void* x, void* y, long long n, int mode, void* stream) {
+  if (n % 8) return 1;
+  act_fwd_kernel<<<grid_for(n / 8, 256), 256, 0, S_(stream)>>>((const bf16*)x, (bf16*)y, n / 8, mode);
+  LB_LAUNCH_END();
+}
+extern "C" int lb_act_bwd(const void* x, const void* dy, void* dx, long long n, int mode, void* stream) {
+  if (n % 8) return 1;
+  act_bwd_kernel<<<grid_for(n / 8, 256), 256, 0, S_(stream)>>>((const bf16*)x, (const bf16*)dy, (bf16*)dx, n / 8, mode);
+  LB_LAUNCH_END();
+}
+extern "C" int lb_add(const void* a, const void* b, void* out, long long n, void* stream) {
+  if (n % 8) return 1;
+  add_kernel<<<grid_for(n / 8, 256), 256, 0, S_(stream)>>>((const bf16*)a, (const bf16*)b, (bf16*)out, n / 8);
+  LB_LAUNCH_END();
+}
+extern "C" int lb_embed_fwd(const long long* tok, const void* table, void* out, long long n_tok, int D, int V,
+                            void* stream) {
+  if (D % 8) return 1;
+  embed_fwd_kernel<<<grid_for(n_tok * (D / 8), 256), 256, 0, S_(stream)>>>(tok, (const bf16*)table, (bf16*)out, n_tok, D, V);
+  LB_LAUNCH_END();
+}
+extern "C" int lb_embed_bwd(const long long* tok, const void* dy, float* dtable, long long n_tok, int D, int V,
+                            void* stream) {
+  if (D % 8) return 1;
+  embed_bwd_kernel<<<grid_for(n_tok * (D / 8), 256), 256, 0, S_(stream)>>>(tok, (const bf16*)dy, dtable, n_tok, D, V);
+  LB_LAUNCH_END();
+}
+extern "C" int lb_ce_fwd(const float* logits, const long long* target, float* loss, float* lse, long long rows,
+                         int V, long long ld, void* stream) {
+  if (V % 4 || ld % 4) return 1;
+  if (rows == 0) return 0;
+  ce_fwd_kernel<<<(unsigned)rows, 512, 0, S_(stream)>>>(logits, target, loss, lse, V, ld);
+  LB_LAUNCH_END();
+}
+extern "C" int lb_ce_bwd(const float* logits, const long long* target, const float* lse, const float* gscale,
+                         float scale, void* dlogits, long long rows, int V, long long ld, long long ldd,
+                         void* stream) {
+  if (V % 8 || ld % 4 || ldd % 8) return 1;
+  if (rows == 0) return 0;
+  ce_bwd_kernel<<<(unsigned)rows, 512, 0, S_(stream)>>>(logits, target, lse, gscale, scale, (bf16*)dlogits, V, ld, ldd);
+  LB_LAUNCH_END();
+}
+extern "C" int lb_sumsq(const float* g, long long n, float* out, void* stream) {
+  if (n == 0) return 0;
+  if (reinterpret_cast<uintptr_t>(g) % 16) return 1;
+  sumsq_kernel<<<grid_for(n / 4 + 1, 512, 4), 512, 0, S_(stream)>>>(g, n, out);
+  LB_LAUNCH_END();
+}
+extern "C" int lb_adamw(float* p, float* m, float* v, const float* g, void* p16, long long n, const float* sumsq,
+                        float max_norm, float grad_mul, float lr, float beta1, float beta2, float eps, float wd,
+                        int step, void* stream) {
+  if (n == 0) return 0;
+  if ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(g)) % 16 || reinterpret_cast<uintptr_t>(p16) % 8)
+    return 1;
+  const float bc1 = 1.f - powf(beta1, (float)step);
+  const float bc2s = sqrtf(1.f - powf(beta2, (float)step));
+  adamw_kernel<<<grid_for(n / 4 + 1, 256, 8), 256, 0, S_(stream)>>>(p, m, v, g, (bf16*)p16, n, sumsq, max_norm,
+                                                                    grad_mul, lr, beta1, beta2, eps, wd, bc1, bc2s);
+  LB_LAUNCH_END();
+}
+extern "C" int lb_cast_f32_bf16(const float* src, void* dst, long long n, void* stream) {
+  if (n == 0) return 0;
+  if (reinterpret_cast<uintptr_t>(src) % 16 || reinterpret_cast<uintptr_t>(dst) % 8) return 1;
+  cast_f32_bf16_kernel<<<grid_for(n / 4 + 1, 256, 8), 256, 0, S_(stream)>>>(src, (bf16*)dst, n);
+  LB_LAUNCH_END();
+}

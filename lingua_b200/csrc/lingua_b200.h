@@ -33,14 +33,42 @@ typedef struct LbGemmArgs {
 
 int lb_gemm(const LbGemmArgs* args, void* stream);
 
+// Flash attention, head_dim 128. q/k/v (and dq/dk/dv, which use the same strides) are
+// [B,S,H,128] views given by element strides; o and dout are contiguous [B,S,H,128].
+// lse: [B,H,S] fp32. doc_start / doc_end: [B*S] int32 or NULL (block-causal masking).
+// Backward scratch, supplied by the caller: delta [B,H,S] fp32, dq_acc [B,S,H,128] fp32.
+typedef struct LbAttnArgs {
+  const void *q, *k, *v;
+  void* o;
+  float* lse;
+  const void* dout;
+  void *dq, *dk, *dv;
+  float* delta;
+  float* dq_acc;
+  const int* doc_start;
+  const int* doc_end;
+  uint32_t* status;
+  int B, S, H, Hkv, D;
+  int causal, window;
+  float scale;
+  long long q_sb, q_ss, q_sh, k_sb, k_ss, k_sh, v_sb, v_ss, v_sh;
+} LbAttnArgs;
+int lb_attn_fwd(const LbAttnArgs* a, void* stream);
+int lb_attn_bwd(const LbAttnArgs* a, void* stream);
+
 // Number of kernels launched by this library in this process so far.
 long long lb_launch_count(void);
 void lb_launch_count_add(long long n);
 
 #ifdef __cplusplus
 }
+#include <cuda.h>
 namespace lb {
 extern std::atomic<long long> g_launches;
 int num_sms();
+// 4-D TMA map {inner, outer, batch0, batch1} with the 128-byte swizzle; strides in elements.
+int make_tmap_4d(CUtensorMap* out, const void* base, int esz, long long inner, long long outer,
+                 long long ld, int nb0, long long bs0, int nb1, long long bs1, int box_inner,
+                 int box_outer);
 }
 #endif

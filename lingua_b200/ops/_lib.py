@@ -36,6 +36,20 @@ class GemmArgs(C.Structure):
     ]
 
 
+class AttnArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("o", C.c_void_p), ("lse", C.c_void_p),
+        ("dout", C.c_void_p), ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p),
+        ("delta", C.c_void_p), ("dq_acc", C.c_void_p),
+        ("doc_start", C.c_void_p), ("doc_end", C.c_void_p), ("status", C.c_void_p),
+        ("B", C.c_int), ("S", C.c_int), ("H", C.c_int), ("Hkv", C.c_int), ("D", C.c_int),
+        ("causal", C.c_int), ("window", C.c_int), ("scale", C.c_float),
+        ("q_sb", C.c_longlong), ("q_ss", C.c_longlong), ("q_sh", C.c_longlong),
+        ("k_sb", C.c_longlong), ("k_ss", C.c_longlong), ("k_sh", C.c_longlong),
+        ("v_sb", C.c_longlong), ("v_ss", C.c_longlong), ("v_sh", C.c_longlong),
+    ]
+
+
 def lib_path() -> Path:
     return _LIB_PATH
 
@@ -71,7 +85,26 @@ def load():
 def _declare(lib) -> None:
     """Signatures of the remaining entry points; a symbol that is absent is left undeclared."""
     vp, i, ll, f = C.c_void_p, C.c_int, C.c_longlong, C.c_float
-    sigs = {}
+    fp, ip, llp = C.c_void_p, C.c_void_p, C.c_void_p  # device pointers are passed as integers
+    sigs = {
+        "lb_rmsnorm_fwd": [vp, vp, vp, vp, vp, fp, ll, i, f, vp],
+        "lb_rmsnorm_bwd": [vp, vp, vp, fp, vp, vp, fp, ll, i, vp],
+        "lb_rope": [vp, vp, ip, ll, i, i, i, i, i, vp],
+        "lb_glu_fwd": [vp, vp, ll, i, i, vp],
+        "lb_glu_bwd": [vp, vp, vp, ll, i, i, vp],
+        "lb_act_fwd": [vp, vp, ll, i, vp],
+        "lb_act_bwd": [vp, vp, vp, ll, i, vp],
+        "lb_add": [vp, vp, vp, ll, vp],
+        "lb_embed_fwd": [llp, vp, vp, ll, i, i, vp],
+        "lb_embed_bwd": [llp, vp, fp, ll, i, i, vp],
+        "lb_ce_fwd": [fp, llp, fp, fp, ll, i, ll, vp],
+        "lb_ce_bwd": [fp, llp, fp, fp, f, vp, ll, i, ll, ll, vp],
+        "lb_sumsq": [fp, ll, fp, vp],
+        "lb_adamw": [fp, fp, fp, fp, vp, ll, fp, f, f, f, f, f, f, f, i, vp],
+        "lb_cast_f32_bf16": [fp, vp, ll, vp],
+        "lb_attn_fwd": [C.POINTER(AttnArgs), vp],
+        "lb_attn_bwd": [C.POINTER(AttnArgs), vp],
+    }
     for name, args in sigs.items():
         if hasattr(lib, name):
             fn = getattr(lib, name)
