@@ -382,12 +382,14 @@ __global__ void __launch_bounds__(512) ce_fwd_kernel(const float* __restrict__ l
     const float4 v = reinterpret_cast<const float4*>(lr)[i];
     mx = fmaxf(mx, fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w)));
   }
+  for (int i = nv * 4 + threadIdx.x; i < V; i += blockDim.x) mx = fmaxf(mx, lr[i]);
   mx = block_max(mx, red);
   float s = 0.f;
   for (int i = threadIdx.x; i < nv; i += blockDim.x) {
     const float4 v = reinterpret_cast<const float4*>(lr)[i];
     s += __expf(v.x - mx) + __expf(v.y - mx) + __expf(v.z - mx) + __expf(v.w - mx);
   }
+  for (int i = nv * 4 + threadIdx.x; i < V; i += blockDim.x) s += __expf(lr[i] - mx);
   s = block_sum(s, red);
   if (threadIdx.x == 0) {
     const float l = mx + logf(s);
@@ -424,6 +426,11 @@ __global__ void __launch_bounds__(512) ce_bwd_kernel(const float* __restrict__ l
     bf16x8 o;
     o.pack(f);
     st8(dr + i * 8, o);
+  }
+  for (int i = nv * 8 + threadIdx.x; i < V; i += blockDim.x) {
+    float p = __expf(lr[i] - l);
+    if (i == t) p -= 1.f;
+    dr[i] = __float2bfloat16(p * sc);
   }
 }
 
@@ -602,7 +609,7 @@ extern "C" int lb_embed_bwd(const long long* tok, const void* dy, float* dtable,
 }
 extern "C" int lb_ce_fwd(const float* logits, const long long* target, float* loss, float* lse, long long rows,
                          int V, long long ld, void* stream) {
-  if (V % 4 || ld % 4) return 1;
+  if (ld % 4) return 1;
   if (rows == 0) return 0;
   ce_fwd_kernel<<<(unsigned)rows, 512, 0, S_(stream)>>>(logits, target, loss, lse, V, ld);
   LB_LAUNCH_END();
@@ -610,7 +617,7 @@ extern "C" int lb_ce_fwd(const float* logits, const long long* target, float* lo
 extern "C" int lb_ce_bwd(const float* logits, const long long* target, const float* lse, const float* gscale,
                          float scale, void* dlogits, long long rows, int V, long long ld, long long ldd,
                          void* stream) {
-  if (V % 8 || ld % 4 || ldd % 8) return 1;
+  if (ld % 4 || ldd % 8) return 1;
   if (rows == 0) return 0;
   ce_bwd_kernel<<<(unsigned)rows, 512, 0, S_(stream)>>>(logits, target, lse, gscale, scale, (bf16*)dlogits, V, ld, ldd);
   LB_LAUNCH_END();

@@ -362,7 +362,8 @@ extern "C" int lb_gemm(const LbGemmArgs* args, void* stream) {
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (a.M <= 0 || a.N <= 0 || a.K <= 0 || a.nb0 <= 0 || a.nb1 <= 0) return 1;
   if (a.in_dtype != LB_BF16) return 2;  // fp8 operands go through lb_gemm_fp8
-  if ((a.N % 8) || (a.ldc % 8) || (a.lda % 8) || (a.ldb % 8)) return 3;
+  // rows of C are written in 8-element vectors: a ragged N needs ldc >= N rounded up to 8
+  if ((a.ldc % 8) || (a.lda % 8) || (a.ldb % 8) || a.ldc < ((a.N + 7) / 8) * 8) return 3;
   if (a.out_dtype == LB_BF16 && a.accumulate) return 4;
   // Narrow outputs use the 128-wide tile so that small N does not waste half of every MMA.
   const bool narrow = a.N <= 128 || a.force_bn == 128;

@@ -247,7 +247,7 @@ def ce_bwd(logits, target, lse, scale: float, gscale: Optional[torch.Tensor] = N
         g = scale * (gscale.float().reshape(()) if gscale is not None else 1.0)
         return (p * valid * g).to(out_dtype)
     rows, V = logits.shape
-    d = torch.empty(rows, V, dtype=torch.bfloat16, device=logits.device)
+    d = torch.empty(rows, (V + 7) // 8 * 8, dtype=torch.bfloat16, device=logits.device)[:, :V]
     _lib.check(_L().lb_ce_bwd(logits.data_ptr(), target.data_ptr(), lse.data_ptr(), _ptr(gscale), scale,
                               d.data_ptr(), rows, V, logits.stride(0), d.stride(0), _lib.stream_ptr()), "lb_ce_bwd")
     return d

@@ -1,0 +1,291 @@
+"""Autograd functions of the native transformer path.
+
+Each function is one "save point" of the layer: it keeps only what cannot be recomputed
+cheaply (GEMM outputs, the attention output and its log-sum-exp) and recomputes the
+memory-bound results (normalised activations, gated activation, logits) in backward.
+This is the fixed, per-op form of the selective activation checkpointing policy of
+lingua/distributed.py:43-53,298-308 (save matmul and attention outputs, recompute the rest).
+
+Weight gradients: when a weight tensor carries a ``main_grad`` attribute (an fp32 view into
+the sharded-parameter engine's gradient buffer) the wgrad GEMM writes or accumulates there
+directly and autograd receives ``None``; otherwise a gradient of the weight's dtype is returned.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import torch
+
+from . import functional as F
+from .attention import flash_bwd, flash_fwd
+from .gemm import gemm, mm_nn, mm_nt, mm_tn
+
+
+# ----------------------------------------------------------------------------- helpers
+def fused_view(ws: Sequence[torch.Tensor]) -> Optional[torch.Tensor]:
+    """[sum(N_i), K] view over row-blocks that are adjacent in memory, or None."""
+    if len(ws) == 1:
+        return ws[0]
+    base = ws[0]
+    K = base.shape[1]
+    ptr = base.data_ptr()
+    for w in ws:
+        if not w.is_contiguous() or w.shape[1] != K or w.data_ptr() != ptr or w.dtype != base.dtype:
+            return None
+        ptr += w.numel() * w.element_size()
+    rows = sum(w.shape[0] for w in ws)
+    return torch.as_strided(base, (rows, K), (K, 1), base.storage_offset())
+
+
+def _weights(ws: Sequence[torch.Tensor]) -> torch.Tensor:
+    v = fused_view([w.detach() for w in ws])
+    return v if v is not None else torch.cat([w.detach() for w in ws], dim=0)
+
+
+def _main_grads(ws: Sequence[torch.Tensor]) -> Optional[torch.Tensor]:
+    if not all(hasattr(w, "main_grad") for w in ws):
+        return None
+    return fused_view([w.main_grad for w in ws])
+
+
+def _emit_wgrad(ws: Sequence[torch.Tensor], dy2d: torch.Tensor, x2d: torch.Tensor) -> List[Optional[torch.Tensor]]:
+    """dW_i = dy[:, rows_i]^T x for the row-blocks ``ws`` of one fused weight."""
+    mg = _main_grads(ws)
+    if mg is not None:
+        written = [getattr(w, "grad_written", False) for w in ws]
+        if all(written) or not any(written):
+            mm_tn(dy2d, x2d, out=mg, accumulate=written[0])
+            for w in ws:
+                w.grad_written = True
+            return [None] * len(ws)
+    outs: List[Optional[torch.Tensor]] = []
+    r0 = 0
+    for w in ws:
+        n = w.shape[0]
+        dyi = dy2d[:, r0:r0 + n]
+        r0 += n
+        if hasattr(w, "main_grad"):
+            mm_tn(dyi, x2d, out=w.main_grad, accumulate=getattr(w, "grad_written", False))
+            w.grad_written = True
+            outs.append(None)
+        else:
+            outs.append(mm_tn(dyi, x2d, out_dtype=torch.float32).to(w.dtype))
+    return outs
+
+
+def _emit_vec_grad(w: torch.Tensor, fn) -> Optional[torch.Tensor]:
+    """Gradient of a 1-D weight through ``fn(dw_out)`` which accumulates into an fp32 buffer."""
+    if hasattr(w, "main_grad"):
+        if not getattr(w, "grad_written", False):
+            w.main_grad.zero_()
+            w.grad_written = True
+        fn(w.main_grad)
+        return None
+    buf = torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+    fn(buf)
+    return buf.to(w.dtype)
+
+
+# ----------------------------------------------------------------------------- linear
+class LinearFn(torch.autograd.Function):
+    """y = x [W_0; W_1; ...]^T for x [M, K] and row-blocks W_i [N_i, K]."""
+
+    @staticmethod
+    def forward(ctx, x, *ws):
+        ctx.save_for_backward(x)
+        ctx.ws = ws
+        return mm_nt(x, _weights(ws))
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x,) = ctx.saved_tensors
+        ws = ctx.ws
+        dy = dy.contiguous()
+        dx = mm_nn(dy, _weights(ws)) if ctx.needs_input_grad[0] else None
+        dws = _emit_wgrad(ws, dy, x) if ws[0].requires_grad else [None] * len(ws)
+        return (dx, *dws)
+
+
+class NormLinearFn(torch.autograd.Function):
+    """h = x (+ res); out = rmsnorm(h) * g @ [W_0; W_1; ...]^T. Returns (out, h); h is None
+    when no residual was given (the caller already holds x).
+
+    Saves h and the per-row rstd; the normalised activation is recomputed in backward."""
+
+    @staticmethod
+    def forward(ctx, x, res, g, eps, *ws):
+        y, h, rstd = F.rmsnorm_fwd(x, g.detach(), eps, res)
+        h = x if h is None else h
+        out = mm_nt(y, _weights(ws))
+        ctx.save_for_backward(h, rstd)
+        ctx.g, ctx.ws, ctx.eps, ctx.has_res = g, ws, eps, res is not None
+        return out, (h if res is not None else None)
+
+    @staticmethod
+    def backward(ctx, dout, dh_out):
+        h, rstd = ctx.saved_tensors
+        g, ws = ctx.g, ctx.ws
+        dout = dout.contiguous()
+        y, _, _ = F.rmsnorm_fwd(h, g.detach(), ctx.eps, None)
+        dws = _emit_wgrad(ws, dout, y) if ws[0].requires_grad else [None] * len(ws)
+        del y
+        dy = mm_nn(dout, _weights(ws))
+        dres_in = dh_out.contiguous() if dh_out is not None else None
+        holder = {}
+
+        def run(dw_buf):
+            holder["dx"], _ = F.rmsnorm_bwd(dy, h, g.detach(), rstd, dres_in, dw_buf)
+
+        dg = _emit_vec_grad(g, run)
+        dx = holder["dx"]
+        return (dx, dx if ctx.has_res else None, dg, None, *dws)
+
+
+class RopeAttnFn(torch.autograd.Function):
+    """qkv [B*S, (H + 2 Hkv) * Dh] -> RoPE on q and k (in place) -> attention -> [B*S, H * Dh]."""
+
+    @staticmethod
+    def forward(ctx, qkv, cs, B, S, H, Hkv, Dh, causal, doc_start, doc_end, window, pos):
+        F.rope_(qkv, cs, H + Hkv, Dh, S, pos)
+        t = qkv.view(B, S, H + 2 * Hkv, Dh)
+        q, k, v = t[:, :, :H], t[:, :, H:H + Hkv], t[:, :, H + Hkv:]
+        o, lse = flash_fwd(q, k, v, causal, doc_start, window)
+        ctx.save_for_backward(qkv, o, lse, cs, doc_start, doc_end, pos)
+        ctx.cfg = (B, S, H, Hkv, Dh, causal, window)
+        return o.view(B * S, H * Dh)
+
+    @staticmethod
+    def backward(ctx, do):
+        qkv, o, lse, cs, doc_start, doc_end, pos = ctx.saved_tensors
+        B, S, H, Hkv, Dh, causal, window = ctx.cfg
+        t = qkv.view(B, S, H + 2 * Hkv, Dh)
+        q, k, v = t[:, :, :H], t[:, :, H:H + Hkv], t[:, :, H + Hkv:]
+        dqkv = torch.empty_like(qkv)
+        dt = dqkv.view(B, S, H + 2 * Hkv, Dh)
+        flash_bwd(do.contiguous().view(B, S, H, Dh), q, k, v, o, lse, dt[:, :, :H], dt[:, :, H:H + Hkv],
+                  dt[:, :, H + Hkv:], causal, doc_start, doc_end, window)
+        F.rope_(dqkv, cs, H + Hkv, Dh, S, pos, backward=True)
+        return (dqkv,) + (None,) * 11
+
+
+class GluLinearFn(torch.autograd.Function):
+    """out = (act(gu[:, :H]) * gu[:, H:]) @ W^T; saves only gu."""
+
+    @staticmethod
+    def forward(ctx, gu, w, mode):
+        a = F.glu_fwd(gu, mode)
+        ctx.save_for_backward(gu)
+        ctx.w, ctx.mode = w, mode
+        return mm_nt(a, w.detach())
+
+    @staticmethod
+    def backward(ctx, dy):
+        (gu,) = ctx.saved_tensors
+        w = ctx.w
+        dy = dy.contiguous()
+        a = F.glu_fwd(gu, ctx.mode)
+        (dw,) = _emit_wgrad([w], dy, a) if w.requires_grad else (None,)
+        del a
+        da = mm_nn(dy, w.detach())
+        return F.glu_bwd(gu, da, ctx.mode), dw, None
+
+
+class ActLinearFn(torch.autograd.Function):
+    """out = act(u) @ W^T for an ungated FFN (squared ReLU); saves only u."""
+
+    @staticmethod
+    def forward(ctx, u, w, mode):
+        a = F.act_fwd(u, mode)
+        ctx.save_for_backward(u)
+        ctx.w, ctx.mode = w, mode
+        return mm_nt(a, w.detach())
+
+    @staticmethod
+    def backward(ctx, dy):
+        (u,) = ctx.saved_tensors
+        w = ctx.w
+        dy = dy.contiguous()
+        a = F.act_fwd(u, ctx.mode)
+        (dw,) = _emit_wgrad([w], dy, a) if w.requires_grad else (None,)
+        del a
+        da = mm_nn(dy, w.detach())
+        return F.act_bwd(u, da, ctx.mode), dw, None
+
+
+class EmbeddingFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, tokens, table):
+        ctx.save_for_backward(tokens)
+        ctx.table = table
+        return F.embed_fwd(tokens, table.detach())
+
+    @staticmethod
+    def backward(ctx, dy):
+        (tokens,) = ctx.saved_tensors
+        table = ctx.table
+        if not table.requires_grad:
+            return None, None
+        dy = dy.contiguous()
+        if hasattr(table, "main_grad"):
+            if not getattr(table, "grad_written", False):
+                table.main_grad.zero_()
+                table.grad_written = True
+            F.embed_bwd(tokens, dy, table.main_grad)
+            return None, None
+        buf = torch.zeros(table.shape, dtype=torch.float32, device=table.device)
+        F.embed_bwd(tokens, dy, buf)
+        return None, buf.to(table.dtype)
+
+
+class LinearCrossEntropyFn(torch.autograd.Function):
+    """mean_i CE(y_i W^T, target_i) over rows with target >= 0, without ever holding more than
+    ``chunk`` rows of logits. Forward keeps the per-row log-sum-exp; backward recomputes each
+    logits chunk, turns it into its gradient in one pass and feeds the two gradient GEMMs
+    (the loss of lingua/transformer.py:51-56 applied to apps/main/transformer.py:115-117)."""
+
+    @staticmethod
+    def forward(ctx, y, w, target, chunk):
+        M = y.shape[0]
+        wd = w.detach()
+        tgt = target.reshape(-1)
+        lse = torch.empty(M, dtype=torch.float32, device=y.device)
+        total = torch.zeros((), dtype=torch.float32, device=y.device)
+        for r0 in range(0, M, chunk):
+            r1 = min(M, r0 + chunk)
+            logits = gemm(y[r0:r1], wd, out_dtype=torch.float32)
+            loss_c, lse_c = F.ce_fwd(logits, tgt[r0:r1])
+            lse[r0:r1] = lse_c
+            total += loss_c.sum()
+            del logits
+        n_valid = (tgt >= 0).sum().clamp(min=1).float()
+        ctx.save_for_backward(y, tgt, lse, n_valid)
+        ctx.w, ctx.chunk = w, chunk
+        return total / n_valid
+
+    @staticmethod
+    def backward(ctx, g):
+        y, tgt, lse, n_valid = ctx.saved_tensors
+        w, chunk = ctx.w, ctx.chunk
+        wd = w.detach()
+        M = y.shape[0]
+        gscale = (g.float() / n_valid).reshape(1).contiguous()
+        dy = torch.empty_like(y)
+        has_mg = hasattr(w, "main_grad")
+        dw_acc = None
+        for r0 in range(0, M, chunk):
+            r1 = min(M, r0 + chunk)
+            logits = gemm(y[r0:r1], wd, out_dtype=torch.float32)
+            dl = F.ce_bwd(logits, tgt[r0:r1], lse[r0:r1], 1.0, gscale)
+            del logits
+            mm_nn(dl, wd, out=dy[r0:r1])
+            if w.requires_grad:
+                if has_mg:
+                    mm_tn(dl, y[r0:r1], out=w.main_grad, accumulate=getattr(w, "grad_written", False))
+                    w.grad_written = True
+                else:
+                    if dw_acc is None:
+                        dw_acc = torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+                    mm_tn(dl, y[r0:r1], out=dw_acc, accumulate=True)
+            del dl
+        dw = None if (has_mg or dw_acc is None) else dw_acc.to(w.dtype)
+        return dy, dw, None, None

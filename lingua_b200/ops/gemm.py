@@ -55,7 +55,9 @@ def gemm(
     batch = list(a.shape[:-2])
     assert list(b.shape[:-2]) == batch
     if out is None:
-        out = torch.empty(*batch, M, N, dtype=out_dtype, device=a.device)
+        # rows are stored in 8-element vectors: pad the row pitch of a ragged N
+        N8 = (N + 7) // 8 * 8
+        out = torch.empty(*batch, M, N8, dtype=out_dtype, device=a.device)[..., :N]
     else:
         assert out.shape[-2:] == (M, N) and out.stride(-1) == 1
     a_major, lda = _major_and_ld(a)

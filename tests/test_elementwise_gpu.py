@@ -9,7 +9,7 @@ DEV = "cuda"
 
 
 def close(a, b, tol=2e-2):
-    a, b = a.float(), b.float()
+    a, b = a.float().cpu(), b.float().cpu()
     err = (a - b).abs().max().item()
     ref = b.abs().max().item() + 1e-6
     assert err / ref < tol, f"rel {err / ref:.4g}"
