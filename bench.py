@@ -1,0 +1,298 @@
+"""Headline benchmark: Llama-7B training throughput (tokens/s, whole job) on N B200s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--model 7b|1b]
+
+N > 1 is launched by torchrun (one rank per GPU, NCCL); RANK / LOCAL_RANK / WORLD_SIZE /
+MASTER_* come from the environment. Weak scaling: every GPU trains batch 2 x 4096 tokens
+(the reference's apps/main/configs/llama_7B.yaml), FSDP full-shard over the N GPUs, bf16
+compute with fp32 master weights / optimiser state / gradient reduction, synthetic
+uniform-random tokens, random-init weights.
+
+Two numbers are measured over exactly K optimiser steps each, after W warm-up steps, with
+CUDA events between barrier + synchronize pairs, max over ranks:
+  * value: device-resident inputs, no host read-back inside the timed region;
+  * e2e:   the public ``Trainer.train_step`` call, which copies each step's token batch from
+           pinned host memory and reads the loss back to the host.
+Rank 0 prints one JSON line. ``--impl reference`` runs the unmodified reference from
+baseline/_ref (see baseline/reference_arm.py) under the same protocol.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+MODELS = {
+    # apps/main/configs/llama_7B.yaml (+ vocab of the 128k tiktoken tokenizer)
+    "7b": dict(dim=4096, n_layers=32, n_heads=32, rope_theta=100000.0, ffn_dim_multiplier=1.0, multiple_of=256,
+               vocab_size=128256, max_seqlen=4096),
+    # apps/main/configs/llama_1B.yaml
+    "1b": dict(dim=2048, n_layers=25, n_heads=16, vocab_size=128256, max_seqlen=4096),
+}
+BATCH = {"7b": 2, "1b": 4}
+SEQ = 4096
+
+
+def flops_per_token(m: dict) -> float:
+    """6 * (params - vocab*dim) + 3.5 * 4 * L * S * D / 2 (apps/main/transformer.py:46-56)."""
+    d, L, V = m["dim"], m["n_layers"], m["vocab_size"]
+    hidden = int(2 * 4 * d / 3)
+    if m.get("ffn_dim_multiplier"):
+        hidden = int(m["ffn_dim_multiplier"] * hidden)
+    mo = m.get("multiple_of", 256)
+    hidden = mo * ((hidden + mo - 1) // mo)
+    per_layer = 4 * d * d + 3 * d * hidden + 2 * d
+    total = L * per_layer + 2 * V * d + d
+    return 6 * (total - V * d) + 3.5 * (4 * L * SEQ * d // 2)
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu)], stdout=subprocess.PIPE, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def timed(torch, dist, fn, steps: int, world: int) -> float:
+    """ms per step: barrier + synchronize, K steps between two CUDA events, max over ranks."""
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ms = torch.tensor([e0.elapsed_time(e1) / steps], device="cuda")
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return float(ms.item())
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="7b", choices=list(MODELS))
+    ap.add_argument("--ref-eager", action="store_true", help="reference arm without torch.compile")
+    a = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29517")
+    if world != a.gpus:
+        if a.gpus > 1 and world == 1:
+            # convenience: relaunch ourselves under torchrun
+            cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={a.gpus}",
+                   "--master-addr", "127.0.0.1", "--master-port", os.environ["MASTER_PORT"], __file__] + sys.argv[1:]
+            raise SystemExit(subprocess.call(cmd))
+        raise SystemExit(f"--gpus {a.gpus} but WORLD_SIZE={world}")
+
+    base = {"impl": a.impl, "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup}
+    if a.impl == "reference":
+        sys.path.insert(0, str(ROOT / "baseline"))
+        import reference_arm
+
+        why = reference_arm.available()
+        if why:
+            if rank == 0:
+                print(json.dumps({"impl": "reference", "unavailable": why}))
+            return
+
+    import torch
+    import torch.distributed as dist
+
+    if not torch.cuda.is_available():
+        if rank == 0:
+            print(json.dumps({**base, "unavailable": "no CUDA device"}))
+        return
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    mcfg = MODELS[a.model]
+    B = BATCH[a.model]
+    fpt = flops_per_token(mcfg)
+    dev = torch.device("cuda", local_rank)
+    gen = torch.Generator().manual_seed(1234 + rank)
+    n_host = 4  # distinct host batches, cycled
+    host = [torch.randint(0, mcfg["vocab_size"], (B, SEQ + 1), generator=gen).pin_memory() for _ in range(n_host)]
+
+    def views(t):  # [B, S+1] -> [B, S, 2] (the loader's n_views=2 layout)
+        return torch.stack((t[:, :-1], t[:, 1:]), dim=-1)
+
+    launches = None
+    extra = {}
+    try:
+        if a.impl == "ours":
+            from lingua_b200.api import Trainer
+            from lingua_b200.distributed import DistributedArgs
+            from lingua_b200.models.transformer import LMTransformerArgs
+            from lingua_b200.ops import _lib
+            from lingua_b200.optim import OptimArgs
+
+            tr = Trainer(LMTransformerArgs(**mcfg), DistributedArgs(dp_shard=world, fsdp_type="full_shard"),
+                         OptimArgs(lr=1e-3, warmup=2000, clip=1.0), total_steps=100000, device=dev)
+            dev_batches = [views(h).to(dev) for h in host]
+            host_batches = [views(h).contiguous().pin_memory() for h in host]
+
+            def dev_step(i):
+                tr.train_step_async(dev_batches[i % n_host])
+
+            def e2e_step(i):
+                return tr.train_step(host_batches[i % n_host])
+
+            h2d = host_batches[0].numel() * host_batches[0].element_size()
+            counter = _lib.launch_count
+        else:
+            step_fn = None
+            errs = []
+            for compile_model, sac in ((not a.ref_eager, False), (not a.ref_eager, True), (False, True)):
+                try:
+                    step_fn, extra = reference_arm.build(mcfg, world, 1e-3, 100000, compile_model, sac)
+                    step_fn(host[0].to(dev))  # first step: compilation and allocator growth
+                    torch.cuda.synchronize()
+                    break
+                except torch.OutOfMemoryError as e:
+                    errs.append(f"compile={compile_model},sac={sac}: OOM")
+                    step_fn = None
+                    import gc
+                    gc.collect()
+                    torch.cuda.empty_cache()
+                except Exception as e:  # e.g. the compiler failing offline
+                    errs.append(f"compile={compile_model},sac={sac}: {type(e).__name__}: {str(e)[:120]}")
+                    step_fn = None
+                    import gc
+                    gc.collect()
+                    torch.cuda.empty_cache()
+            ok = torch.tensor([1 if step_fn is not None else 0], device=dev)
+            if world > 1:
+                dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if int(ok.item()) == 0:
+                if rank == 0:
+                    print(json.dumps({"impl": "reference", "n_gpus": a.gpus, "unavailable": "; ".join(errs)[:400]}))
+                return
+            extra["fallbacks"] = errs
+            dev_batches = [h.to(dev) for h in host]
+
+            def dev_step(i):
+                step_fn(dev_batches[i % n_host])
+
+            def e2e_step(i):
+                return float(step_fn(host[i % n_host].to(dev, non_blocking=True)).item())
+
+            h2d = host[0].numel() * host[0].element_size()
+            counter = None
+
+        for i in range(a.warmup):
+            dev_step(i)
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        c0 = counter() if counter else 0
+        ms = timed(torch, dist, dev_step, a.steps, world)
+        c1 = counter() if counter else 0
+        e2e_step(0)
+        ms_e2e = timed(torch, dist, e2e_step, a.steps, world)
+        clocks = sampler.stop() if rank == 0 else {}
+        if counter:
+            launches = c1 - c0
+    except torch.OutOfMemoryError as e:
+        if rank == 0:
+            print(json.dumps({**base, "unavailable": f"out of memory: {str(e)[:200]}"}))
+        return
+
+    tokens = B * SEQ * world
+    value = tokens / ms * 1e3
+    e2e_value = tokens / ms_e2e * 1e3
+    peaks = {}
+    try:
+        peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+    except Exception:
+        pass
+    peak_tf = peaks.get("bf16_tflops_sustained") or 1400.0
+    out = {
+        "metric": "training tokens/s (wps summed over GPUs), Llama-7B FSDP bf16" if a.model == "7b"
+        else "training tokens/s (wps summed over GPUs), Llama-1B FSDP bf16",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup,
+        "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic uniform-random token ids, random-init weights",
+        "impl": a.impl,
+        "config": {"model": f"llama_{a.model}", "global_batch": B * world, "seq_len": SEQ,
+                   "parallelism": f"fsdp{world}", "tokens_per_gpu_per_step": B * SEQ,
+                   "l2": "working set (>= 15 GB of weights re-read every step) exceeds the 126 MB L2; no explicit flush",
+                   "optimizer": "AdamW fp32 states, clip 1.0, inside the timed region", **extra},
+        "wps_per_gpu": round(value / world, 1),
+        "mfu_of_measured_sustained_peak": round(value / world * fpt / (peak_tf * 1e12), 4),
+        "tflops_per_gpu": round(value / world * fpt / 1e12, 1),
+        "clocks": clocks,
+        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "ms_per_step": round(ms_e2e, 3),
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
+        "gpu_launches": launches,
+    }
+    if rank == 0:
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
