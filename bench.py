@@ -165,7 +165,11 @@ def main() -> None:
             print(json.dumps({**base, "unavailable": "no CUDA device"}))
         return
     torch.cuda.set_device(local_rank)
-    if world > 1:
+    if world > 1 or a.impl == "reference":
+        # the reference builds a DeviceMesh even on one GPU, which needs a process group
+        os.environ.setdefault("RANK", "0")
+        os.environ.setdefault("WORLD_SIZE", "1")
+        os.environ.setdefault("LOCAL_RANK", "0")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     mcfg = MODELS[a.model]
@@ -290,7 +294,7 @@ def main() -> None:
     }
     if rank == 0:
         print(json.dumps(out))
-    if world > 1:
+    if dist.is_initialized():
         dist.destroy_process_group()
 
 
