@@ -718,3 +718,37 @@ extern "C" int lb_attn_bwd(const LbAttnArgs* a, void* stream) {
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Attention backward for callers that must not allocate device memory (see lingua_b200.h).
+// The two scratch buffers of lb_attn_bwd live in one fixed array inside the library image.
+namespace lb {
+constexpr long long NOALLOC_MAX_ROWS = 65536;  // B * S * H
+constexpr int NOALLOC_MAX_DEVICES = 64;
+// [0, ROWS*128): dQ accumulator; [ROWS*128, ROWS*129): per-row delta. 33,816,576 bytes per GPU.
+static __device__ __align__(256) float g_attn_bwd_scratch[NOALLOC_MAX_ROWS * 129];
+// Device address of the array for each device that has been set up (the symbol itself is only a
+// host-side handle and must never be handed to a kernel).
+static float* g_attn_bwd_scratch_addr[NOALLOC_MAX_DEVICES] = {nullptr};
+}  // namespace lb
+
+extern "C" long long lb_attn_bwd_noalloc_max_rows(void) { return lb::NOALLOC_MAX_ROWS; }
+
+extern "C" int lb_attn_bwd_noalloc(const LbAttnArgs* a, void* stream) {
+  using namespace lb;
+  if (!a) return 1;
+  const long long rows = (long long)a->B * a->S * a->H;
+  if (a->B < 0 || a->S < 0 || a->H < 0 || rows > NOALLOC_MAX_ROWS) return 30;  // beyond the fixed scratch
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) return 31;
+  if (!g_attn_bwd_scratch_addr[dev]) {
+    // once per device, with that device current: resolve the array's address on this device
+    float* p = nullptr;
+    if (cudaGetSymbolAddress((void**)&p, g_attn_bwd_scratch) != cudaSuccess || !p) return 32;
+    g_attn_bwd_scratch_addr[dev] = p;
+  }
+  LbAttnArgs b = *a;
+  b.dq_acc = g_attn_bwd_scratch_addr[dev];
+  b.delta = g_attn_bwd_scratch_addr[dev] + NOALLOC_MAX_ROWS * 128;
+  return lb_attn_bwd(&b, stream);  // clears dq_acc with a memset on `stream`, then launches
+}

@@ -56,6 +56,25 @@ typedef struct LbAttnArgs {
 int lb_attn_fwd(const LbAttnArgs* a, void* stream);
 int lb_attn_bwd(const LbAttnArgs* a, void* stream);
 
+// lb_attn_bwd for hosts that cannot allocate device memory at call time -- for example a
+// serving or training process that has handed every byte of the GPU to its own arena, or a
+// latency-critical loop that cannot afford the device-wide synchronisation a cudaMalloc /
+// cudaFree implies. This entry point has no counterpart in the reference implementation.
+//
+// Same arguments and results as lb_attn_bwd, except that a->delta and a->dq_acc are ignored:
+// the scratch comes from a fixed array compiled into the library (about 32.3 MB, resident on
+// every GPU that loads the library until the process exits). It allocates nothing: no
+// cudaMalloc / cudaFree, no allocating library call. Limits and rules:
+//   * B * S * H must not exceed lb_attn_bwd_noalloc_max_rows() (65536); larger problems are
+//     rejected with return code 30 and nothing is launched.
+//   * The first call on each device looks up the array's device address (with that device
+//     current). Make that first call outside any stream capture.
+//   * All calls on one GPU share the array. Each call clears the part that must start at zero
+//     on its own stream, but two calls that overlap in time on the same GPU (different streams,
+//     threads or processes sharing the context) race on it: serialise them.
+int lb_attn_bwd_noalloc(const LbAttnArgs* a, void* stream);
+long long lb_attn_bwd_noalloc_max_rows(void);
+
 // Number of kernels launched by this library in this process so far.
 long long lb_launch_count(void);
 void lb_launch_count_add(long long n);

@@ -1,0 +1,74 @@
+"""The allocation-free attention-backward entry point, called through its exported C symbol.
+
+Some hosts of this library cannot allocate device memory when they call it: a process that
+has given the whole GPU to its own memory arena, or a loop that cannot tolerate the
+device-wide synchronisation of cudaMalloc / cudaFree. For them ``lb_attn_bwd_noalloc`` runs the
+same backward pass as ``lb_attn_bwd`` with its scratch taken from a fixed array inside the
+library. This test checks, twice in a row (the array keeps the previous call's contents), that
+it produces the gradients of the regular entry point, and that it refuses problems larger than
+its fixed scratch.
+
+The file name sorts last so that a run that stops at the first failure has already executed
+every other test; it also passes when run alone in a fresh process.
+"""
+import ctypes as C
+
+import pytest
+import torch
+
+from lingua_b200.ops import _lib
+from lingua_b200.ops import attention as A
+
+pytestmark = pytest.mark.gpu
+
+
+def _close(a, b, tol=3e-2):
+    a, b = a.float(), b.float()
+    err = (a - b).abs().max().item()
+    ref = b.abs().max().item() + 1e-6
+    assert err / ref < tol, f"rel {err / ref:.4g}"
+
+
+def _call_noalloc(fn, dout, q, k, v, o, lse, dq, dk, dv):
+    a = _lib.AttnArgs()
+    A._fill(a, q, k, v, True, None, None, 0, None)
+    a.o, a.lse, a.dout = o.data_ptr(), lse.data_ptr(), dout.data_ptr()
+    a.dq, a.dk, a.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+    # delta / dq_acc stay NULL: the entry point supplies its own scratch
+    return fn(C.byref(a), torch.cuda.current_stream().cuda_stream)
+
+
+def test_noalloc_matches_regular_entry_point_twice():
+    lib = C.CDLL(str(_lib.lib_path()))
+    fn = lib.lb_attn_bwd_noalloc
+    fn.argtypes = [C.POINTER(_lib.AttnArgs), C.c_void_p]
+    fn.restype = C.c_int
+    lib.lb_attn_bwd_noalloc_max_rows.restype = C.c_longlong
+    max_rows = lib.lb_attn_bwd_noalloc_max_rows()
+    assert max_rows == 65536
+
+    for call, (B, S, H, Hkv) in enumerate([(2, 512, 4, 2), (1, 384, 2, 2)]):
+        torch.manual_seed(call)
+        qkv = torch.randn(B, S, H + 2 * Hkv, 128, device="cuda", dtype=torch.bfloat16)
+        q, k, v = qkv[:, :, :H], qkv[:, :, H:H + Hkv], qkv[:, :, H + Hkv:]
+        o, lse = A.flash_fwd(q, k, v)
+        dout = torch.randn_like(o)
+        ref = torch.zeros_like(qkv)
+        A.flash_bwd(dout, q, k, v, o, lse, ref[:, :, :H], ref[:, :, H:H + Hkv], ref[:, :, H + Hkv:])
+        out = torch.zeros_like(qkv)
+        torch.cuda.synchronize()
+        before = torch.cuda.memory_allocated()
+        rc = _call_noalloc(fn, dout, q, k, v, o, lse, out[:, :, :H], out[:, :, H:H + Hkv], out[:, :, H + Hkv:])
+        torch.cuda.synchronize()
+        assert rc == 0, f"lb_attn_bwd_noalloc returned {rc}"
+        assert torch.cuda.memory_allocated() == before
+        _close(out, ref)
+
+    # one row more than the scratch can hold is refused and launches nothing
+    B, S, H = 1, 128, 513  # 65664 rows
+    q = torch.empty(B, S, H, 128, device="cuda", dtype=torch.bfloat16)
+    o = torch.empty_like(q)
+    lse = torch.empty(B, H, S, device="cuda")
+    assert B * S * H > max_rows
+    assert _call_noalloc(fn, o, q, q, q, o, lse, o, o, o) == 30
+    _lib.check_status()
