@@ -41,6 +41,8 @@ class Trainer:
         with torch.random.fork_rng(devices=[device] if device.type == "cuda" else []):
             torch.manual_seed(model_args.seed)
             self.engine.init_weights_fp32(self.model.init_weights)
+        # the loss of every micro-batch receives the gradient 1 / grad_acc_steps (see train_step_async)
+        self.model.loss_grad_scale = 1.0 / grad_acc_steps
         self.scheduler = LRScheduler(self.optim_args.lr, build_lr_fn(self.optim_args, total_steps))
         self.step = 0
         self.acc_step = 0

@@ -20,6 +20,7 @@
 namespace lb {
 
 constexpr int AT_THREADS = 192;
+constexpr int BWD_THREADS = 320;  // TMA warp, MMA warp, 8 softmax warps (two per TMEM lane quarter)
 constexpr int AT_TILE = 128 * 128 * 2;  // one 128 x 128 bf16 tile: two 16 KB halves of 64 columns
 constexpr int AT_HALF = 128 * 64 * 2;
 constexpr float LOG2E = 1.4426950408889634f;
@@ -207,22 +208,29 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       tc_fence_after();
       const uint32_t tS = tS0 + buf * 128 + lane_off;
       const bool need_mask = (p.causal && j == qb) || (kv0 < lo_last) || (kv0 + 128 > p.S);
+      // all 128 scores of this row in registers: one TMEM round trip, then the buffer is free
+      uint32_t sv[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, sv[c]);
+      tmem_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_empty(buf));
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t rr[32];
-        tmem_ld32(tS + c * 32, rr);
-        tmem_wait_ld();
-        if (need_mask) {
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
             const int kv = kv0 + c * 32 + e;
-            if (kv >= lo && kv <= hi) mx = fmaxf(mx, __uint_as_float(rr[e]));
+            if (kv < lo || kv > hi) sv[c][e] = 0xFF800000u;  // -inf
+            mx = fmaxf(mx, __uint_as_float(sv[c][e]));
           }
-        } else {
+      } else {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(rr[e]));
-        }
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(sv[c][e]));
       }
       mx *= sl2;
       const float m_new = fmaxf(m_used, mx);
@@ -251,32 +259,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         }
       }
       const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
-#pragma unroll 1
+#pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t rr[32], pk[16];
-        tmem_ld32(tS + c * 32, rr);
-        tmem_wait_ld();
+        uint32_t pk[16];
 #pragma unroll
         for (int e = 0; e < 32; e += 2) {
-          float p0 = exp2f(__uint_as_float(rr[e]) * sl2 - m_eff);
-          float p1 = exp2f(__uint_as_float(rr[e + 1]) * sl2 - m_eff);
-          if (need_mask) {
-            const int kv = kv0 + c * 32 + e;
-            if (kv < lo || kv > hi) p0 = 0.f;
-            if (kv + 1 < lo || kv + 1 > hi) p1 = 0.f;
-          }
+          // masked scores are -inf and give exactly 0
+          const float p0 = exp2f(__uint_as_float(sv[c][e]) * sl2 - m_eff);
+          const float p1 = exp2f(__uint_as_float(sv[c][e + 1]) * sl2 - m_eff);
           l += p0 + p1;
           pk[e >> 1] = pack_bf16(p0, p1);
         }
         st_tile_row32(sP, r, c, pk);
       }
-      tc_fence_before();
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(s_empty(buf));
-        mbar_arrive(p_full);
-      }
+      if (lane == 0) mbar_arrive(p_full);
     }
     if (ok && n > 0) ok = mbar_wait(o_done, (n - 1) & 1, &abort_flag, p.status, 0x1A);
     if (ok) {
@@ -376,7 +374,7 @@ __global__ void attn_dq_store_kernel(const float* __restrict__ acc, __nv_bfloat1
 
 constexpr int BWD_SMEM = 2 * AT_TILE /*K,V*/ + 4 * AT_TILE /*Q,dO x 2*/ + AT_TILE /*P|dS*/ + 1024 + 256;
 
-__global__ void __launch_bounds__(AT_THREADS, 1)
+__global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                 const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo,
                 const AttnParams p) {
@@ -393,7 +391,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   auto qd_full = [&](int s) { return bars + 8 + 8 * s; };
   auto qd_empty = [&](int s) { return bars + 24 + 8 * s; };
   const uint32_t s_full = bars + 40, p_full = bars + 48, dv_done = bars + 56, ds_full = bars + 64;
-  const uint32_t dq_full = bars + 72, dq_drained = bars + 80;
+  const uint32_t dq_full = bars + 72, dq_drained = bars + 80, dp_full = bars + 88, s_free = bars + 96;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nqb = (p.S + 127) / 128;
@@ -419,11 +417,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       mbar_init(qd_empty(s), 1);
     }
     mbar_init(s_full, 1);
-    mbar_init(p_full, 4);
+    mbar_init(p_full, 8);
     mbar_init(dv_done, 1);
-    mbar_init(ds_full, 4);
+    mbar_init(ds_full, 8);
     mbar_init(dq_full, 1);
-    mbar_init(dq_drained, 4);
+    mbar_init(dq_drained, 8);
+    mbar_init(dp_full, 1);
+    mbar_init(s_free, 8);
     fence_mbar_init();
     tma_prefetch_desc(&tq);
     tma_prefetch_desc(&tk);
@@ -461,18 +461,27 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     }
   } else if (warp == 1) {
     if (lane == 0) {
+      // Issue order per query block i (softmax warps work on i while the tensor cores already
+      // run what does not depend on them):
+      //   dV(i) | S(i+1) | dK(i), dQ(i) | dP(i+1)
+      // dQ(i) lands in the TMEM columns of dP, so dP(i+1) waits until dQ(i) has been read out,
+      // while S(i+1) only needs the softmax warps to have copied S(i) into registers.
       bool ok = mbar_wait(kv_full, 0, &abort_flag, p.status, 0x22);
+      if (ok && n > 0) {
+        ok = mbar_wait(qd_full(0), 0, &abort_flag, p.status, 0x23);
+        if (ok) {
+          tc_fence_after();
+#pragma unroll
+          for (int k = 0; k < 8; ++k) umma_f16(tS, desc_k(sQ(0), k), desc_k(sK, k), IDESC_KK, k != 0);
+          umma_commit(s_full);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) umma_f16(tdP, desc_k(sdO(0), k), desc_k(sV, k), IDESC_KK, k != 0);
+          umma_commit(dp_full);
+        }
+      }
       for (int it = 0; ok && it < n; ++it) {
-        const int s = it & 1;
-        ok = mbar_wait(qd_full(s), (it >> 1) & 1, &abort_flag, p.status, 0x23);
-        if (ok && it > 0) ok = mbar_wait(dq_drained, (it - 1) & 1, &abort_flag, p.status, 0x24);
-        if (!ok) break;
-        tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < 8; ++k) umma_f16(tS, desc_k(sQ(s), k), desc_k(sK, k), IDESC_KK, k != 0);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) umma_f16(tdP, desc_k(sdO(s), k), desc_k(sV, k), IDESC_KK, k != 0);
-        umma_commit(s_full);
+        const int s = it & 1, s1 = s ^ 1;
+        const bool more = it + 1 < n;
         ok = mbar_wait(p_full, it & 1, &abort_flag, p.status, 0x25);
         if (!ok) break;
         tc_fence_after();
@@ -480,35 +489,97 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma_f16(tdV, desc_mn(sP, k), desc_mn(sdO(s), k), IDESC_MM, (it | k) != 0);
         umma_commit(dv_done);
+        if (more) {
+          ok = mbar_wait(qd_full(s1), ((it + 1) >> 1) & 1, &abort_flag, p.status, 0x23) &&
+               mbar_wait(s_free, it & 1, &abort_flag, p.status, 0x24);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int k = 0; k < 8; ++k) umma_f16(tS, desc_k(sQ(s1), k), desc_k(sK, k), IDESC_KK, k != 0);
+          umma_commit(s_full);
+        }
         ok = mbar_wait(ds_full, it & 1, &abort_flag, p.status, 0x26);
         if (!ok) break;
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma_f16(tdK, desc_mn(sP, k), desc_mn(sQ(s), k), IDESC_MM, (it | k) != 0);
-        // dQ[q, d] = dS K, into the columns that held S
+        // dQ[q, d] = dS K, into the columns that held dP
 #pragma unroll
-        for (int k = 0; k < 8; ++k) umma_f16(tS, desc_k(sP, k), desc_mn(sK, k), IDESC_KM, k != 0);
+        for (int k = 0; k < 8; ++k) umma_f16(tdP, desc_k(sP, k), desc_mn(sK, k), IDESC_KM, k != 0);
         umma_commit(qd_empty(s));
         umma_commit(dq_full);
+        if (more) {
+          ok = mbar_wait(dq_drained, it & 1, &abort_flag, p.status, 0x2A);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int k = 0; k < 8; ++k) umma_f16(tdP, desc_k(sdO(s1), k), desc_k(sV, k), IDESC_KK, k != 0);
+          umma_commit(dp_full);
+        }
       }
     }
   } else {
+    // Two warps share each quarter of the TMEM lanes: both own the same 32 rows, `ch` selects which
+    // 64 of the 128 columns a thread handles. Two resident warps per scheduler hide each other's
+    // latencies, and no reduction along a row is needed in the backward pass.
     const int quarter = warp & 3;
+    const int ch = (warp - 2) >> 2;  // 0: columns [0,64), 1: columns [64,128)
     const int r = quarter * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t col_off = ch * 64;
     const float sl2 = p.scale * LOG2E;
     bool ok = true;
+    float* prev_dqrow = nullptr;  // where the dQ half-row of the previous iteration goes (null: out of range)
+
+    auto drain_dq = [&](int it_done, bool release) -> bool {
+      if (!mbar_wait(dq_full, it_done & 1, &abort_flag, p.status, 0x29)) return false;
+      tc_fence_after();
+      uint32_t qv[2][32];
+      tmem_ld32(tdP + lane_off + col_off, qv[0]);
+      tmem_ld32(tdP + lane_off + col_off + 32, qv[1]);
+      tmem_wait_ld();
+      if (release) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(dq_drained);
+      }
+      if (prev_dqrow) {
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc)
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            float4 v = make_float4(__uint_as_float(qv[cc][4 * g]), __uint_as_float(qv[cc][4 * g + 1]),
+                                   __uint_as_float(qv[cc][4 * g + 2]), __uint_as_float(qv[cc][4 * g + 3]));
+            atomicAdd(reinterpret_cast<float4*>(prev_dqrow + cc * 32 + g * 4), v);
+          }
+      }
+      return true;
+    };
+
+    // per-row statistics of the next iteration are fetched one iteration ahead
+    auto row_stats = [&](int it, float& lse2, float& dlt, int& lo) {
+      const int h = hk * group + it / nq;
+      const int q_idx = (i0 + it % nq) * 128 + r;
+      const bool row_ok = q_idx < p.S;
+      const long long stat_i = ((long long)b * p.H + h) * p.S + min(q_idx, p.S - 1);
+      lse2 = row_ok ? p.lse[stat_i] * LOG2E : INFINITY;
+      dlt = row_ok ? p.delta[stat_i] : 0.f;
+      lo = 0;
+      if (p.doc_start) lo = p.doc_start[(long long)b * p.S + min(q_idx, p.S - 1)];
+      if (p.window > 0) lo = max(lo, q_idx - p.window + 1);
+    };
+    float lse2_n = 0.f, dlt_n = 0.f;
+    int lo_n = 0;
+    if (n > 0) row_stats(0, lse2_n, dlt_n, lo_n);
+
     for (int it = 0; it < n; ++it) {
       const int h = hk * group + it / nq;
       const int ib = i0 + it % nq;
       const int q_idx = ib * 128 + r;
       const bool row_ok = q_idx < p.S;
-      const long long stat_i = ((long long)b * p.H + h) * p.S + min(q_idx, p.S - 1);
-      const float lse2 = row_ok ? p.lse[stat_i] * LOG2E : INFINITY;
-      const float dlt = row_ok ? p.delta[stat_i] : 0.f;
-      int lo = 0;
-      if (p.doc_start) lo = p.doc_start[(long long)b * p.S + min(q_idx, p.S - 1)];
-      if (p.window > 0) lo = max(lo, q_idx - p.window + 1);
+      const float lse2 = lse2_n, dlt = dlt_n;
+      const int lo = lo_n;
+      if (it + 1 < n) row_stats(it + 1, lse2_n, dlt_n, lo_n);
       const int hi = p.causal ? min(q_idx, p.S - 1) : p.S - 1;
       int lo_blk = 0;
       {
@@ -521,99 +592,95 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       ok = mbar_wait(s_full, it & 1, &abort_flag, p.status, 0x27);
       if (!ok) break;
       tc_fence_after();
-      // pass A: P = exp(S - lse) -> shared memory (bf16)
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t rr[32], pk[16];
-        tmem_ld32(tS + lane_off + c * 32, rr);
+      // P = exp(S - lse), packed to bf16 in registers; S's TMEM columns are released right away
+      uint32_t pkP[32];
+      {
+        uint32_t sv[2][32];
+        tmem_ld32(tS + lane_off + col_off, sv[0]);
+        tmem_ld32(tS + lane_off + col_off + 32, sv[1]);
         tmem_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(s_free);
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float p0 = exp2f(__uint_as_float(rr[e]) * sl2 - lse2);
-          float p1 = exp2f(__uint_as_float(rr[e + 1]) * sl2 - lse2);
-          if (need_mask) {
-            const int kv = kv0 + c * 32 + e;
-            if (!row_ok || kv < lo || kv > hi) p0 = 0.f;
-            if (!row_ok || kv + 1 < lo || kv + 1 > hi) p1 = 0.f;
+        for (int cc = 0; cc < 2; ++cc) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            float p0 = exp2f(__uint_as_float(sv[cc][e]) * sl2 - lse2);
+            float p1 = exp2f(__uint_as_float(sv[cc][e + 1]) * sl2 - lse2);
+            if (need_mask) {
+              const int kv = kv0 + col_off + cc * 32 + e;
+              if (!row_ok || kv < lo || kv > hi) p0 = 0.f;
+              if (!row_ok || kv + 1 < lo || kv + 1 > hi) p1 = 0.f;
+            }
+            pkP[cc * 16 + (e >> 1)] = pack_bf16(p0, p1);
           }
-          pk[e >> 1] = pack_bf16(p0, p1);
         }
-        st_tile_row32(sP, r, c, pk);
       }
+      // The shared P|dS tile is free once dK(i-1) and dQ(i-1) have completed; reading dQ(i-1) out
+      // here also lets the tensor cores start dP(i).
+      if (it > 0) {
+        ok = drain_dq(it - 1, true);
+        if (!ok) break;
+      }
+      prev_dqrow = row_ok ? p.dq_acc + (((long long)b * p.S + q_idx) * p.H + h) * 128 + col_off : nullptr;
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc)
+        st_tile_row32(sP, r, 2 * ch + cc, *reinterpret_cast<const uint32_t(*)[16]>(&pkP[cc * 16]));
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
 
-      ok = mbar_wait(dv_done, it & 1, &abort_flag, p.status, 0x28);
+      // dS = P * (dP - delta) * scale
+      ok = mbar_wait(dp_full, it & 1, &abort_flag, p.status, 0x2B);
       if (!ok) break;
       tc_fence_after();
-      // pass B: dS = P * (dP - delta) * scale -> the same shared-memory tile
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t rr[32], dd[32], pk[16];
-        tmem_ld32(tS + lane_off + c * 32, rr);
-        tmem_ld32(tdP + lane_off + c * 32, dd);
+      {
+        uint32_t dd[2][32];
+        tmem_ld32(tdP + lane_off + col_off, dd[0]);
+        tmem_ld32(tdP + lane_off + col_off + 32, dd[1]);
         tmem_wait_ld();
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float p0 = exp2f(__uint_as_float(rr[e]) * sl2 - lse2);
-          float p1 = exp2f(__uint_as_float(rr[e + 1]) * sl2 - lse2);
-          if (need_mask) {
-            const int kv = kv0 + c * 32 + e;
-            if (!row_ok || kv < lo || kv > hi) p0 = 0.f;
-            if (!row_ok || kv + 1 < lo || kv + 1 > hi) p1 = 0.f;
+        for (int cc = 0; cc < 2; ++cc) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 2) {
+            const uint32_t pp = pkP[cc * 16 + (e >> 1)];
+            const float p0 = __uint_as_float(pp << 16), p1 = __uint_as_float(pp & 0xFFFF0000u);
+            const float d0 = p0 * (__uint_as_float(dd[cc][e]) - dlt) * p.scale;
+            const float d1 = p1 * (__uint_as_float(dd[cc][e + 1]) - dlt) * p.scale;
+            pkP[cc * 16 + (e >> 1)] = pack_bf16(d0, d1);
           }
-          const float d0 = p0 * (__uint_as_float(dd[e]) - dlt) * p.scale;
-          const float d1 = p1 * (__uint_as_float(dd[e + 1]) - dlt) * p.scale;
-          pk[e >> 1] = pack_bf16(d0, d1);
         }
-        st_tile_row32(sP, r, c, pk);
       }
+      ok = mbar_wait(dv_done, it & 1, &abort_flag, p.status, 0x28);
+      if (!ok) break;
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc)
+        st_tile_row32(sP, r, 2 * ch + cc, *reinterpret_cast<const uint32_t(*)[16]>(&pkP[cc * 16]));
       tc_fence_before();
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(ds_full);
-
-      ok = mbar_wait(dq_full, it & 1, &abort_flag, p.status, 0x29);
-      if (!ok) break;
-      tc_fence_after();
-      float* dqrow = p.dq_acc + (((long long)b * p.S + q_idx) * p.H + h) * 128;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t rr[32];
-        tmem_ld32(tS + lane_off + c * 32, rr);
-        tmem_wait_ld();
-        if (row_ok) {
-#pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            float4 v = make_float4(__uint_as_float(rr[4 * g]), __uint_as_float(rr[4 * g + 1]),
-                                   __uint_as_float(rr[4 * g + 2]), __uint_as_float(rr[4 * g + 3]));
-            atomicAdd(reinterpret_cast<float4*>(dqrow + c * 32 + g * 4), v);
-          }
-        }
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(dq_drained);
     }
-    // epilogue: dK, dV rows of this key block (every MMA has completed: dq_full was the last commit)
+    if (ok && n > 0) ok = drain_dq(n - 1, false);
+    // epilogue: dK (warps with ch == 0) and dV (ch == 1) rows of this key block; every MMA has
+    // completed because the last dq_full was the last commit.
     if (ok) {
       tc_fence_after();
       const int kv_idx = kv0 + r;
-      __nv_bfloat16* dkrow = p.dk + b * p.k_sb + (long long)kv_idx * p.k_ss + hk * p.k_sh;
-      __nv_bfloat16* dvrow = p.dv + b * p.v_sb + (long long)kv_idx * p.v_ss + hk * p.v_sh;
+      __nv_bfloat16* drow = ch == 0 ? p.dk + b * p.k_sb + (long long)kv_idx * p.k_ss + hk * p.k_sh
+                                    : p.dv + b * p.v_sb + (long long)kv_idx * p.v_ss + hk * p.v_sh;
 #pragma unroll 1
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < 4; ++c) {
         uint32_t rr[32];
         if (n > 0) {
-          tmem_ld32((c < 4 ? tdK : tdV) + lane_off + (c & 3) * 32, rr);
+          tmem_ld32((ch == 0 ? tdK : tdV) + lane_off + c * 32, rr);
           tmem_wait_ld();
         } else {
 #pragma unroll
           for (int e = 0; e < 32; ++e) rr[e] = 0u;
         }
         if (kv_idx < p.S) {
-          __nv_bfloat16* dst = (c < 4 ? dkrow : dvrow) + (c & 3) * 32;
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             uint4 v;
@@ -621,7 +688,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
             v.y = pack_bf16(__uint_as_float(rr[g * 8 + 2]), __uint_as_float(rr[g * 8 + 3]));
             v.z = pack_bf16(__uint_as_float(rr[g * 8 + 4]), __uint_as_float(rr[g * 8 + 5]));
             v.w = pack_bf16(__uint_as_float(rr[g * 8 + 6]), __uint_as_float(rr[g * 8 + 7]));
-            *reinterpret_cast<uint4*>(dst + g * 8) = v;
+            *reinterpret_cast<uint4*>(drow + c * 32 + g * 8) = v;
           }
         }
       }
@@ -710,7 +777,7 @@ extern "C" int lb_attn_bwd(const LbAttnArgs* a, void* stream) {
     attr = true;
   }
   dim3 grid((a->S + 127) / 128, a->Hkv, a->B);
-  attn_bwd_kernel<<<grid, AT_THREADS, BWD_SMEM, st>>>(tq, tk, tv, tdo, p);
+  attn_bwd_kernel<<<grid, BWD_THREADS, BWD_SMEM, st>>>(tq, tk, tv, tdo, p);
   long long total = rows * 16;
   int blocks = (int)((total + 255) / 256 < (long long)num_sms() * 8 ? (total + 255) / 256 : (long long)num_sms() * 8);
   attn_dq_store_kernel<<<blocks, 256, 0, st>>>(a->dq_acc, (__nv_bfloat16*)a->dq, a->B, a->S, a->H, a->q_sb, a->q_ss, a->q_sh);

@@ -365,6 +365,11 @@ extern "C" int lb_gemm(const LbGemmArgs* args, void* stream) {
   // rows of C are written in 8-element vectors: a ragged N needs ldc >= N rounded up to 8
   if ((a.ldc % 8) || (a.lda % 8) || (a.ldb % 8) || a.ldc < ((a.N + 7) / 8) * 8) return 3;
   if (a.out_dtype == LB_BF16 && a.accumulate) return 4;
+  // Large problems run on SM pairs (256 x 256 tiles); force_bn = 512 selects that explicitly,
+  // 128 / 256 select the single-SM kernels.
+  const long long tiles2 = (long long)((a.M + 255) / 256) * ((a.N + 255) / 256) * a.nb0 * a.nb1;
+  if (a.force_bn == 512 || (a.force_bn == 0 && a.M >= 256 && a.N >= 256 && tiles2 >= num_sms() / 2))
+    return gemm2_dispatch(a, s);
   // Narrow outputs use the 128-wide tile so that small N does not waste half of every MMA.
   const bool narrow = a.N <= 128 || a.force_bn == 128;
   if (a.out_dtype == LB_BF16)

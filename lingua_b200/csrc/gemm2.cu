@@ -1,0 +1,343 @@
+// Two-SM variant of the tcgen05 GEMM: a cluster of two CTAs (one per SM) computes one 256 x 256
+// output tile with tcgen05.mma.cta_group::2. Each CTA TMA-loads its own 128 rows of A and its
+// own 128-row half of B (no multicast: every byte of shared memory is written by the CTA that
+// owns it), the leader CTA's MMA thread issues the paired MMA that reads both halves of B, and
+// each CTA drains the 128 x 256 accumulator held in its own TMEM. Halving the B traffic per
+// SM shrinks a stage to 32 KB, which buys a 6-deep TMA ring instead of 4.
+//
+// Same contract as gemm_kernel in gemm.cu (operand majors, alpha, fp32 accumulate, batching).
+#include "common.cuh"
+#include "lingua_b200.h"
+
+namespace lb {
+
+constexpr int G2_THREADS = 192;
+constexpr int G2_BM = 256, G2_BN = 256;   // per cluster
+constexpr int G2_ROWS = 128;              // A rows and B rows loaded by one CTA
+constexpr int G2_BK = 64;                 // bf16 elements per stage (128 bytes)
+constexpr int G2_A_BYTES = G2_ROWS * 128;
+constexpr int G2_STAGE_BYTES = 2 * G2_A_BYTES;
+constexpr int G2_STAGES = 6;
+constexpr int G2_SMEM = G2_STAGES * G2_STAGE_BYTES + 1024 + 256;
+
+struct Gemm2Params {
+  int M, N, K;
+  int tiles_m, tiles_n, nb0, nb1;
+  long long ldc, c_bs0, c_bs1;
+  float alpha;
+  int accumulate;
+  void* C;
+  uint32_t* status;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load issued by either CTA of the pair; the transaction bytes are counted on an mbarrier that
+// may live in the other CTA (cluster address).
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst_smem, const CUtensorMap* m, uint32_t bar_cluster,
+                                                 int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma2_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}\n"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrive on one mbarrier (cluster address, either CTA) when all MMAs issued so far have completed
+__device__ __forceinline__ void umma2_commit(uint32_t bar_cluster) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster)
+               : "memory");
+}
+
+template <int AMAJ, int BMAJ, typename OutT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
+gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+             const Gemm2Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ int abort_flag;
+  __shared__ uint32_t tmem_base_slot;
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_base + G2_STAGES * G2_STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (G2_STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * G2_STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * G2_STAGES + 2 + a); };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < G2_STAGES; ++s) {
+      mbar_init(full_bar(s), 1);   // the leader's producer arrives; bytes come from both CTAs
+      mbar_init(empty_bar(s), 1);  // one commit from the leader's MMA thread
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 8);  // 4 epilogue warps x 2 CTAs (used in the leader only)
+    }
+    fence_mbar_init();
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+  }
+  if (warp == 1) {
+    tmem_alloc2(smem_u32(&tmem_base_slot), 512);
+    tmem_relinquish2();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // barriers of both CTAs are initialised before any remote arrive / TMA
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  const int num_kb = (p.K + G2_BK - 1) / G2_BK;
+  const int tiles_per_batch = p.tiles_m * p.tiles_n;
+  const int num_tiles = tiles_per_batch * p.nb0 * p.nb1;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------------------------ TMA producer (both CTAs)
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = pair; ok && tile < num_tiles; tile += n_pairs) {
+        const int batch = tile / tiles_per_batch;
+        const int t = tile - batch * tiles_per_batch;
+        const int m0 = (t % p.tiles_m) * G2_BM + rank * G2_ROWS;
+        const int n0 = (t / p.tiles_m) * G2_BN + rank * G2_ROWS;
+        const int b0 = batch % p.nb0, b1 = batch / p.nb0;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % G2_STAGES;
+          const uint32_t ph = (it / G2_STAGES) & 1u;
+          ok = mbar_wait(empty_bar(s), ph ^ 1u, &abort_flag, p.status, 0x31);
+          if (!ok) break;
+          if (leader) mbar_arrive_expect_tx(full_bar(s), 2 * G2_STAGE_BYTES);
+          const uint32_t lead_full = mapa(full_bar(s), 0);
+          const uint32_t sa = smem_base + s * G2_STAGE_BYTES;
+          const uint32_t sb = sa + G2_A_BYTES;
+          const int k0 = kb * G2_BK;
+          if (AMAJ == 0) {
+            tma_load_4d_pair(sa, &tma_a, lead_full, k0, m0, b0, b1);
+          } else {
+#pragma unroll
+            for (int c = 0; c < 2; ++c)
+              tma_load_4d_pair(sa + c * (G2_BK * 128), &tma_a, lead_full, m0 + c * 64, k0, b0, b1);
+          }
+          if (BMAJ == 0) {
+            tma_load_4d_pair(sb, &tma_b, lead_full, k0, n0, b0, b1);
+          } else {
+#pragma unroll
+            for (int c = 0; c < 2; ++c)
+              tma_load_4d_pair(sb + c * (G2_BK * 128), &tma_b, lead_full, n0 + c * 64, k0, b0, b1);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && leader) {
+      // ------------------------------------------------ MMA issuer (leader CTA only)
+      constexpr uint32_t idesc = make_idesc(G2_BM, G2_BN, 1, 1, AMAJ, BMAJ);
+      constexpr uint32_t SBO = 1024, LBO_MN = G2_BK * 128;
+      constexpr uint32_t A_KSTEP = (AMAJ == 0) ? 32u : 16u * 128u;
+      constexpr uint32_t B_KSTEP = (BMAJ == 0) ? 32u : 16u * 128u;
+      uint32_t it = 0, tile_iter = 0;
+      bool ok = true;
+      for (int tile = pair; ok && tile < num_tiles; tile += n_pairs, ++tile_iter) {
+        const int acc = tile_iter & 1;
+        const uint32_t acc_ph = (tile_iter >> 1) & 1u;
+        ok = mbar_wait(tempty_bar(acc), acc_ph ^ 1u, &abort_flag, p.status, 0x32);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * G2_BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % G2_STAGES;
+          const uint32_t ph = (it / G2_STAGES) & 1u;
+          ok = mbar_wait(full_bar(s), ph, &abort_flag, p.status, 0x33);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t sa = smem_base + s * G2_STAGE_BYTES;
+          const uint32_t sb = sa + G2_A_BYTES;
+#pragma unroll
+          for (int k = 0; k < G2_BK / 16; ++k) {
+            const uint64_t ad = make_smem_desc(sa + k * A_KSTEP, AMAJ ? LBO_MN : 16u, SBO);
+            const uint64_t bd = make_smem_desc(sb + k * B_KSTEP, BMAJ ? LBO_MN : 16u, SBO);
+            umma2_f16(tmem_d, ad, bd, idesc, (kb | k) != 0);
+          }
+          umma2_commit(mapa(empty_bar(s), 0));
+          umma2_commit(mapa(empty_bar(s), 1));
+        }
+        if (!ok) break;
+        umma2_commit(mapa(tfull_bar(acc), 0));
+        umma2_commit(mapa(tfull_bar(acc), 1));
+      }
+    }
+  } else {
+    // -------------------------------------------------- epilogue (warps 2..5, both CTAs)
+    const int quarter = warp & 3;
+    uint32_t tile_iter = 0;
+    for (int tile = pair; tile < num_tiles; tile += n_pairs, ++tile_iter) {
+      const int acc = tile_iter & 1;
+      const uint32_t acc_ph = (tile_iter >> 1) & 1u;
+      const int batch = tile / tiles_per_batch;
+      const int t = tile - batch * tiles_per_batch;
+      const int m0 = (t % p.tiles_m) * G2_BM + rank * G2_ROWS;
+      const int n0 = (t / p.tiles_m) * G2_BN;
+      const int b0 = batch % p.nb0, b1 = batch / p.nb0;
+      if (!mbar_wait(tfull_bar(acc), acc_ph, &abort_flag, p.status, 0x34)) break;
+      tc_fence_after();
+      const int row = m0 + quarter * 32 + lane;
+      OutT* crow = reinterpret_cast<OutT*>(p.C) + b0 * p.c_bs0 + b1 * p.c_bs1 + static_cast<long long>(row) * p.ldc;
+      const uint32_t taddr = tmem_base + acc * G2_BN + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < G2_BN / 32; ++c) {
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.N) break;
+        uint32_t r[32];
+        tmem_ld32(taddr + c * 32, r);
+        tmem_wait_ld();
+        if (row < p.M) {
+          if (sizeof(OutT) == 2) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              if (col0 + g * 8 < p.N) {
+                uint4 v;
+                v.x = pack_bf16(__uint_as_float(r[g * 8 + 0]) * p.alpha, __uint_as_float(r[g * 8 + 1]) * p.alpha);
+                v.y = pack_bf16(__uint_as_float(r[g * 8 + 2]) * p.alpha, __uint_as_float(r[g * 8 + 3]) * p.alpha);
+                v.z = pack_bf16(__uint_as_float(r[g * 8 + 4]) * p.alpha, __uint_as_float(r[g * 8 + 5]) * p.alpha);
+                v.w = pack_bf16(__uint_as_float(r[g * 8 + 6]) * p.alpha, __uint_as_float(r[g * 8 + 7]) * p.alpha);
+                *reinterpret_cast<uint4*>(crow + col0 + g * 8) = v;
+              }
+            }
+          } else {
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              if (col0 + g * 4 < p.N) {
+                float4* dst = reinterpret_cast<float4*>(crow + col0 + g * 4);
+                float4 v;
+                v.x = __uint_as_float(r[g * 4 + 0]) * p.alpha;
+                v.y = __uint_as_float(r[g * 4 + 1]) * p.alpha;
+                v.z = __uint_as_float(r[g * 4 + 2]) * p.alpha;
+                v.w = __uint_as_float(r[g * 4 + 3]) * p.alpha;
+                if (p.accumulate) {
+                  const float4 o = *dst;
+                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                }
+                *dst = v;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa(tempty_bar(acc), 0));
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  // Neither CTA may leave (or free tensor memory) while its partner can still signal its barriers
+  // or while paired MMAs may still be writing into its TMEM.
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc2(tmem_base, 512);
+  }
+}
+
+template <int AMAJ, int BMAJ, typename OutT>
+static int launch_gemm2(const LbGemmArgs& a, cudaStream_t stream) {
+  CUtensorMap ta, tb;
+  int rc;
+  if (AMAJ == 0)
+    rc = make_tmap_4d(&ta, a.A, 2, a.K, a.M, a.lda, a.nb0, a.a_bs0, a.nb1, a.a_bs1, G2_BK, G2_ROWS);
+  else
+    rc = make_tmap_4d(&ta, a.A, 2, a.M, a.K, a.lda, a.nb0, a.a_bs0, a.nb1, a.a_bs1, 64, G2_BK);
+  if (rc) return 100 + rc;
+  if (BMAJ == 0)
+    rc = make_tmap_4d(&tb, a.B, 2, a.K, a.N, a.ldb, a.nb0, a.b_bs0, a.nb1, a.b_bs1, G2_BK, G2_ROWS);
+  else
+    rc = make_tmap_4d(&tb, a.B, 2, a.N, a.K, a.ldb, a.nb0, a.b_bs0, a.nb1, a.b_bs1, 64, G2_BK);
+  if (rc) return 200 + rc;
+  Gemm2Params p;
+  p.M = a.M; p.N = a.N; p.K = a.K;
+  p.tiles_m = (a.M + G2_BM - 1) / G2_BM;
+  p.tiles_n = (a.N + G2_BN - 1) / G2_BN;
+  p.nb0 = a.nb0; p.nb1 = a.nb1;
+  p.ldc = a.ldc; p.c_bs0 = a.c_bs0; p.c_bs1 = a.c_bs1;
+  p.alpha = a.alpha; p.accumulate = a.accumulate;
+  p.C = a.C; p.status = a.status;
+  const long long tiles = (long long)p.tiles_m * p.tiles_n * a.nb0 * a.nb1;
+  const int max_pairs = num_sms() / 2;
+  const int pairs = (int)(tiles < max_pairs ? tiles : max_pairs);
+  auto kern = gemm2_kernel<AMAJ, BMAJ, OutT>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM);
+    if (e != cudaSuccess) return 300 + (int)e;
+    attr_set = true;
+  }
+  kern<<<2 * pairs, G2_THREADS, G2_SMEM, stream>>>(ta, tb, p);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}
+
+template <typename OutT>
+static int dispatch2(const LbGemmArgs& a, cudaStream_t s) {
+  if (a.a_major == 0 && a.b_major == 0) return launch_gemm2<0, 0, OutT>(a, s);
+  if (a.a_major == 0 && a.b_major == 1) return launch_gemm2<0, 1, OutT>(a, s);
+  if (a.a_major == 1 && a.b_major == 0) return launch_gemm2<1, 0, OutT>(a, s);
+  return launch_gemm2<1, 1, OutT>(a, s);
+}
+
+int gemm2_dispatch(const LbGemmArgs& a, cudaStream_t s) {
+  if (a.out_dtype == LB_BF16) return dispatch2<__nv_bfloat16>(a, s);
+  if (a.out_dtype == LB_F32) return dispatch2<float>(a, s);
+  return 5;
+}
+
+}  // namespace lb

@@ -82,12 +82,16 @@ void lb_launch_count_add(long long n);
 #ifdef __cplusplus
 }
 #include <cuda.h>
+#include <cuda_runtime.h>
 namespace lb {
 extern std::atomic<long long> g_launches;
 int num_sms();
+struct LbGemmArgsFwd;
 // 4-D TMA map {inner, outer, batch0, batch1} with the 128-byte swizzle; strides in elements.
 int make_tmap_4d(CUtensorMap* out, const void* base, int esz, long long inner, long long outer,
                  long long ld, int nb0, long long bs0, int nb1, long long bs1, int box_inner,
                  int box_outer);
+// two-SM (cta_group::2) 256 x 256-tile variant, gemm2.cu
+int gemm2_dispatch(const LbGemmArgs& a, cudaStream_t s);
 }
 #endif

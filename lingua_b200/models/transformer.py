@@ -357,7 +357,9 @@ class LMTransformer(BaseTransformer):
         w_out = self.output.weight
         if target is not None:
             y, _ = _final_norm(x, pending, self.norm)
-            return fused.LinearCrossEntropyFn.apply(y, w_out, target.reshape(-1), self.loss_chunk)
+            # set by the training engine: the constant gradient that will reach the loss
+            gs = getattr(self, "loss_grad_scale", None) if torch.is_grad_enabled() else None
+            return fused.LinearCrossEntropyFn.apply(y, w_out, target.reshape(-1), self.loss_chunk, gs)
         y, _ = _final_norm(x, pending, self.norm)
         return fused.LinearFn.apply(y, w_out).view(B, S, -1)
 

@@ -239,33 +239,69 @@ class EmbeddingFn(torch.autograd.Function):
 
 class LinearCrossEntropyFn(torch.autograd.Function):
     """mean_i CE(y_i W^T, target_i) over rows with target >= 0, without ever holding more than
-    ``chunk`` rows of logits. Forward keeps the per-row log-sum-exp; backward recomputes each
-    logits chunk, turns it into its gradient in one pass and feeds the two gradient GEMMs
-    (the loss of lingua/transformer.py:51-56 applied to apps/main/transformer.py:115-117)."""
+    ``chunk`` rows of logits (the loss of lingua/transformer.py:51-56 applied to
+    apps/main/transformer.py:115-117).
+
+    ``grad_scale=None``: forward keeps the per-row log-sum-exp; backward recomputes each logits
+    chunk, turns it into its gradient in one pass and feeds the two gradient GEMMs. Exact for any
+    incoming gradient, at the price of one extra vocabulary GEMM.
+
+    ``grad_scale=s`` (what the training engine uses): the caller promises that the gradient that
+    will flow into the returned loss is the constant ``s`` (1 / grad_acc_steps). The gradient of
+    every chunk is then produced in forward right after its loss, so the logits are computed once;
+    backward only hands out the stored input gradient."""
 
     @staticmethod
-    def forward(ctx, y, w, target, chunk):
+    def forward(ctx, y, w, target, chunk, grad_scale=None):
         M = y.shape[0]
         wd = w.detach()
         tgt = target.reshape(-1)
-        lse = torch.empty(M, dtype=torch.float32, device=y.device)
         total = torch.zeros((), dtype=torch.float32, device=y.device)
+        n_valid = (tgt >= 0).sum().clamp(min=1).float()
+        fused_bwd = grad_scale is not None and (ctx.needs_input_grad[0] or w.requires_grad)
+        ctx.fused_bwd, ctx.w, ctx.chunk, ctx.grad_scale = fused_bwd, w, chunk, grad_scale
+        if not fused_bwd:
+            lse = torch.empty(M, dtype=torch.float32, device=y.device)
+            for r0 in range(0, M, chunk):
+                r1 = min(M, r0 + chunk)
+                logits = gemm(y[r0:r1], wd, out_dtype=torch.float32)
+                loss_c, lse_c = F.ce_fwd(logits, tgt[r0:r1])
+                lse[r0:r1] = lse_c
+                total += loss_c.sum()
+                del logits
+            ctx.save_for_backward(y, tgt, lse, n_valid)
+            return total / n_valid
+        gscale = (float(grad_scale) / n_valid).reshape(1).contiguous()
+        dy = torch.empty_like(y)
+        has_mg = hasattr(w, "main_grad")
+        dw_acc = None
         for r0 in range(0, M, chunk):
             r1 = min(M, r0 + chunk)
             logits = gemm(y[r0:r1], wd, out_dtype=torch.float32)
             loss_c, lse_c = F.ce_fwd(logits, tgt[r0:r1])
-            lse[r0:r1] = lse_c
             total += loss_c.sum()
+            dl = F.ce_bwd(logits, tgt[r0:r1], lse_c, 1.0, gscale)
             del logits
-        n_valid = (tgt >= 0).sum().clamp(min=1).float()
-        ctx.save_for_backward(y, tgt, lse, n_valid)
-        ctx.w, ctx.chunk = w, chunk
+            mm_nn(dl, wd, out=dy[r0:r1])
+            if w.requires_grad:
+                if has_mg:
+                    mm_tn(dl, y[r0:r1], out=w.main_grad, accumulate=getattr(w, "grad_written", False))
+                    w.grad_written = True
+                else:
+                    if dw_acc is None:
+                        dw_acc = torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+                    mm_tn(dl, y[r0:r1], out=dw_acc, accumulate=True)
+            del dl
+        ctx.save_for_backward(dy, dw_acc)
         return total / n_valid
 
     @staticmethod
     def backward(ctx, g):
-        y, tgt, lse, n_valid = ctx.saved_tensors
         w, chunk = ctx.w, ctx.chunk
+        if ctx.fused_bwd:
+            dy, dw_acc = ctx.saved_tensors
+            return dy, (None if dw_acc is None else dw_acc.to(w.dtype)), None, None, None
+        y, tgt, lse, n_valid = ctx.saved_tensors
         wd = w.detach()
         M = y.shape[0]
         gscale = (g.float() / n_valid).reshape(1).contiguous()
@@ -288,4 +324,4 @@ class LinearCrossEntropyFn(torch.autograd.Function):
                     mm_tn(dl, y[r0:r1], out=dw_acc, accumulate=True)
             del dl
         dw = None if (has_mg or dw_acc is None) else dw_acc.to(w.dtype)
-        return dy, dw, None, None
+        return dy, dw, None, None, None

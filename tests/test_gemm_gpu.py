@@ -71,3 +71,28 @@ def test_linear_three_gemms():
     _check(G.mm_nt(x, w), x.float() @ w.float().t(), K)
     _check(G.mm_nn(dy, w), dy.float() @ w.float(), N)
     _check(G.mm_tn(dy, x, out_dtype=torch.float32), dy.float().t() @ x.float(), M)
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 768, 512), (300, 264, 200), (2048, 4096, 1024), (130, 72, 1032)])
+@pytest.mark.parametrize("a_t,b_t", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_two_sm_variant(M, N, K, a_t, b_t, out_dtype):
+    torch.manual_seed(0)
+    dev = "cuda"
+    if (a_t and M % 8) or (b_t and N % 8):
+        pytest.skip("TMA stride alignment")
+    a = torch.randn(K, M, device=dev, dtype=torch.bfloat16).t() if a_t else torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+    b = torch.randn(K, N, device=dev, dtype=torch.bfloat16).t() if b_t else torch.randn(N, K, device=dev, dtype=torch.bfloat16)
+    out = G.gemm(a, b, out_dtype=out_dtype, force_bn=512)
+    torch.cuda.synchronize()
+    _check(out, _ref(a, b), K)
+
+
+def test_gemm_two_sm_batched_accumulate():
+    torch.manual_seed(5)
+    a = torch.randn(3, 384, 320, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(3, 512, 320, device="cuda", dtype=torch.bfloat16)
+    c0 = torch.randn(3, 384, 512, device="cuda", dtype=torch.float32)
+    c = c0.clone()
+    G.gemm(a, b, out=c, accumulate=True, alpha=2.0, force_bn=512)
+    _check(c, c0 + _ref(a, b, 2.0), 320)

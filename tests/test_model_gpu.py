@@ -65,3 +65,20 @@ def test_native_training_reduces_loss():
         eng.step(1e-3)
         losses.append(loss.item())
     assert losses[-1] < losses[0] - 0.5, losses
+
+
+def test_fused_loss_backward_equals_recompute_mode():
+    args = LMTransformerArgs(dim=256, n_layers=1, n_heads=2, vocab_size=1000, max_seqlen=128, loss_chunk=100)
+    _, nat, eng = _build(args, seed=2)
+    tok = torch.randint(0, 1000, (2, 129), device="cuda")
+    x, y = tok[:, :-1].contiguous(), tok[:, 1:].contiguous()
+    grads = []
+    for scale in (None, 0.5):
+        eng.zero_grad()
+        nat.loss_grad_scale = scale
+        loss = nat(x, y)
+        (loss * 0.5).backward()
+        grads.append({n: p.main_grad.clone() for n, p in nat.named_parameters()})
+    for n in grads[0]:
+        a, b = grads[0][n], grads[1][n]
+        assert (a - b).abs().max().item() <= 2e-2 * (a.abs().max().item() + 1e-8), n
