@@ -35,8 +35,9 @@ class Trainer:
         with torch.device("meta"):
             model = model_cls(model_args)
         plan = grouping_plan if grouping_plan is not None else build_fsdp_grouping_plan(model_args)
+        from .parallel.tensor_parallel import tp_parallelize as tp_plan
         self.model, self.engine = parallelize_model(model, self.mesh, model_args, self.dist_args,
-                                                    fsdp_grouping_plan=plan,
+                                                    fsdp_grouping_plan=plan, tp_parallelize=tp_plan,
                                                     optim=build_engine_optim(self.optim_args), device=device)
         with torch.random.fork_rng(devices=[device] if device.type == "cuda" else []):
             torch.manual_seed(model_args.seed)

@@ -1,0 +1,298 @@
+"""Sharded (torch.distributed.checkpoint) and consolidated checkpoints.
+
+On-disk layout and retention rules are those of lingua/checkpoint.py (constants :37-47,
+SaveEvery :51, CheckpointArgs :57, consolidate_checkpoints :69, load_from_checkpoint :90,
+CheckpointManager :104): ``checkpoints/{step:010d}/`` holds the DCP files of
+``{"model": {fqn: tensor}, "optim": {"state": {fqn: {step, exp_avg, exp_avg_sq}},
+"param_groups": [...]}}``, ``params.json`` (the full training config) and one
+``train_state_{dp_rank:05d}.json`` per data-parallel rank; ``consolidated/consolidated.pth`` is
+the single-file form used by generation and evaluation.
+
+The sharded engine keeps flat per-group slices that cut through parameters, so for the
+checkpoint every parameter (fp32 master weights and both Adam moments) is re-presented as a
+``DTensor`` sharded on dim 0 over the data-parallel group - the form FSDP2 checkpoints have -
+which also lets a checkpoint be loaded on a different number of GPUs.
+"""
+from __future__ import annotations
+
+import json
+import logging
+import os
+import re
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import Any, Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+import torch.distributed.checkpoint as dcp
+from torch.distributed.checkpoint.format_utils import dcp_to_torch_save
+
+from .config import dataclass_to_dict
+from .distributed import get_is_master
+
+logger = logging.getLogger("CHECKPOINT")
+
+FOLDER_NAME = "{:010d}"
+RE_FOLDER = r"\d{10}"
+RE_CKPT = r"__\d_\d\.distcp"
+CONSOLIDATE_FOLDER = "consolidated"
+CONSOLIDATE_NAME = "consolidated.pth"
+CONFIG_NAME = "params.json"
+TRAIN_STATE_NAME = "train_state_{:05d}.json"
+RE_DIGITS = re.compile(r"\d+")
+
+
+@dataclass
+class SaveEvery:
+    every: int = 1000
+    keep: int = 0
+
+
+@dataclass
+class CheckpointArgs:
+    dump: SaveEvery = field(default_factory=SaveEvery)
+    eval: SaveEvery = field(default_factory=SaveEvery)
+    path: Optional[str] = None
+    init_ckpt_path: Optional[str] = None
+    continue_training_from_init: bool = False
+
+
+def _get_key_step(name: str) -> int:
+    return int(re.findall(RE_DIGITS, name)[-1])
+
+
+def _barrier() -> None:
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        dist.barrier()
+
+
+def consolidate_checkpoints(ckpt_dir: str) -> Path:
+    """Merge a sharded checkpoint into ``<ckpt_dir>/consolidated/consolidated.pth`` (+ params.json)."""
+    out = Path(ckpt_dir) / CONSOLIDATE_FOLDER
+    if not (out / CONSOLIDATE_NAME).exists():
+        out.mkdir(exist_ok=True)
+        logger.info(f"Consolidating to: {out}")
+        dcp_to_torch_save(ckpt_dir, str(out / CONSOLIDATE_NAME))
+        (out / CONFIG_NAME).write_text((Path(ckpt_dir) / CONFIG_NAME).read_text())
+        logger.info("Consolidated !")
+    return out
+
+
+# ----------------------------------------------------------------------------- engine <-> state dict
+def _row_range(n_rows: int, world: int, rank: int) -> Tuple[int, int]:
+    per = (n_rows + world - 1) // world
+    return min(n_rows, rank * per), min(n_rows, (rank + 1) * per)
+
+
+def _device_mesh(engine):
+    from torch.distributed.device_mesh import DeviceMesh
+
+    if getattr(engine, "_dcp_mesh", None) is None:
+        engine._dcp_mesh = DeviceMesh.from_group(engine.pg if engine.pg not in (None, False) else dist.group.WORLD,
+                                                 engine.device.type, mesh_dim_names=("dp_shard",))
+    return engine._dcp_mesh
+
+
+def engine_state_dict(engine, lr: float = 0.0) -> Dict[str, Any]:
+    """``{"model": ..., "optim": ...}`` with the reference's keys; tensors are plain (one rank) or
+    dim-0 sharded DTensors holding this rank's rows."""
+    from torch.distributed.tensor import DTensor, Shard
+
+    W, R = engine.world, engine.rank
+    model_sd: Dict[str, Any] = {}
+    opt_state: Dict[str, Any] = {}
+    names: List[str] = []
+    step_t = torch.tensor(float(engine.step_count))
+    for gi, g in enumerate(engine.groups):
+        if W == 1:
+            bufs = {"p": g.master, "m": g.exp_avg, "v": g.exp_avg_sq}
+        else:
+            bufs = {}
+            for key, shard in (("p", g.master), ("m", g.exp_avg), ("v", g.exp_avg_sq)):
+                full = torch.empty(g.padded, dtype=torch.float32, device=engine.device)
+                dist.all_gather_into_tensor(full, shard, group=engine.pg)
+                bufs[key] = full
+        for fqn, p in g.params:
+            o, n = g.offsets[fqn]
+            names.append(fqn)
+            out = {}
+            for key in ("p", "m", "v"):
+                full = bufs[key][o:o + n].view(p.shape)
+                if W == 1:
+                    out[key] = full
+                else:
+                    r0, r1 = _row_range(p.shape[0], W, R)
+                    local = full[r0:r1].clone()
+                    out[key] = DTensor.from_local(local, _device_mesh(engine), [Shard(0)], run_check=False,
+                                                  shape=p.shape, stride=full.stride())
+            model_sd[fqn] = out["p"]
+            opt_state[fqn] = {"step": step_t.clone(), "exp_avg": out["m"], "exp_avg_sq": out["v"]}
+        del bufs
+    o = engine.optim
+    group = {"lr": lr, "betas": (o.beta1, o.beta2), "eps": o.eps, "weight_decay": o.weight_decay, "amsgrad": False,
+             "maximize": False, "foreach": None, "capturable": False, "differentiable": False, "fused": True,
+             "initial_lr": lr, "params": names}
+    return {"model": model_sd, "optim": {"state": opt_state, "param_groups": [group]}}
+
+
+def load_engine_state_dict(engine, sd: Dict[str, Any], load_optim: bool = True) -> None:
+    """Scatter a (loaded) state dict of the above form back into the engine's flat slices."""
+    from torch.distributed.tensor import DTensor
+
+    def full_of(t):
+        return (t.full_tensor() if isinstance(t, DTensor) else t).to(device=engine.device, dtype=torch.float32)
+
+    for g in engine.groups:
+        buf = torch.zeros(g.padded, dtype=torch.float32, device=engine.device)
+        for fqn, p in g.params:
+            o, n = g.offsets[fqn]
+            buf[o:o + n].copy_(full_of(sd["model"][fqn]).reshape(-1))
+        g.master.copy_(buf[g.shard_slice])
+        g.full.copy_(buf)
+        if load_optim and "optim" in sd:
+            for key, dst in (("exp_avg", g.exp_avg), ("exp_avg_sq", g.exp_avg_sq)):
+                buf.zero_()
+                for fqn, p in g.params:
+                    o, n = g.offsets[fqn]
+                    buf[o:o + n].copy_(full_of(sd["optim"]["state"][fqn][key]).reshape(-1))
+                dst.copy_(buf[g.shard_slice])
+        del buf
+    if load_optim and "optim" in sd:
+        steps = [float(v["step"]) for v in sd["optim"]["state"].values()]
+        if steps:
+            engine.step_count = int(max(steps))
+
+
+def load_from_checkpoint(ckpt_dir: str, engine, model_key: str = "model", load_optim: bool = False) -> None:
+    """Fill the engine (weights, optionally optimiser state) from a sharded checkpoint directory."""
+    if not (Path(ckpt_dir) / ".metadata").exists():
+        raise ValueError("Please convert the checkpoint to distcp format using "
+                         "`torch.distributed.checkpoint.format_utils.torch_save_to_dcp` before loading it")
+    sd = engine_state_dict(engine)
+    # model_key "" means the directory stores the parameters at top level (a bare model checkpoint)
+    to_load: Dict[str, Any] = {model_key: sd["model"]} if model_key else dict(sd["model"])
+    if load_optim:
+        to_load["optim"] = sd["optim"]
+    dcp.load(to_load, checkpoint_id=ckpt_dir)
+    load_engine_state_dict(engine, sd, load_optim=load_optim)
+
+
+# ----------------------------------------------------------------------------- manager
+class CheckpointManager:
+    def __init__(self, args: CheckpointArgs):
+        self.path = args.path
+        self.dump_every = args.dump
+        self.eval_every = args.eval
+        self.init_ckpt_path = args.init_ckpt_path
+        self.continue_training_from_init = args.continue_training_from_init
+        assert os.path.exists(self.path), (
+            f"Path {self.path} does not exist and needs to be created before using CheckpointManager "
+            f"(use instantiate_and_make_dir)")
+        self.existing_saves = self.get_existing_saves()
+
+    def get_existing_saves(self) -> List[Path]:
+        folders = [p for p in Path(self.path).iterdir() if p.is_dir() and re.match(RE_FOLDER, p.name)]
+        folders.sort(key=lambda p: _get_key_step(p.name))
+        return folders
+
+    def clean_up(self) -> None:
+        """Keep the last ``keep`` folders of each kind (all of them when keep <= 0); a folder that is
+        neither a dump nor an eval step (e.g. a preemption save) is always kept."""
+        logger.info("Cleaning up checkpoints...")
+        dumps, evals, others = [], [], []
+        for p in self.existing_saves:
+            step = _get_key_step(p.name)
+            is_dump = step % self.dump_every.every == 0
+            is_eval = step % self.eval_every.every == 0
+            if is_dump:
+                dumps.append(p)
+            if is_eval:
+                evals.append(p)
+            if not (is_dump or is_eval):
+                others.append(p)
+        if self.dump_every.keep > 0:
+            dumps = dumps[-self.dump_every.keep:]
+        if self.eval_every.keep > 0:
+            evals = evals[-self.eval_every.keep:]
+        keep = set(others + dumps + evals)
+        remove = set(self.existing_saves) - keep
+        logger.info(f"Removing folders: {remove}")
+        if get_is_master():
+            for folder in remove:
+                for f in folder.iterdir():
+                    if f.is_file():
+                        f.unlink()
+                    elif f.is_dir():
+                        assert f.name in [CONSOLIDATE_FOLDER]
+                        for ff in f.iterdir():
+                            ff.unlink()
+                        f.rmdir()
+                folder.rmdir()
+        _barrier()
+        self.existing_saves = sorted(keep, key=lambda p: _get_key_step(p.name))
+
+    def get_last_step_path(self, dp_rank: int = 0) -> Optional[Path]:
+        for p in reversed(self.existing_saves):
+            if (p / TRAIN_STATE_NAME.format(dp_rank)).is_file():
+                return p
+        return None
+
+    def _create_folder(self, base_path: Path, folder_name: str) -> Path:
+        folder = base_path / folder_name
+        if get_is_master():
+            folder.mkdir(parents=False, exist_ok=True)
+        _barrier()
+        return folder
+
+    @staticmethod
+    def _get_dp_tp_mesh(mesh=None) -> Tuple[int, int]:
+        if mesh is None:
+            return 0, 0
+        return mesh.local_rank("dp"), mesh.local_rank("tp")
+
+    @torch.no_grad()
+    def save(self, engine, train_state, config, mesh=None, lr: float = 0.0) -> bool:
+        path = Path(self.path)
+        cur = self._create_folder(path, FOLDER_NAME.format(train_state.step))
+        logger.info(f"Saving to: {cur}")
+        _barrier()
+        sd = engine_state_dict(engine, lr)
+        dcp.save(sd, checkpoint_id=cur)
+        del sd
+        logger.info("State dict saved!")
+        _barrier()
+        if get_is_master():
+            with open(cur / CONFIG_NAME, "w") as f:
+                json.dump(dataclass_to_dict(config), f)
+        dp_rank, tp_rank = self._get_dp_tp_mesh(mesh)
+        if tp_rank == 0:
+            name = TRAIN_STATE_NAME.format(dp_rank)
+            logger.info(f"Saving train state to: {cur / name}")
+            with open(cur / name, "w") as f:
+                json.dump(train_state.state_dict(), f)
+        self.existing_saves.append(cur)
+        self.clean_up()
+        _barrier()
+        return True
+
+    @torch.no_grad()
+    def load(self, engine, train_state, mesh=None, path: Optional[Path] = None) -> None:
+        dp_rank, _ = self._get_dp_tp_mesh(mesh)
+        path = path or self.get_last_step_path(dp_rank=dp_rank)
+        if path is None:
+            return
+        with open(Path(path) / TRAIN_STATE_NAME.format(dp_rank), "r") as f:
+            train_state.load_state_dict(json.load(f))
+        logger.info(f"Train state reloaded; loading from: {path}")
+        sd = engine_state_dict(engine)
+        dcp.load(sd, checkpoint_id=path)
+        load_engine_state_dict(engine, sd, load_optim=True)
+        logger.info("Model and optim reloaded")
+
+    @classmethod
+    def instantiate_and_make_dir(cls, args: CheckpointArgs):
+        if get_is_master():
+            os.makedirs(args.path, exist_ok=True)
+        _barrier()
+        return cls(args)

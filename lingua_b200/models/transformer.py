@@ -25,6 +25,7 @@ import torch.nn.functional as TF
 from ..ops import functional as F
 from ..ops import fused
 from ..ops.attention import attention_ref
+from ..parallel.tensor_parallel import ReduceBwd, ReduceFwd
 
 
 class InitStdFactor(Enum):
@@ -73,6 +74,24 @@ def _is_native(w: torch.Tensor) -> bool:
 def _trunc(w: torch.Tensor, std: float, bound_std: Optional[float] = None) -> None:
     b = 3 * (bound_std if bound_std is not None else std)
     nn.init.trunc_normal_(w, mean=0.0, std=std, a=-b, b=b)
+
+
+def _init_linear(mod: nn.Module, std: float, bound_std: Optional[float] = None) -> None:
+    """Truncated-normal init of ``mod.weight``. A tensor-parallel slice (``mod.tp_shard = (dim, tp,
+    rank)``) takes its part of a full-size draw, so that the assembled weight does not depend on
+    the TP degree and replicas of the random stream stay in step on every rank."""
+    shard = getattr(mod, "tp_shard", None)
+    w = mod.weight
+    if shard is None:
+        _trunc(w, std, bound_std)
+        return
+    dim, tp, rank = shard
+    shape = list(w.shape)
+    shape[dim] *= tp
+    full = torch.empty(shape, dtype=w.dtype, device=w.device)
+    _trunc(full, std, bound_std)
+    with torch.no_grad():
+        w.copy_(full.chunk(tp, dim=dim)[rank])
 
 
 class Linear(nn.Module):
@@ -127,7 +146,8 @@ class RotaryEmbedding(nn.Module):
         self.register_buffer("freqs_cis", F.rope_table(head_dim, max_seqlen, theta), persistent=False)
 
     def reset_parameters(self):
-        self.freqs_cis[...] = F.rope_table(self.head_dim, self.max_seqlen, self.theta, self.freqs_cis.device)
+        # always fp32, whatever dtype the module was cast to
+        self.freqs_cis = F.rope_table(self.head_dim, self.max_seqlen, self.theta, self.freqs_cis.device)
 
     def forward(self) -> torch.Tensor:
         return self.freqs_cis
@@ -151,6 +171,9 @@ class Attention(nn.Module):
     def forward_ref(self, x, cs, tok_idx=None, doc_start=None, window=0, causal=True):
         """x: [B, S, dim] already normalised."""
         B, S, _ = x.shape
+        tpg = getattr(self, "tp_group", None)
+        if tpg is not None:
+            x = ReduceBwd.apply(x, tpg)
         q = self.wq(x).view(B, S, self.n_heads, self.head_dim)
         k = self.wk(x).view(B, S, self.n_kv_heads, self.head_dim)
         v = self.wv(x).view(B, S, self.n_kv_heads, self.head_dim)
@@ -158,15 +181,17 @@ class Attention(nn.Module):
         q = F.rope_ref(q, cs, pos)
         k = F.rope_ref(k, cs, pos)
         if self.kv_cache is not None:
-            return self.wo(self.kv_cache.attend(q, k, v, tok_idx).reshape(B, S, -1))
+            out = self.wo(self.kv_cache.attend(q, k, v, tok_idx).reshape(B, S, -1))
+            return ReduceFwd.apply(out, tpg) if tpg is not None else out
         o = _attention_torch(q, k, v, causal, doc_start, window)
-        return self.wo(o.reshape(B, S, self.n_heads * self.head_dim))
+        out = self.wo(o.reshape(B, S, self.n_heads * self.head_dim))
+        return ReduceFwd.apply(out, tpg) if tpg is not None else out
 
     def reset_parameters(self, init_std=None, factor=1.0):
         std = init_std or (self.dim ** (-0.5))
         for w in (self.wq, self.wk, self.wv):
-            _trunc(w.weight, std)
-        _trunc(self.wo.weight, std / factor, std)
+            _init_linear(w, std)
+        _init_linear(self.wo, std / factor, std)
 
 
 def _attention_torch(q, k, v, causal, doc_start, window):
@@ -213,23 +238,34 @@ class FeedForward(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if _is_native(self.w1.weight):
             x2 = x.reshape(-1, self.dim)
+            if getattr(self, "tp_group", None) is not None:
+                x2 = ReduceBwd.apply(x2, self.tp_group)
             if self.activation == "swiglu":
                 gu = fused.LinearFn.apply(x2, *self.in_weights())
                 out = fused.GluLinearFn.apply(gu, self.w2.weight, F.ACT_SILU)
             else:
                 u = fused.LinearFn.apply(x2, self.w1.weight)
                 out = fused.ActLinearFn.apply(u, self.w2.weight, F.ACT_RELU2)
+            tpg = getattr(self, "tp_group", None)
+            if tpg is not None:
+                out = ReduceFwd.apply(out, tpg)
             return out.view(*x.shape[:-1], self.dim)
+        tpg = getattr(self, "tp_group", None)
+        if tpg is not None:
+            x = ReduceBwd.apply(x, tpg)
         if self.activation == "swiglu":
-            return self.w2(TF.silu(self.w1(x)) * self.w3(x))
-        return self.w2(torch.relu(self.w1(x)).pow(2))
+            out = self.w2(TF.silu(self.w1(x)) * self.w3(x))
+        else:
+            out = self.w2(torch.relu(self.w1(x)).pow(2))
+        return ReduceFwd.apply(out, tpg) if tpg is not None else out
 
     def reset_parameters(self, init_std=None, factor=1.0):
         in_std = init_std or (self.dim ** (-0.5))
         out_std = (init_std or (self.hidden_dim ** (-0.5))) / factor
-        for w in self.in_weights():
-            _trunc(w, in_std)
-        _trunc(self.w2.weight, out_std)
+        _init_linear(self.w1, in_std)
+        if self.activation == "swiglu":
+            _init_linear(self.w3, in_std)
+        _init_linear(self.w2, out_std)
 
 
 class TransformerBlock(nn.Module):
@@ -256,17 +292,28 @@ class TransformerBlock(nn.Module):
     # ---- native path: x, pending are [B*S, dim]; the residual stream is x + pending
     def forward_native(self, x, pending, cs, B, S, doc_start=None, doc_end=None, window=0, pos=None, causal=True):
         at, ff = self.attention, self.feed_forward
-        qkv, h = fused.NormLinearFn.apply(x, pending, self.attention_norm.weight, self.attention_norm.eps,
+        tpg = getattr(self, "tp_group", None)
+        qkv, h = fused.NormLinearFn.apply(x, pending, self.attention_norm.weight, self.attention_norm.eps, tpg,
                                           *at.qkv_weights())
         x = x if h is None else h
-        o = fused.RopeAttnFn.apply(qkv, cs, B, S, at.n_heads, at.n_kv_heads, at.head_dim, causal, doc_start,
-                                   doc_end, window, pos)
+        if at.kv_cache is not None:  # generation: rotate, then attend through the KV cache
+            F.rope_(qkv, cs, at.n_heads + at.n_kv_heads, at.head_dim, S, pos)
+            t = qkv.view(B * S, at.n_heads + 2 * at.n_kv_heads, at.head_dim)
+            o = at.kv_cache.native_attention(t[:, :at.n_heads], t[:, at.n_heads:at.n_heads + at.n_kv_heads],
+                                             t[:, at.n_heads + at.n_kv_heads:])
+        else:
+            o = fused.RopeAttnFn.apply(qkv, cs, B, S, at.n_heads, at.n_kv_heads, at.head_dim, causal, doc_start,
+                                       doc_end, window, pos, at.wo.weight)
         ao = fused.LinearFn.apply(o, at.wo.weight)
-        u, x2 = fused.NormLinearFn.apply(x, ao, self.ffn_norm.weight, self.ffn_norm.eps, *ff.in_weights())
+        if tpg is not None:
+            ao = ReduceFwd.apply(ao, tpg)
+        u, x2 = fused.NormLinearFn.apply(x, ao, self.ffn_norm.weight, self.ffn_norm.eps, tpg, *ff.in_weights())
         if ff.activation == "swiglu":
             out = fused.GluLinearFn.apply(u, ff.w2.weight, F.ACT_SILU)
         else:
             out = fused.ActLinearFn.apply(u, ff.w2.weight, F.ACT_RELU2)
+        if tpg is not None:
+            out = ReduceFwd.apply(out, tpg)
         return x2, out
 
     def init_weights(self, init_std=None, factor=1.0):
@@ -326,7 +373,7 @@ class LMTransformer(BaseTransformer):
         B, S = token_values.shape
         window = self.sliding_window or 0
         cs = self.rope_embeddings()
-        if _is_native(self.tok_embeddings.weight) and self.layers[0].attention.kv_cache is None:
+        if _is_native(self.tok_embeddings.weight):
             return self._forward_native(token_values, target, tok_idx, doc_start, doc_end, window, causal, cs, B, S)
         h = self.tok_embeddings(token_values)
         for layer in self.layers:

@@ -104,6 +104,7 @@ def _declare(lib) -> None:
         "lb_cast_f32_bf16": [fp, vp, ll, vp],
         "lb_attn_fwd": [C.POINTER(AttnArgs), vp],
         "lb_attn_bwd": [C.POINTER(AttnArgs), vp],
+        "lb_decode_attn": [vp, vp, vp, vp, vp, ip, ip, vp, i, i, i, i, ll, ll, f, vp],
     }
     for name, args in sigs.items():
         if hasattr(lib, name):

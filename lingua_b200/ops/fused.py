@@ -21,6 +21,16 @@ from .attention import flash_bwd, flash_fwd
 from .gemm import gemm, mm_nn, mm_nt, mm_tn
 
 
+# Statistics probe (lingua_b200.probe.AutoProbeD): when set, the functions below report their
+# operands to it. None on the normal path.
+_OBSERVER = None
+
+
+def set_observer(obs) -> None:
+    global _OBSERVER
+    _OBSERVER = obs
+
+
 # ----------------------------------------------------------------------------- helpers
 def fused_view(ws: Sequence[torch.Tensor]) -> Optional[torch.Tensor]:
     """[sum(N_i), K] view over row-blocks that are adjacent in memory, or None."""
@@ -94,7 +104,10 @@ class LinearFn(torch.autograd.Function):
     def forward(ctx, x, *ws):
         ctx.save_for_backward(x)
         ctx.ws = ws
-        return mm_nt(x, _weights(ws))
+        out = mm_nt(x, _weights(ws))
+        if _OBSERVER is not None:
+            _OBSERVER.linear_fwd(ws, x, out)
+        return out
 
     @staticmethod
     def backward(ctx, dy):
@@ -103,22 +116,28 @@ class LinearFn(torch.autograd.Function):
         dy = dy.contiguous()
         dx = mm_nn(dy, _weights(ws)) if ctx.needs_input_grad[0] else None
         dws = _emit_wgrad(ws, dy, x) if ws[0].requires_grad else [None] * len(ws)
+        if _OBSERVER is not None:
+            _OBSERVER.linear_bwd(ws, dy, dx, dws)
         return (dx, *dws)
 
 
 class NormLinearFn(torch.autograd.Function):
     """h = x (+ res); out = rmsnorm(h) * g @ [W_0; W_1; ...]^T. Returns (out, h); h is None
-    when no residual was given (the caller already holds x).
+    when no residual was given (the caller already holds x). ``tp_group``: the weights are
+    column-parallel slices, so the input gradient is summed over that group in backward.
 
     Saves h and the per-row rstd; the normalised activation is recomputed in backward."""
 
     @staticmethod
-    def forward(ctx, x, res, g, eps, *ws):
+    def forward(ctx, x, res, g, eps, tp_group, *ws):
         y, h, rstd = F.rmsnorm_fwd(x, g.detach(), eps, res)
         h = x if h is None else h
         out = mm_nt(y, _weights(ws))
+        if _OBSERVER is not None:
+            _OBSERVER.resid(g, h)
+            _OBSERVER.linear_fwd(ws, y, out)
         ctx.save_for_backward(h, rstd)
-        ctx.g, ctx.ws, ctx.eps, ctx.has_res = g, ws, eps, res is not None
+        ctx.g, ctx.ws, ctx.eps, ctx.has_res, ctx.tp_group = g, ws, eps, res is not None, tp_group
         return out, (h if res is not None else None)
 
     @staticmethod
@@ -130,6 +149,11 @@ class NormLinearFn(torch.autograd.Function):
         dws = _emit_wgrad(ws, dout, y) if ws[0].requires_grad else [None] * len(ws)
         del y
         dy = mm_nn(dout, _weights(ws))
+        if _OBSERVER is not None:
+            _OBSERVER.linear_bwd(ws, dout, dy, dws)
+        if ctx.tp_group is not None:
+            # column-parallel weights: every TP rank holds a partial sum of the input gradient
+            torch.distributed.all_reduce(dy, group=ctx.tp_group)
         dres_in = dh_out.contiguous() if dh_out is not None else None
         holder = {}
 
@@ -138,17 +162,19 @@ class NormLinearFn(torch.autograd.Function):
 
         dg = _emit_vec_grad(g, run)
         dx = holder["dx"]
-        return (dx, dx if ctx.has_res else None, dg, None, *dws)
+        return (dx, dx if ctx.has_res else None, dg, None, None, *dws)
 
 
 class RopeAttnFn(torch.autograd.Function):
     """qkv [B*S, (H + 2 Hkv) * Dh] -> RoPE on q and k (in place) -> attention -> [B*S, H * Dh]."""
 
     @staticmethod
-    def forward(ctx, qkv, cs, B, S, H, Hkv, Dh, causal, doc_start, doc_end, window, pos):
+    def forward(ctx, qkv, cs, B, S, H, Hkv, Dh, causal, doc_start, doc_end, window, pos, anchor=None):
         F.rope_(qkv, cs, H + Hkv, Dh, S, pos)
         t = qkv.view(B, S, H + 2 * Hkv, Dh)
         q, k, v = t[:, :, :H], t[:, :, H:H + Hkv], t[:, :, H + Hkv:]
+        if _OBSERVER is not None and anchor is not None:
+            _OBSERVER.attention(anchor, q, k, causal, doc_start)
         o, lse = flash_fwd(q, k, v, causal, doc_start, window)
         ctx.save_for_backward(qkv, o, lse, cs, doc_start, doc_end, pos)
         ctx.cfg = (B, S, H, Hkv, Dh, causal, window)
@@ -165,7 +191,7 @@ class RopeAttnFn(torch.autograd.Function):
         flash_bwd(do.contiguous().view(B, S, H, Dh), q, k, v, o, lse, dt[:, :, :H], dt[:, :, H:H + Hkv],
                   dt[:, :, H + Hkv:], causal, doc_start, doc_end, window)
         F.rope_(dqkv, cs, H + Hkv, Dh, S, pos, backward=True)
-        return (dqkv,) + (None,) * 11
+        return (dqkv,) + (None,) * 12
 
 
 class GluLinearFn(torch.autograd.Function):
@@ -176,7 +202,10 @@ class GluLinearFn(torch.autograd.Function):
         a = F.glu_fwd(gu, mode)
         ctx.save_for_backward(gu)
         ctx.w, ctx.mode = w, mode
-        return mm_nt(a, w.detach())
+        out = mm_nt(a, w.detach())
+        if _OBSERVER is not None:
+            _OBSERVER.linear_fwd([w], a, out)
+        return out
 
     @staticmethod
     def backward(ctx, dy):
@@ -187,6 +216,8 @@ class GluLinearFn(torch.autograd.Function):
         (dw,) = _emit_wgrad([w], dy, a) if w.requires_grad else (None,)
         del a
         da = mm_nn(dy, w.detach())
+        if _OBSERVER is not None:
+            _OBSERVER.linear_bwd([w], dy, da, [dw])
         return F.glu_bwd(gu, da, ctx.mode), dw, None
 
 
@@ -198,7 +229,10 @@ class ActLinearFn(torch.autograd.Function):
         a = F.act_fwd(u, mode)
         ctx.save_for_backward(u)
         ctx.w, ctx.mode = w, mode
-        return mm_nt(a, w.detach())
+        out = mm_nt(a, w.detach())
+        if _OBSERVER is not None:
+            _OBSERVER.linear_fwd([w], a, out)
+        return out
 
     @staticmethod
     def backward(ctx, dy):
@@ -209,6 +243,8 @@ class ActLinearFn(torch.autograd.Function):
         (dw,) = _emit_wgrad([w], dy, a) if w.requires_grad else (None,)
         del a
         da = mm_nn(dy, w.detach())
+        if _OBSERVER is not None:
+            _OBSERVER.linear_bwd([w], dy, da, [dw])
         return F.act_bwd(u, da, ctx.mode), dw, None
 
 
