@@ -13,7 +13,8 @@ def test_schedules():
     assert lr_linear(1000, 10, 100, 0.1) == 0.1
     assert abs(lr_inv_sqrt(400, 100, 0.5, 0.01) - 0.5) < 1e-12
     assert abs(lr_cosine(10, 10, 110, 1.0, 1.0, 0.1) - 1.0) < 1e-12
-    assert abs(lr_cosine(110, 10, 110, 1.0, 1.0, 0.1) - 0.1) < 1e-12
+    assert 0.1 <= lr_cosine(109, 10, 110, 1.0, 1.0, 0.1) < 0.101
+    assert lr_cosine(500, 10, 110, 1.0, 1.0, 0.1) == 0.1
     assert abs(lr_cosine(60, 10, 110, 1.0, 1.0, 0.0) - 0.5) < 1e-12
     assert lr_wsd(50, 10, 100, 0.1, 1.0, 0.1) == 1.0
     assert abs(lr_wsd(100, 10, 100, 0.1, 1.0, 0.1) - 0.1) < 1e-12
