@@ -1,0 +1,288 @@
+// Sequence kernels of the recurrent / state-space models, all on channel-last [B, S, C] tensors
+// (one row per token, as the GEMMs produce them), so no transposes surround them:
+//
+//   * causal depthwise conv1d (+ SiLU) forward / backward with document resets, replacing the
+//     causal_conv1d extension used through apps/mamba/component/causal_conv1d_compilable.py;
+//   * first-order linear recurrence h_t = a_t h_{t-1} + b_t forward / backward for any sequence
+//     length, with document resets, replacing accelerated_scan
+//     (apps/fastRNN/component/compilable_scan.py), whose warp kernel needs power-of-two lengths.
+//
+// The scan is chunked: pass 1 reduces every chunk of SCAN_CHUNK steps to its transfer pair
+// (prod a, local h_end); pass 2 lets every chunk fold the pairs of the chunks before it (a few
+// dozen steps over a tiny array) and then replays its own steps with the right carry. Work is
+// (batch x chunks x channels) threads, reads are coalesced across channels.
+#include "common.cuh"
+#include "lingua_b200.h"
+
+namespace lb {
+
+constexpr int SCAN_CHUNK = 64;
+
+__device__ __forceinline__ float bf2f(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
+__device__ __forceinline__ float dsilu_f(float x) {
+  const float s = 1.f / (1.f + __expf(-x));
+  return s * (1.f + x * (1.f - s));
+}
+
+// ------------------------------------------------------------------ conv1d
+// y[b,s,c] = act(sum_j w[c,j] * x[b, s-(W-1)+j, c]); taps before doc_start[b,s] (or before 0) are 0.
+template <int W>
+__global__ void conv1d_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                  const int* __restrict__ doc_start, __nv_bfloat16* __restrict__ y, int B, int S,
+                                  int C, long long ldx, long long ldy, int act) {
+  const long long total = (long long)B * S * C;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int c = i % C;
+    const long long bs = i / C;
+    const int s = bs % S;
+    const int b = bs / S;
+    const int lo = doc_start ? doc_start[bs] : 0;
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < W; ++j) {
+      const int t = s - (W - 1) + j;
+      if (t >= lo) acc += bf2f(w[c * W + j]) * bf2f(x[((long long)b * S + t) * ldx + c]);
+    }
+    y[bs * ldy + c] = __float2bfloat16(act ? silu_f(acc) : acc);
+  }
+}
+// dx[b,t,c] = sum_j w[c,j] * g[b, t+(W-1)-j, c] where g = dy * act'(pre) and the tap is valid for
+// the receiving token (t >= its doc_start); dw[c,j] accumulated with atomics from per-thread sums.
+template <int W>
+__global__ void conv1d_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                  const int* __restrict__ doc_start, const __nv_bfloat16* __restrict__ dy,
+                                  __nv_bfloat16* __restrict__ dx, float* __restrict__ dw, int B, int S, int C,
+                                  long long ldx, long long ldy, long long lddx, int act, int rows_per_thread) {
+  // thread = (channel c, block of rows); rows are consecutive tokens of one sequence
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const long long n_rows = (long long)B * S;
+  const long long r0 = (long long)blockIdx.y * rows_per_thread;
+  float wv[W], dwacc[W];
+#pragma unroll
+  for (int j = 0; j < W; ++j) {
+    wv[j] = bf2f(w[c * W + j]);
+    dwacc[j] = 0.f;
+  }
+  for (long long r = r0; r < r0 + rows_per_thread && r < n_rows; ++r) {
+    const int s = r % S;
+    const long long b = r / S;
+    // dx for token (b, s): contributions of outputs s .. s+W-1 of the same sequence
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < W; ++j) {
+      const int so = s + (W - 1) - j;  // output position that used x[s] with tap j
+      if (so < S) {
+        const long long ro = b * S + so;
+        const int lo = doc_start ? doc_start[ro] : 0;
+        if (s >= lo) {
+          float g = bf2f(dy[ro * ldy + c]);
+          if (act) {
+            float pre = 0.f;
+#pragma unroll
+            for (int jj = 0; jj < W; ++jj) {
+              const int t = so - (W - 1) + jj;
+              if (t >= lo) pre += wv[jj] * bf2f(x[(b * S + t) * ldx + c]);
+            }
+            g *= dsilu_f(pre);
+          }
+          acc += wv[j] * g;
+          dwacc[j] += g * bf2f(x[r * ldx + c]);
+        }
+      }
+    }
+    dx[r * lddx + c] = __float2bfloat16(acc);
+  }
+#pragma unroll
+  for (int j = 0; j < W; ++j) atomicAdd(dw + c * W + j, dwacc[j]);
+}
+
+// ------------------------------------------------------------------ linear recurrence
+// Forward pass 1: per (b, chunk, c): A = prod a, H = local end state (zero carry). A document
+// start inside the chunk cuts the product (a is taken as 0 at the first token of a document).
+__global__ void scan_reduce_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ bb,
+                                   const int* __restrict__ doc_start, float* __restrict__ agg_a,
+                                   float* __restrict__ agg_h, int B, int S, int C, int n_chunks, int reverse,
+                                   const __nv_bfloat16* __restrict__ shifted_a) {
+  const long long total = (long long)B * n_chunks * C;
+  const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int c = i % C;
+  const long long bk = i / C;
+  const int k = bk % n_chunks;
+  const int b = bk / n_chunks;
+  const int s0 = k * SCAN_CHUNK, s1 = min(S, s0 + SCAN_CHUNK);
+  float A = 1.f, H = 0.f;
+  if (!reverse) {
+    for (int s = s0; s < s1; ++s) {
+      const long long idx = ((long long)b * S + s) * C + c;
+      float av = bf2f(a[idx]);
+      if (doc_start && doc_start[(long long)b * S + s] == s) av = 0.f;
+      H = av * H + bf2f(bb[idx]);
+      A *= av;
+    }
+  } else {
+    // reverse recurrence g_s = dh_s + a_{s+1} g_{s+1}: coefficient of step s is a_{s+1} (0 past the
+    // end or when s+1 starts a new document)
+    for (int s = s1 - 1; s >= s0; --s) {
+      const long long idx = ((long long)b * S + s) * C + c;
+      float av = 0.f;
+      if (s + 1 < S && !(doc_start && doc_start[(long long)b * S + s + 1] == s + 1))
+        av = bf2f(shifted_a[idx + C]);
+      H = av * H + bf2f(bb[idx]);
+      A *= av;
+    }
+  }
+  agg_a[i] = A;
+  agg_h[i] = H;
+}
+
+// Forward pass 2: fold the aggregates of the earlier chunks into a carry, then replay.
+// mode 0: h (bf16) out. Optionally h0 [B, C] initial state and h_last [B, C] final state.
+__global__ void scan_apply_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ bb,
+                                  const int* __restrict__ doc_start, const float* __restrict__ agg_a,
+                                  const float* __restrict__ agg_h, const float* __restrict__ h0,
+                                  __nv_bfloat16* __restrict__ h, float* __restrict__ h_last, int B, int S, int C,
+                                  int n_chunks) {
+  const long long total = (long long)B * n_chunks * C;
+  const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int c = i % C;
+  const long long bk = i / C;
+  const int k = bk % n_chunks;
+  const int b = bk / n_chunks;
+  float carry = h0 ? h0[(long long)b * C + c] : 0.f;
+  for (int kk = 0; kk < k; ++kk) {
+    const long long j = ((long long)b * n_chunks + kk) * C + c;
+    carry = agg_a[j] * carry + agg_h[j];
+  }
+  const int s0 = k * SCAN_CHUNK, s1 = min(S, s0 + SCAN_CHUNK);
+  float H = carry;
+  for (int s = s0; s < s1; ++s) {
+    const long long idx = ((long long)b * S + s) * C + c;
+    float av = bf2f(a[idx]);
+    if (doc_start && doc_start[(long long)b * S + s] == s) av = 0.f;
+    H = av * H + bf2f(bb[idx]);
+    h[idx] = __float2bfloat16(H);
+  }
+  if (h_last && k == n_chunks - 1) h_last[(long long)b * C + c] = H;
+}
+
+// Backward pass 2: g_s = dh_s + a_{s+1} g_{s+1} (reverse); db_s = g_s; da_s = g_s * h_{s-1}
+// (h_{-1} = h0 or 0; 0 at a document start).
+__global__ void scan_bwd_apply_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ h,
+                                      const __nv_bfloat16* __restrict__ dh, const int* __restrict__ doc_start,
+                                      const float* __restrict__ agg_a, const float* __restrict__ agg_h,
+                                      const float* __restrict__ h0, __nv_bfloat16* __restrict__ da,
+                                      __nv_bfloat16* __restrict__ db, int B, int S, int C, int n_chunks) {
+  const long long total = (long long)B * n_chunks * C;
+  const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int c = i % C;
+  const long long bk = i / C;
+  const int k = bk % n_chunks;
+  const int b = bk / n_chunks;
+  float carry = 0.f;
+  for (int kk = n_chunks - 1; kk > k; --kk) {
+    const long long j = ((long long)b * n_chunks + kk) * C + c;
+    carry = agg_a[j] * carry + agg_h[j];
+  }
+  const int s0 = k * SCAN_CHUNK, s1 = min(S, s0 + SCAN_CHUNK);
+  float G = carry;
+  for (int s = s1 - 1; s >= s0; --s) {
+    const long long idx = ((long long)b * S + s) * C + c;
+    float av = 0.f;
+    if (s + 1 < S && !(doc_start && doc_start[(long long)b * S + s + 1] == s + 1)) av = bf2f(a[idx + C]);
+    G = av * G + bf2f(dh[idx]);
+    db[idx] = __float2bfloat16(G);
+    // forward took a_s = 0 at the first token of a document: no gradient flows into it
+    const bool cut = doc_start && doc_start[(long long)b * S + s] == s;
+    float hprev = 0.f;
+    if (!cut) hprev = s > 0 ? bf2f(h[idx - C]) : (h0 ? h0[(long long)b * C + c] : 0.f);
+    da[idx] = __float2bfloat16(G * hprev);
+  }
+}
+
+static inline int blocks_for(long long n, int t) { return (int)((n + t - 1) / t); }
+
+}  // namespace lb
+
+using namespace lb;
+typedef __nv_bfloat16 bf16;
+
+extern "C" int lb_conv1d_fwd(const void* x, const void* w, const int* doc_start, void* y, int B, int S, int C,
+                             int W, long long ldx, long long ldy, int act, void* stream) {
+  const long long total = (long long)B * S * C;
+  if (total == 0) return 0;
+  long long nb = (total + 255) / 256;
+  const long long cap = (long long)num_sms() * 16;
+  int grid = (int)(nb < cap ? nb : cap);
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (W) {
+    case 2: conv1d_fwd_kernel<2><<<grid, 256, 0, st>>>((const bf16*)x, (const bf16*)w, doc_start, (bf16*)y, B, S, C, ldx, ldy, act); break;
+    case 3: conv1d_fwd_kernel<3><<<grid, 256, 0, st>>>((const bf16*)x, (const bf16*)w, doc_start, (bf16*)y, B, S, C, ldx, ldy, act); break;
+    case 4: conv1d_fwd_kernel<4><<<grid, 256, 0, st>>>((const bf16*)x, (const bf16*)w, doc_start, (bf16*)y, B, S, C, ldx, ldy, act); break;
+    default: return 1;
+  }
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}
+
+// dw: fp32 [C, W], accumulated into (zero it first for a fresh gradient)
+extern "C" int lb_conv1d_bwd(const void* x, const void* w, const int* doc_start, const void* dy, void* dx, float* dw,
+                             int B, int S, int C, int W, long long ldx, long long ldy, long long lddx, int act,
+                             void* stream) {
+  if ((long long)B * S * C == 0) return 0;
+  const int rows_per_thread = 64;
+  dim3 grid((C + 127) / 128, (unsigned)(((long long)B * S + rows_per_thread - 1) / rows_per_thread));
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (W) {
+    case 2: conv1d_bwd_kernel<2><<<grid, 128, 0, st>>>((const bf16*)x, (const bf16*)w, doc_start, (const bf16*)dy, (bf16*)dx, dw, B, S, C, ldx, ldy, lddx, act, rows_per_thread); break;
+    case 3: conv1d_bwd_kernel<3><<<grid, 128, 0, st>>>((const bf16*)x, (const bf16*)w, doc_start, (const bf16*)dy, (bf16*)dx, dw, B, S, C, ldx, ldy, lddx, act, rows_per_thread); break;
+    case 4: conv1d_bwd_kernel<4><<<grid, 128, 0, st>>>((const bf16*)x, (const bf16*)w, doc_start, (const bf16*)dy, (bf16*)dx, dw, B, S, C, ldx, ldy, lddx, act, rows_per_thread); break;
+    default: return 1;
+  }
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}
+
+// a, b, h: contiguous [B, S, C] bf16. scratch: 2 * B * ceil(S/64) * C floats. h0 / h_last: [B, C]
+// fp32 or NULL.
+extern "C" int lb_scan_fwd(const void* a, const void* b, const int* doc_start, const float* h0, void* h,
+                           float* h_last, float* scratch, int B, int S, int C, void* stream) {
+  if ((long long)B * S * C == 0) return 0;
+  const int n_chunks = (S + SCAN_CHUNK - 1) / SCAN_CHUNK;
+  const long long n = (long long)B * n_chunks * C;
+  float* agg_a = scratch;
+  float* agg_h = scratch + n;
+  cudaStream_t st = (cudaStream_t)stream;
+  scan_reduce_kernel<<<blocks_for(n, 256), 256, 0, st>>>((const bf16*)a, (const bf16*)b, doc_start, agg_a, agg_h, B,
+                                                         S, C, n_chunks, 0, nullptr);
+  scan_apply_kernel<<<blocks_for(n, 256), 256, 0, st>>>((const bf16*)a, (const bf16*)b, doc_start, agg_a, agg_h, h0,
+                                                        (bf16*)h, h_last, B, S, C, n_chunks);
+  g_launches.fetch_add(2, std::memory_order_relaxed);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}
+
+extern "C" int lb_scan_bwd(const void* a, const void* h, const void* dh, const int* doc_start, const float* h0,
+                           void* da, void* db, float* scratch, int B, int S, int C, void* stream) {
+  if ((long long)B * S * C == 0) return 0;
+  const int n_chunks = (S + SCAN_CHUNK - 1) / SCAN_CHUNK;
+  const long long n = (long long)B * n_chunks * C;
+  float* agg_a = scratch;
+  float* agg_h = scratch + n;
+  cudaStream_t st = (cudaStream_t)stream;
+  scan_reduce_kernel<<<blocks_for(n, 256), 256, 0, st>>>(nullptr, (const bf16*)dh, doc_start, agg_a, agg_h, B, S, C,
+                                                         n_chunks, 1, (const bf16*)a);
+  scan_bwd_apply_kernel<<<blocks_for(n, 256), 256, 0, st>>>((const bf16*)a, (const bf16*)h, (const bf16*)dh,
+                                                            doc_start, agg_a, agg_h, h0, (bf16*)da, (bf16*)db, B, S,
+                                                            C, n_chunks);
+  g_launches.fetch_add(2, std::memory_order_relaxed);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}

@@ -129,6 +129,9 @@ class RMSNorm(nn.Module):
         self.weight = nn.Parameter(torch.ones(dim))
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if _is_native(self.weight) and x.dtype == torch.bfloat16:
+            y = _AddNormFn.apply(x.reshape(-1, x.shape[-1]).contiguous(), None, self.weight, self.eps)
+            return y.view(x.shape)
         xf = x.float()
         out = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.eps)
         return (out * self.weight.float()).type_as(x)

@@ -104,6 +104,10 @@ def _declare(lib) -> None:
         "lb_cast_f32_bf16": [fp, vp, ll, vp],
         "lb_attn_fwd": [C.POINTER(AttnArgs), vp],
         "lb_attn_bwd": [C.POINTER(AttnArgs), vp],
+        "lb_conv1d_fwd": [vp, vp, ip, vp, i, i, i, i, ll, ll, i, vp],
+        "lb_conv1d_bwd": [vp, vp, ip, vp, vp, fp, i, i, i, i, ll, ll, ll, i, vp],
+        "lb_scan_fwd": [vp, vp, ip, fp, vp, fp, fp, i, i, i, vp],
+        "lb_scan_bwd": [vp, vp, vp, ip, fp, vp, vp, fp, i, i, i, vp],
         "lb_decode_attn": [vp, vp, vp, vp, vp, ip, ip, vp, i, i, i, i, ll, ll, f, vp],
     }
     for name, args in sigs.items():
