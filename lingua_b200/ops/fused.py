@@ -39,8 +39,11 @@ def fused_view(ws: Sequence[torch.Tensor]) -> Optional[torch.Tensor]:
     base = ws[0]
     K = base.shape[1]
     ptr = base.data_ptr()
+    store = base.untyped_storage().data_ptr()
     for w in ws:
         if not w.is_contiguous() or w.shape[1] != K or w.data_ptr() != ptr or w.dtype != base.dtype:
+            return None
+        if w.untyped_storage().data_ptr() != store:  # neighbours by accident, not one buffer
             return None
         ptr += w.numel() * w.element_size()
     rows = sum(w.shape[0] for w in ws)
