@@ -1,0 +1,159 @@
+"""Kernel micro-benchmarks: ``python -m lingua_b200.ops.microbench <op> [--size ...] [--iters N]``.
+
+Runs one native op on synthetic inputs, times it with CUDA events (after warm-up, inputs larger
+than L2 or an L2 flush between iterations) and prints achieved TFLOP/s or GB/s next to the
+measured peaks of ``MEASURED_PEAKS.json`` when that file is present. It is also the small,
+self-terminating workload to put under ``ncu`` when profiling a single kernel.
+
+ops: gemm, gemm_wgrad, attn_fwd, attn_bwd, rmsnorm, rmsnorm_bwd, glu, ce, adamw, rope, scan, conv1d, decode
+"""
+from __future__ import annotations
+
+import argparse
+import json
+from pathlib import Path
+
+import torch
+
+from . import _lib
+from . import attention as A
+from . import functional as F
+from . import gemm as G
+from . import sequence as Q
+
+
+def _peaks():
+    p = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    try:
+        return json.loads(p.read_text())
+    except Exception:
+        return {}
+
+
+def _time(fn, iters, flush):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    tot = 0.0
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()  # 256 MB write evicts the 126 MB L2
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        tot += e0.elapsed_time(e1)
+    return tot / iters
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("op")
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=8192)
+    ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--batch", type=int, default=2)
+    ap.add_argument("--seq", type=int, default=4096)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--bn", type=int, default=0, help="gemm tile selector: 0 auto, 128, 256, 512 (two-SM)")
+    a = ap.parse_args(argv)
+    dev, bf = "cuda", torch.bfloat16
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    flops = bytes_ = 0.0
+    M, N, K = a.m, a.n, a.k
+    if a.op == "gemm":
+        x, w = torch.randn(M, K, device=dev, dtype=bf), torch.randn(N, K, device=dev, dtype=bf)
+        fn = lambda: G.gemm(x, w, force_bn=a.bn)
+        flops = 2.0 * M * N * K
+    elif a.op == "gemm_wgrad":
+        dy, x = torch.randn(K, M, device=dev, dtype=bf), torch.randn(K, N, device=dev, dtype=bf)
+        out = torch.zeros(M, N, device=dev)
+        fn = lambda: G.mm_tn(dy, x, out=out, accumulate=True, force_bn=a.bn)
+        flops = 2.0 * M * N * K
+    elif a.op in ("attn_fwd", "attn_bwd"):
+        B, S, H = a.batch, a.seq, a.heads
+        qkv = torch.randn(B, S, 3 * H, 128, device=dev, dtype=bf)
+        q, k, v = qkv[:, :, :H], qkv[:, :, H:2 * H], qkv[:, :, 2 * H:]
+        o, lse = A.flash_fwd(q, k, v)
+        do, dqkv = torch.randn_like(o), torch.empty_like(qkv)
+        if a.op == "attn_fwd":
+            fn = lambda: A.flash_fwd(q, k, v)
+            flops = 4.0 * B * H * S * S * 128 / 2
+        else:
+            fn = lambda: A.flash_bwd(do, q, k, v, o, lse, dqkv[:, :, :H], dqkv[:, :, H:2 * H], dqkv[:, :, 2 * H:])
+            flops = 10.0 * B * H * S * S * 128 / 2
+    elif a.op in ("rmsnorm", "rmsnorm_bwd"):
+        x, w = torch.randn(M, K, device=dev, dtype=bf), torch.ones(K, device=dev, dtype=bf)
+        y, _, rstd = F.rmsnorm_fwd(x, w, 1e-5)
+        if a.op == "rmsnorm":
+            fn = lambda: F.rmsnorm_fwd(x, w, 1e-5)
+            bytes_ = 2.0 * M * K * 2
+        else:
+            dy, dw = torch.randn_like(x), torch.zeros(K, device=dev)
+            fn = lambda: F.rmsnorm_bwd(dy, x, w, rstd, None, dw)
+            bytes_ = 3.0 * M * K * 2
+    elif a.op == "glu":
+        gu = torch.randn(M, 2 * K, device=dev, dtype=bf)
+        fn = lambda: F.glu_fwd(gu)
+        bytes_ = 3.0 * M * K * 2
+    elif a.op == "ce":
+        logits = torch.randn(2048, 128256, device=dev)
+        tgt = torch.randint(0, 128256, (2048,), device=dev)
+        fn = lambda: F.ce_fwd(logits, tgt)
+        bytes_ = 2.0 * logits.numel() * 4
+    elif a.op == "adamw":
+        n = 512 << 20
+        p, m, v, g = (torch.zeros(n, device=dev) for _ in range(4))
+        p16 = torch.zeros(n, device=dev, dtype=bf)
+        fn = lambda: F.adamw_step(p, m, v, g, p16, step=1, lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1)
+        bytes_ = n * 30.0
+    elif a.op == "rope":
+        B, S, H = a.batch, a.seq, a.heads
+        qkv = torch.randn(B * S, 3 * H * 128, device=dev, dtype=bf)
+        cs = F.rope_table(128, S, 10000.0, dev)
+        fn = lambda: F.rope_(qkv, cs, 2 * H, 128, S)
+        bytes_ = 2.0 * B * S * 2 * H * 128 * 2
+    elif a.op == "scan":
+        B, S, C = 4, a.seq, 4096
+        aa = torch.rand(B, S, C, device=dev).bfloat16()
+        bb = torch.randn(B, S, C, device=dev, dtype=bf)
+        fn = lambda: Q.linear_scan(aa, bb)
+        bytes_ = 5.0 * B * S * C * 2
+    elif a.op == "conv1d":
+        B, S, C = 4, a.seq, 4352
+        x, w = torch.randn(B, S, C, device=dev, dtype=bf), torch.randn(C, 4, device=dev, dtype=bf)
+        fn = lambda: Q.causal_conv1d(x, w)
+        bytes_ = 2.0 * B * S * C * 2
+    elif a.op == "decode":
+        import math
+
+        nseq, H, L = 32, a.heads, 768
+        q = torch.randn(nseq, H, 128, device=dev, dtype=bf)
+        kc, vc = torch.randn(nseq * L, H, 128, device=dev, dtype=bf), torch.randn(nseq * L, H, 128, device=dev, dtype=bf)
+        start = (torch.arange(nseq, device=dev) * L).int()
+        ln = torch.full((nseq,), L, device=dev, dtype=torch.int32)
+        out = torch.empty_like(q)
+        lib = _lib.load()
+        fn = lambda: _lib.check(lib.lb_decode_attn(q.data_ptr(), None, None, kc.data_ptr(), vc.data_ptr(),
+                                                   start.data_ptr(), ln.data_ptr(), out.data_ptr(), nseq, H, H, 128,
+                                                   H * 128, H * 128, 1 / math.sqrt(128), _lib.stream_ptr()), "decode")
+        bytes_ = 2.0 * nseq * L * H * 128 * 2
+    else:
+        raise SystemExit(f"unknown op {a.op}")
+    ms = _time(fn, a.iters, flush)
+    _lib.check_status()
+    pk = _peaks()
+    if flops:
+        tf = flops / ms / 1e9
+        frac = f", {tf / pk['bf16_tflops']:.2f} of measured cuBLAS burst peak" if pk.get("bf16_tflops") else ""
+        print(f"{a.op}: {ms:.3f} ms, {tf:.0f} TFLOP/s{frac}")
+    else:
+        gbs = bytes_ / ms / 1e6
+        frac = f", {gbs / pk['hbm_gbs']:.2f} of measured copy bandwidth" if pk.get("hbm_gbs") else ""
+        print(f"{a.op}: {ms:.3f} ms, {gbs:.0f} GB/s{frac}")
+
+
+if __name__ == "__main__":
+    main()
