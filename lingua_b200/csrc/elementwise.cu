@@ -126,72 +126,87 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(
   }
 }
 
-// dx = rstd * (dy*w - xhat * mean(dy*w*xhat)) (+ dres); dw += sum_rows dy * xhat (fp32 atomics).
-// Persistent over rows so that each block issues one set of atomics.
-__global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(
+// Backward in two kernels. (1) one block per row: dx = rstd * (dy*w - xhat * mean(dy*w*xhat)) (+ dres).
+// (2) dw += sum_rows dy * xhat as a column reduction: a block owns 256 columns and a band of rows,
+// 8 row lanes accumulate in registers, are combined in shared memory and added with one atomic
+// per column. Splitting costs one extra read of dy and x but keeps both kernels small enough for
+// full occupancy (the fused single-kernel form was latency bound at 24 % of copy bandwidth).
+__global__ void __launch_bounds__(256) rmsnorm_bwd_dx_kernel(
     const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
     const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
-    const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
-    float* __restrict__ dw, int M, int D) {
+    const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx, int D) {
   __shared__ float red[33];
+  const long long row = blockIdx.x;
   const int nvec = D / 8;
-  float dwacc[NORM_MAX_VEC][8];
-  float wv[NORM_MAX_VEC][8];
+  const float rs = rstd[row];
+  float xh[NORM_MAX_VEC][8], g[NORM_MAX_VEC][8];
+  float dot = 0.f;
 #pragma unroll
   for (int i = 0; i < NORM_MAX_VEC; ++i) {
     const int v = threadIdx.x + i * blockDim.x;
+    if (v < nvec) {
+      float xv[8], dv[8], wv[8];
+      ld8(x + row * D + v * 8).unpack(xv);
+      ld8(dy + row * D + v * 8).unpack(dv);
+      ld8(w + v * 8).unpack(wv);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
-    if (v < nvec) ld8(w + v * 8).unpack(wv[i]);
-  }
-  for (long long row = blockIdx.x; row < M; row += gridDim.x) {
-    const float rs = rstd[row];
-    float xh[NORM_MAX_VEC][8], g[NORM_MAX_VEC][8];
-    float dot = 0.f;
-#pragma unroll
-    for (int i = 0; i < NORM_MAX_VEC; ++i) {
-      const int v = threadIdx.x + i * blockDim.x;
-      if (v < nvec) {
-        float xv[8], dv[8];
-        ld8(x + row * D + v * 8).unpack(xv);
-        ld8(dy + row * D + v * 8).unpack(dv);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          xh[i][j] = xv[j] * rs;
-          g[i][j] = dv[j] * wv[i][j];
-          dot += g[i][j] * xh[i][j];
-          dwacc[i][j] += dv[j] * xh[i][j];
-        }
-      }
-    }
-    dot = block_sum(dot, red) / D;
-#pragma unroll
-    for (int i = 0; i < NORM_MAX_VEC; ++i) {
-      const int v = threadIdx.x + i * blockDim.x;
-      if (v < nvec) {
-        float o[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = rs * (g[i][j] - xh[i][j] * dot);
-        if (dres) {
-          float r[8];
-          ld8(dres + row * D + v * 8).unpack(r);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] += r[j];
-        }
-        bf16x8 ov;
-        ov.pack(o);
-        st8(dx + row * D + v * 8, ov);
+      for (int j = 0; j < 8; ++j) {
+        xh[i][j] = xv[j] * rs;
+        g[i][j] = dv[j] * wv[j];
+        dot += g[i][j] * xh[i][j];
       }
     }
   }
-  if (dw) {
+  dot = block_sum(dot, red) / D;
 #pragma unroll
-    for (int i = 0; i < NORM_MAX_VEC; ++i) {
-      const int v = threadIdx.x + i * blockDim.x;
-      if (v < nvec) {
+  for (int i = 0; i < NORM_MAX_VEC; ++i) {
+    const int v = threadIdx.x + i * blockDim.x;
+    if (v < nvec) {
+      float o[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) atomicAdd(dw + v * 8 + j, dwacc[i][j]);
+      for (int j = 0; j < 8; ++j) o[j] = rs * (g[i][j] - xh[i][j] * dot);
+      if (dres) {
+        float r[8];
+        ld8(dres + row * D + v * 8).unpack(r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] += r[j];
       }
+      bf16x8 ov;
+      ov.pack(o);
+      st8(dx + row * D + v * 8, ov);
+    }
+  }
+}
+
+constexpr int DW_ROWS_PER_BLOCK = 128;
+__global__ void __launch_bounds__(256) rmsnorm_bwd_dw_kernel(
+    const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x, const float* __restrict__ rstd,
+    float* __restrict__ dw, long long M, int D) {
+  __shared__ float part[8][32][8];
+  const int cv = blockIdx.x * 32 + threadIdx.x;  // 8-column vector index
+  const int ry = threadIdx.y;
+  const long long r0 = (long long)blockIdx.y * DW_ROWS_PER_BLOCK;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (cv * 8 < D) {
+    for (long long r = r0 + ry; r < r0 + DW_ROWS_PER_BLOCK && r < M; r += 8) {
+      float xv[8], dv[8];
+      ld8(x + r * D + cv * 8).unpack(xv);
+      ld8(dy + r * D + cv * 8).unpack(dv);
+      const float rs = rstd[r];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += dv[j] * xv[j] * rs;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) part[ry][threadIdx.x][j] = acc[j];
+  __syncthreads();
+  if (ry == 0 && cv * 8 < D) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float t = 0.f;
+#pragma unroll
+      for (int y = 0; y < 8; ++y) t += part[y][threadIdx.x][j];
+      atomicAdd(dw + cv * 8 + j, t);
     }
   }
 }
@@ -556,9 +571,13 @@ extern "C" int lb_rmsnorm_bwd(const void* dy, const void* x, const void* w, cons
                               const void* dres, void* dx, float* dw, long long M, int D, void* stream) {
   if (D % 8 || D > 256 * 8 * NORM_MAX_VEC) return 1;
   if (M == 0) return 0;
-  long long grid = M < num_sms() * 4 ? M : num_sms() * 4;
-  rmsnorm_bwd_kernel<<<(unsigned)grid, 256, 0, S_(stream)>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w,
-                                                             rstd, (const bf16*)dres, (bf16*)dx, dw, (int)M, D);
+  rmsnorm_bwd_dx_kernel<<<(unsigned)M, 256, 0, S_(stream)>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd,
+                                                            (const bf16*)dres, (bf16*)dx, D);
+  if (dw) {
+    dim3 grid((D / 8 + 31) / 32, (unsigned)((M + DW_ROWS_PER_BLOCK - 1) / DW_ROWS_PER_BLOCK));
+    rmsnorm_bwd_dw_kernel<<<grid, dim3(32, 8), 0, S_(stream)>>>((const bf16*)dy, (const bf16*)x, rstd, dw, M, D);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+  }
   LB_LAUNCH_END();
 }
 extern "C" int lb_rope(void* qk, const void* cs, const int* pos_idx, long long n_tok, int seq_len, int ld,
