@@ -131,6 +131,8 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="7b", choices=list(MODELS))
     ap.add_argument("--ref-eager", action="store_true", help="reference arm without torch.compile")
+    ap.add_argument("--sac", default="auto", choices=["auto", "on", "off"],
+                    help="recompute cheap activations in backward (auto: only where memory needs it)")
     a = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -193,7 +195,12 @@ def main() -> None:
             from lingua_b200.ops import _lib
             from lingua_b200.optim import OptimArgs
 
-            tr = Trainer(LMTransformerArgs(**mcfg), DistributedArgs(dp_shard=world, fsdp_type="full_shard"),
+            # the reference's 7B config trains without activation checkpointing; a single GPU holding the
+            # whole 7B optimiser state has no room for that, so there the cheap activations are recomputed
+            sac = a.sac == "on" or (a.sac == "auto" and world == 1 and a.model == "7b")
+            extra["selective_activation_checkpointing"] = sac
+            tr = Trainer(LMTransformerArgs(**mcfg), DistributedArgs(dp_shard=world, fsdp_type="full_shard",
+                                                                    selective_activation_checkpointing=sac),
                          OptimArgs(lr=1e-3, warmup=2000, clip=1.0), total_steps=100000, device=dev)
             dev_batches = [views(h).to(dev) for h in host]
             host_batches = [views(h).contiguous().pin_memory() for h in host]

@@ -347,4 +347,8 @@ def parallelize_model(model, mesh: Mesh, model_args, distributed_args: Distribut
             elif buf is not None and buf.device != device:
                 buf_owner._buffers[name] = buf.to(device)
     model._engine = engine
+    # selective activation checkpointing on = recompute the cheap activations in backward
+    from .ops import fused
+
+    fused.set_recompute(distributed_args.selective_activation_checkpointing)
     return model, engine

@@ -31,6 +31,16 @@ def set_observer(obs) -> None:
     _OBSERVER = obs
 
 
+# True: keep only GEMM / attention outputs and recompute normalised and gated activations in
+# backward (the selective-checkpointing policy). False: keep them too (more memory, ~1.5 % faster).
+_RECOMPUTE = True
+
+
+def set_recompute(flag: bool) -> None:
+    global _RECOMPUTE
+    _RECOMPUTE = bool(flag)
+
+
 # ----------------------------------------------------------------------------- helpers
 def fused_view(ws: Sequence[torch.Tensor]) -> Optional[torch.Tensor]:
     """[sum(N_i), K] view over row-blocks that are adjacent in memory, or None."""
@@ -139,16 +149,22 @@ class NormLinearFn(torch.autograd.Function):
         if _OBSERVER is not None:
             _OBSERVER.resid(g, h)
             _OBSERVER.linear_fwd(ws, y, out)
-        ctx.save_for_backward(h, rstd)
+        if _RECOMPUTE:
+            ctx.save_for_backward(h, rstd)
+        else:
+            ctx.save_for_backward(h, rstd, y)
         ctx.g, ctx.ws, ctx.eps, ctx.has_res, ctx.tp_group = g, ws, eps, res is not None, tp_group
         return out, (h if res is not None else None)
 
     @staticmethod
     def backward(ctx, dout, dh_out):
-        h, rstd = ctx.saved_tensors
+        h, rstd = ctx.saved_tensors[:2]
         g, ws = ctx.g, ctx.ws
         dout = dout.contiguous()
-        y, _, _ = F.rmsnorm_fwd(h, g.detach(), ctx.eps, None)
+        if len(ctx.saved_tensors) == 3:
+            y = ctx.saved_tensors[2]
+        else:
+            y, _, _ = F.rmsnorm_fwd(h, g.detach(), ctx.eps, None)
         dws = _emit_wgrad(ws, dout, y) if ws[0].requires_grad else [None] * len(ws)
         del y
         dy = mm_nn(dout, _weights(ws))
@@ -203,7 +219,10 @@ class GluLinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, gu, w, mode):
         a = F.glu_fwd(gu, mode)
-        ctx.save_for_backward(gu)
+        if _RECOMPUTE:
+            ctx.save_for_backward(gu)
+        else:
+            ctx.save_for_backward(gu, a)
         ctx.w, ctx.mode = w, mode
         out = mm_nt(a, w.detach())
         if _OBSERVER is not None:
@@ -212,10 +231,10 @@ class GluLinearFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
-        (gu,) = ctx.saved_tensors
+        gu = ctx.saved_tensors[0]
         w = ctx.w
         dy = dy.contiguous()
-        a = F.glu_fwd(gu, ctx.mode)
+        a = ctx.saved_tensors[1] if len(ctx.saved_tensors) == 2 else F.glu_fwd(gu, ctx.mode)
         (dw,) = _emit_wgrad([w], dy, a) if w.requires_grad else (None,)
         del a
         da = mm_nn(dy, w.detach())
