@@ -1,0 +1,159 @@
+// Small kernels around the fused tensor-parallel GEMMs (gemm_tp.cu):
+//
+//   lb_peer_barrier   all ranks of a tensor-parallel group meet; every store a rank made before
+//                     the barrier (to its own or to a peer's memory) is visible to every rank's
+//                     kernels launched after it. One counter per (destination, source) pair in
+//                     peer-visible memory, bumped with a system-scope release and polled with a
+//                     system-scope acquire. The wait is bounded: after LB_WAIT_LIMIT_NS the kernel
+//                     records ST_TIMEOUT_FLAG in the status word and returns.
+//   lb_reduce_norm    h = residual + sum over slots (the partial products that gemm_tp mode 2
+//                     scattered to this rank), y = RMSNorm(h) * w, for this rank's rows. It is the
+//                     "reduce" half of the reduce-scatter fused with the residual add and the norm
+//                     that follows every attention / feed-forward output projection
+//                     (lingua/transformer.py:520-527).
+#include "common.cuh"
+#include "lingua_b200.h"
+
+namespace lb {
+
+struct BarrierParams {
+  uint32_t* pads[LB_MAX_PEERS];
+  int world, rank;
+  uint32_t epoch;
+  uint32_t* status;
+};
+
+__global__ void peer_barrier_kernel(const BarrierParams p) {
+  const int r = threadIdx.x;
+  if (r >= p.world) return;
+  __threadfence_system();
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.pads[r] + p.rank), "r"(1u) : "memory");
+  const uint32_t* mine = p.pads[p.rank] + r;
+  uint64_t t0 = 0;
+  for (uint32_t it = 0;; ++it) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+    if (static_cast<int32_t>(v - p.epoch) >= 0) break;
+    __nanosleep(100);
+    if ((it & 0xFFu) == 0xFFu) {
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > LB_WAIT_LIMIT_NS) {
+        if (p.status) atomicOr(p.status, ST_TIMEOUT_FLAG | 7u);
+        break;
+      }
+    }
+  }
+  __threadfence_system();
+}
+
+constexpr int RN_THREADS = 256;
+constexpr int RN_MAXV = 4;  // 8-element vectors per thread kept in registers: D <= 8192
+
+__global__ void __launch_bounds__(RN_THREADS)
+reduce_norm_kernel(const __nv_bfloat16* __restrict__ slots, int n_slots, long long slot_stride,
+                   const __nv_bfloat16* resid, const __nv_bfloat16* __restrict__ w, float eps,
+                   __nv_bfloat16* h_out, __nv_bfloat16* __restrict__ y_out,
+                   float* __restrict__ rstd_out, int D) {
+  const long long row = blockIdx.x;
+  const int nvec = D / 8;
+  float h[RN_MAXV][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < RN_MAXV; ++i) {
+    const int v = threadIdx.x + i * RN_THREADS;
+    if (v < nvec) {
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      for (int s = 0; s < n_slots; ++s) {
+        const uint4 q = *reinterpret_cast<const uint4*>(slots + s * slot_stride + row * D + v * 8);
+        const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(b[j]);
+          acc[2 * j] += f.x;
+          acc[2 * j + 1] += f.y;
+        }
+      }
+      if (resid) {
+        const uint4 q = *reinterpret_cast<const uint4*>(resid + row * D + v * 8);
+        const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(b[j]);
+          acc[2 * j] += f.x;
+          acc[2 * j + 1] += f.y;
+        }
+      }
+      // the residual stream is stored in bf16; the norm sees the stored value
+      uint4 o;
+      uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        ow[j] = pack_bf16(acc[2 * j], acc[2 * j + 1]);
+        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ow[j]));
+        h[i][2 * j] = f.x;
+        h[i][2 * j + 1] = f.y;
+        ss += f.x * f.x + f.y * f.y;
+      }
+      if (h_out) *reinterpret_cast<uint4*>(h_out + row * D + v * 8) = o;
+    }
+  }
+  if (!y_out) return;
+  __shared__ float red[RN_THREADS / 32];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int i = 0; i < RN_THREADS / 32; ++i) tot += red[i];
+  const float rstd = rsqrtf(tot / D + eps);
+  if (rstd_out && threadIdx.x == 0) rstd_out[row] = rstd;
+#pragma unroll
+  for (int i = 0; i < RN_MAXV; ++i) {
+    const int v = threadIdx.x + i * RN_THREADS;
+    if (v < nvec) {
+      const uint4 q = *reinterpret_cast<const uint4*>(w + v * 8);
+      const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&q);
+      uint4 o;
+      uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 g = __bfloat1622float2(b[j]);
+        ow[j] = pack_bf16(h[i][2 * j] * rstd * g.x, h[i][2 * j + 1] * rstd * g.y);
+      }
+      *reinterpret_cast<uint4*>(y_out + row * D + v * 8) = o;
+    }
+  }
+}
+
+}  // namespace lb
+
+extern "C" int lb_peer_barrier(void* const* pads, int world, int rank, uint32_t epoch, uint32_t* status,
+                               void* stream) {
+  if (!pads || world < 1 || world > LB_MAX_PEERS || rank < 0 || rank >= world) return 1;
+  lb::BarrierParams p;
+  for (int r = 0; r < LB_MAX_PEERS; ++r) p.pads[r] = reinterpret_cast<uint32_t*>(pads[r < world ? r : 0]);
+  p.world = world; p.rank = rank; p.epoch = epoch; p.status = status;
+  lb::peer_barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+  lb::g_launches.fetch_add(1, std::memory_order_relaxed);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}
+
+extern "C" int lb_reduce_norm(const void* slots, int n_slots, long long slot_stride, const void* resid,
+                              const void* w, float eps, void* h_out, void* y_out, float* rstd_out,
+                              long long rows, int D, void* stream) {
+  if (!slots || n_slots < 1 || rows <= 0) return 1;
+  if (D % 8 != 0 || D > 8 * lb::RN_THREADS * lb::RN_MAXV || slot_stride % 8 != 0) return 2;
+  if (y_out && !w) return 3;
+  using bf = __nv_bfloat16;
+  lb::reduce_norm_kernel<<<(unsigned)rows, lb::RN_THREADS, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const bf*>(slots), n_slots, slot_stride, reinterpret_cast<const bf*>(resid),
+      reinterpret_cast<const bf*>(w), eps, reinterpret_cast<bf*>(h_out), reinterpret_cast<bf*>(y_out), rstd_out, D);
+  lb::g_launches.fetch_add(1, std::memory_order_relaxed);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}

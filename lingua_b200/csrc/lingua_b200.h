@@ -75,6 +75,49 @@ int lb_attn_bwd(const LbAttnArgs* a, void* stream);
 int lb_attn_bwd_noalloc(const LbAttnArgs* a, void* stream);
 long long lb_attn_bwd_noalloc_max_rows(void);
 
+// Tensor-parallel GEMM with the collective fused in (bf16, K-contiguous operands, head of
+// gemm_tp.cu for the algorithm). `world` ranks, this one is `rank`; M is the row count of the
+// whole problem and must be a multiple of 128 * world; K % 64 == 0, N % 8 == 0.
+//   mode 1: C[M, N] = gather(a_peers[r] : [M/world, K] contiguous) * B[N, K]^T. a_peers[] are
+//           peer-visible addresses of every rank's slab (own included); gather is a local
+//           [M, K] bf16 buffer, flags a local uint32 array of M/128 + 1 words (world > 1 only).
+//   mode 2: partial = A[M, K] * B[N, K]^T; rows of owner o are stored into
+//           c_peers[o] + rank * slot_stride (row pitch ldc), i.e. every rank's staging buffer
+//           has one [M/world, N] slot per source rank.
+// The kernel never waits on another GPU; order the ranks with lb_peer_barrier.
+#define LB_MAX_PEERS 8
+typedef struct LbTpGemmArgs {
+  int mode;
+  int world, rank;
+  int M, N, K;
+  float alpha;
+  const void* B;
+  long long ldb;
+  uint32_t* status;
+  // mode 1
+  const void* a_peers[LB_MAX_PEERS];
+  void* gather;
+  uint32_t* flags;
+  void* C;
+  long long ldc;  // row pitch of C (mode 1) or of a staging slot (mode 2)
+  // mode 2
+  const void* A;
+  long long lda;
+  void* c_peers[LB_MAX_PEERS];
+  long long slot_stride;
+} LbTpGemmArgs;
+int lb_gemm_tp(const LbTpGemmArgs* a, void* stream);
+
+// Barrier over the ranks of a group. pads[r] is the peer-visible address of rank r's pad
+// (uint32[world], zero before first use); epoch is the number of this barrier on these pads,
+// counted from 1 by every rank alike. Bounded wait: on timeout the status word is set.
+int lb_peer_barrier(void* const* pads, int world, int rank, uint32_t epoch, uint32_t* status, void* stream);
+
+// h = resid + sum_s slots[s] (bf16 [rows, D] each, slot_stride elements apart), y = RMSNorm(h) * w.
+// resid, h_out, y_out (with w) and rstd_out are optional. D % 8 == 0, D <= 8192.
+int lb_reduce_norm(const void* slots, int n_slots, long long slot_stride, const void* resid, const void* w,
+                   float eps, void* h_out, void* y_out, float* rstd_out, long long rows, int D, void* stream);
+
 // Number of kernels launched by this library in this process so far.
 long long lb_launch_count(void);
 void lb_launch_count_add(long long n);

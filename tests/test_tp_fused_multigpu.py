@@ -1,0 +1,21 @@
+"""Fused tensor-parallel kernels over real NVLink peers: needs at least two GPUs in the box."""
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_tp_two_ranks():
+    n = 2
+    worker = Path(__file__).with_name("tp_fused_worker.py")
+    env = dict(os.environ)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+           "--master-addr", "127.0.0.1", "--master-port", "29653", str(worker)]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "TP_FUSED_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
