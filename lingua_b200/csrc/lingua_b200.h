@@ -75,6 +75,26 @@ int lb_attn_bwd(const LbAttnArgs* a, void* stream);
 int lb_attn_bwd_noalloc(const LbAttnArgs* a, void* stream);
 long long lb_attn_bwd_noalloc_max_rows(void);
 
+// Float8 linear layers (gemm_fp8.cu). C[m,n] = (A8[m,:] . B8[n,:]) * row_scale[m] * col_scale[n];
+// A8 [M, K], B8 [N, K] e4m3 with K contiguous (lda, ldb, K multiples of 16), scales fp32 or NULL.
+typedef struct LbGemmFp8Args {
+  const void* A;
+  const void* B;
+  void* C;
+  const float* row_scale;
+  const float* col_scale;
+  uint32_t* status;
+  int M, N, K;
+  int out_dtype;  // LB_BF16 or LB_F32
+  long long lda, ldb, ldc;
+} LbGemmFp8Args;
+int lb_gemm_fp8(const LbGemmFp8Args* a, void* stream);
+// x bf16 [rows, K] (row pitch ldx) -> out e4m3 [rows, K] (pitch ldo bytes), scale[r] = max(amax_r, 1e-12) / 448.
+int lb_quant_rows(const void* x, long long ldx, long long rows, int K, void* out, long long ldo, float* scale,
+                  void* stream);
+// w bf16 [N, K] contiguous -> out e4m3 [K, N] (pitch ldo bytes), every element divided by *scale (device fp32).
+int lb_quant_transpose(const void* w, int N, int K, const float* scale, void* out, long long ldo, void* stream);
+
 // Tensor-parallel GEMM with the collective fused in (bf16, K-contiguous operands, head of
 // gemm_tp.cu for the algorithm). `world` ranks, this one is `rank`; M is the row count of the
 // whole problem and must be a multiple of 128 * world; K % 64 == 0, N % 8 == 0.

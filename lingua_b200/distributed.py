@@ -37,6 +37,7 @@ class DistributedArgs:
     dp_shard: int = 1  # ranks that share one copy of the sharded state
     dp_replicate: int = 1  # replicas of that group (outer data-parallel dim)
     tp_size: int = 1
+    fused_tp_forward: bool = True  # no-grad TP passes use the fused all-gather / reduce-scatter GEMMs
     selective_activation_checkpointing: bool = False
     compile: bool = False
     fsdp_type: str = "no_shard"
@@ -351,4 +352,10 @@ def parallelize_model(model, mesh: Mesh, model_args, distributed_args: Distribut
     from .ops import fused
 
     fused.set_recompute(distributed_args.selective_activation_checkpointing)
+    if distributed_args.tp_size > 1 and distributed_args.fused_tp_forward and device.type == "cuda" \
+            and hasattr(model, "tok_embeddings"):
+        # evaluation / scoring passes run with the TP collectives inside the GEMM kernels
+        from .parallel.tp_fused import enable_fused_tp_forward
+
+        enable_fused_tp_forward(model, mesh.group("tp"), device)
     return model, engine

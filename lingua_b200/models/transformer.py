@@ -106,6 +106,11 @@ class Linear(nn.Module):
         if _is_native(self.weight):
             y = fused.LinearFn.apply(x.reshape(-1, self.in_features), self.weight)
             return y.view(*x.shape[:-1], self.out_features)
+        if getattr(self.weight, "lb_fp8", False):
+            from ..float8 import Fp8LinearFn
+
+            y = Fp8LinearFn.apply(x.reshape(-1, self.in_features), self.weight, None)
+            return y.view(*x.shape[:-1], self.out_features)
         return TF.linear(x, self.weight)
 
 
@@ -377,6 +382,11 @@ class LMTransformer(BaseTransformer):
         window = self.sliding_window or 0
         cs = self.rope_embeddings()
         if _is_native(self.tok_embeddings.weight):
+            tpf = getattr(self, "tp_fused", None)
+            if (tpf is not None and not torch.is_grad_enabled() and causal and tok_idx is None
+                    and doc_start is None and tpf.accepts(B, S) and self.layers[0].attention.kv_cache is None):
+                # tensor-parallel scoring / evaluation: collectives fused into the GEMM kernels
+                return tpf(token_values, target)
             return self._forward_native(token_values, target, tok_idx, doc_start, doc_end, window, causal, cs, B, S)
         h = self.tok_embeddings(token_values)
         for layer in self.layers:

@@ -65,6 +65,26 @@ def _weights(ws: Sequence[torch.Tensor]) -> torch.Tensor:
     return v if v is not None else torch.cat([w.detach() for w in ws], dim=0)
 
 
+def _fwd_mm(x: torch.Tensor, ws: Sequence[torch.Tensor]) -> torch.Tensor:
+    """x @ [W_0; W_1; ...]^T - in e4m3 with row-wise scales when the weights are marked for float8."""
+    w = _weights(ws)
+    if getattr(ws[0], "lb_fp8", False) and x.is_cuda and x.shape[0] >= 16:
+        from ..float8 import fp8_forward_mm
+
+        return fp8_forward_mm(x, w)
+    return mm_nt(x, w)
+
+
+def _dgrad_mm(dy: torch.Tensor, ws: Sequence[torch.Tensor]) -> torch.Tensor:
+    """dy @ [W_0; W_1; ...] - the float8 form scales dy by row and the stacked weight as one tensor."""
+    w = _weights(ws)
+    if getattr(ws[0], "lb_fp8", False) and dy.is_cuda and dy.shape[0] >= 16:
+        from ..float8 import fp8_dgrad_mm
+
+        return fp8_dgrad_mm(dy, w)
+    return mm_nn(dy, w)
+
+
 def _main_grads(ws: Sequence[torch.Tensor]) -> Optional[torch.Tensor]:
     if not all(hasattr(w, "main_grad") for w in ws):
         return None
@@ -117,7 +137,7 @@ class LinearFn(torch.autograd.Function):
     def forward(ctx, x, *ws):
         ctx.save_for_backward(x)
         ctx.ws = ws
-        out = mm_nt(x, _weights(ws))
+        out = _fwd_mm(x, ws)
         if _OBSERVER is not None:
             _OBSERVER.linear_fwd(ws, x, out)
         return out
@@ -127,7 +147,7 @@ class LinearFn(torch.autograd.Function):
         (x,) = ctx.saved_tensors
         ws = ctx.ws
         dy = dy.contiguous()
-        dx = mm_nn(dy, _weights(ws)) if ctx.needs_input_grad[0] else None
+        dx = _dgrad_mm(dy, ws) if ctx.needs_input_grad[0] else None
         dws = _emit_wgrad(ws, dy, x) if ws[0].requires_grad else [None] * len(ws)
         if _OBSERVER is not None:
             _OBSERVER.linear_bwd(ws, dy, dx, dws)
@@ -145,7 +165,7 @@ class NormLinearFn(torch.autograd.Function):
     def forward(ctx, x, res, g, eps, tp_group, *ws):
         y, h, rstd = F.rmsnorm_fwd(x, g.detach(), eps, res)
         h = x if h is None else h
-        out = mm_nt(y, _weights(ws))
+        out = _fwd_mm(y, ws)
         if _OBSERVER is not None:
             _OBSERVER.resid(g, h)
             _OBSERVER.linear_fwd(ws, y, out)
@@ -167,7 +187,7 @@ class NormLinearFn(torch.autograd.Function):
             y, _, _ = F.rmsnorm_fwd(h, g.detach(), ctx.eps, None)
         dws = _emit_wgrad(ws, dout, y) if ws[0].requires_grad else [None] * len(ws)
         del y
-        dy = mm_nn(dout, _weights(ws))
+        dy = _dgrad_mm(dout, ws)
         if _OBSERVER is not None:
             _OBSERVER.linear_bwd(ws, dout, dy, dws)
         if ctx.tp_group is not None:
@@ -224,7 +244,7 @@ class GluLinearFn(torch.autograd.Function):
         else:
             ctx.save_for_backward(gu, a)
         ctx.w, ctx.mode = w, mode
-        out = mm_nt(a, w.detach())
+        out = _fwd_mm(a, (w,))
         if _OBSERVER is not None:
             _OBSERVER.linear_fwd([w], a, out)
         return out
@@ -237,7 +257,7 @@ class GluLinearFn(torch.autograd.Function):
         a = ctx.saved_tensors[1] if len(ctx.saved_tensors) == 2 else F.glu_fwd(gu, ctx.mode)
         (dw,) = _emit_wgrad([w], dy, a) if w.requires_grad else (None,)
         del a
-        da = mm_nn(dy, w.detach())
+        da = _dgrad_mm(dy, (w,))
         if _OBSERVER is not None:
             _OBSERVER.linear_bwd([w], dy, da, [dw])
         return F.glu_bwd(gu, da, ctx.mode), dw, None
@@ -251,7 +271,7 @@ class ActLinearFn(torch.autograd.Function):
         a = F.act_fwd(u, mode)
         ctx.save_for_backward(u)
         ctx.w, ctx.mode = w, mode
-        out = mm_nt(a, w.detach())
+        out = _fwd_mm(a, (w,))
         if _OBSERVER is not None:
             _OBSERVER.linear_fwd([w], a, out)
         return out
@@ -264,7 +284,7 @@ class ActLinearFn(torch.autograd.Function):
         a = F.act_fwd(u, ctx.mode)
         (dw,) = _emit_wgrad([w], dy, a) if w.requires_grad else (None,)
         del a
-        da = mm_nn(dy, w.detach())
+        da = _dgrad_mm(dy, (w,))
         if _OBSERVER is not None:
             _OBSERVER.linear_bwd([w], dy, da, [dw])
         return F.act_bwd(u, da, ctx.mode), dw, None

@@ -67,6 +67,15 @@ def main(argv=None):
         x, w = torch.randn(M, K, device=dev, dtype=bf), torch.randn(N, K, device=dev, dtype=bf)
         fn = lambda: G.gemm(x, w, force_bn=a.bn)
         flops = 2.0 * M * N * K
+    elif a.op in ("gemm_fp8", "linear_fp8"):
+        from .. import float8 as F8
+
+        x, w = torch.randn(M, K, device=dev, dtype=bf), torch.randn(N, K, device=dev, dtype=bf)
+        x8, sx = F8.quant_rows(x)
+        w8, sw = F8.quant_rows(w)
+        # gemm_fp8: the scaled e4m3 product alone; linear_fp8: both quantisation passes included
+        fn = (lambda: F8.scaled_mm(x8, sx, w8, sw)) if a.op == "gemm_fp8" else (lambda: F8.fp8_forward_mm(x, w))
+        flops = 2.0 * M * N * K
     elif a.op == "gemm_wgrad":
         dy, x = torch.randn(K, M, device=dev, dtype=bf), torch.randn(K, N, device=dev, dtype=bf)
         out = torch.zeros(M, N, device=dev)

@@ -77,6 +77,8 @@ class ParamGroup:
             new_p = nn.Parameter(view, requires_grad=p.requires_grad)
             new_p.main_grad = self.grad[o:o + n].view(p.shape)
             new_p.grad_written = False
+            if getattr(p, "lb_fp8", False):  # float8 matmuls were requested for this weight
+                new_p.lb_fp8 = True
             params[i] = (fqn, new_p)
 
     def sync_master_from_full(self) -> None:

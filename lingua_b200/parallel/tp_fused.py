@@ -238,7 +238,10 @@ class FusedTPForward:
     def _cat(self, key, ws):
         # weights of one fused projection as a single [N, K] matrix (a view when they are adjacent)
         if key not in self._w:
-            self._w[key] = _weights(ws)
+            v = _weights(ws)
+            if v.data_ptr() != ws[0].data_ptr():
+                return v  # a copy: it would go stale after the next optimiser step, so it is not kept
+            self._w[key] = v
         return self._w[key]
 
     def steps(self, tokens: torch.Tensor, targets: Optional[torch.Tensor], out: dict) -> Generator[None, None, None]:
@@ -304,6 +307,22 @@ class FusedTPForward:
             self.peers.barrier()
         return out
 
+    def accepts(self, B: int, S: int) -> bool:
+        """Row tiles of 128 tokens must not straddle ranks."""
+        return (B * S) % (ROW_TILE * self.world) == 0
+
+    @torch.no_grad()
+    def __call__(self, tokens, targets=None) -> torch.Tensor:
+        """Same contract as ``LMTransformer.forward``: mean loss with targets, else logits [B, S, vocab]."""
+        if targets is not None:
+            return self.loss(tokens, targets)
+        local = self.forward(tokens)["logits"]
+        if self.world == 1 or not isinstance(self.peers, SymmetricPeers):
+            return local.view(*tokens.shape, -1)
+        full = torch.empty(local.shape[0] * self.world, local.shape[1], dtype=local.dtype, device=local.device)
+        dist.all_gather_into_tensor(full, local.contiguous(), group=self.peers.group)
+        return full.view(*tokens.shape, -1)
+
     @torch.no_grad()
     def loss(self, tokens, targets) -> torch.Tensor:
         out = self.forward(tokens, targets)
@@ -326,3 +345,19 @@ def run_local_group(runners: Sequence[FusedTPForward], tokens, targets=None) -> 
             except StopIteration:
                 alive = False
     return outs
+
+
+def enable_fused_tp_forward(model, group: dist.ProcessGroup, device: torch.device) -> bool:
+    """Route no-grad forward passes of a TP-sharded model through ``FusedTPForward``.
+
+    Returns False (and leaves the NCCL all-reduce path in place) when peer-visible memory cannot be
+    set up for ``group``, e.g. ranks on different nodes."""
+    import logging
+
+    try:
+        peers = SymmetricPeers(group, device)
+    except Exception as e:  # no NVLink peer access between the ranks of this group
+        logging.getLogger(__name__).warning("fused tensor-parallel forward disabled: %s", e)
+        return False
+    object.__setattr__(model, "tp_fused", FusedTPForward(model, peers))
+    return True
