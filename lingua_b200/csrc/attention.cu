@@ -377,7 +377,7 @@ constexpr int BWD_SMEM = 2 * AT_TILE /*K,V*/ + 4 * AT_TILE /*Q,dO x 2*/ + AT_TIL
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                 const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo,
-                const AttnParams p) {
+                const __grid_constant__ CUtensorMap tdq, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ int abort_flag;
   __shared__ uint32_t tmem_slot;
@@ -389,7 +389,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   const uint32_t bars = sbase + 7 * AT_TILE;
   const uint32_t kv_full = bars;
   auto qd_full = [&](int s) { return bars + 8 + 8 * s; };
-  auto qd_empty = [&](int s) { return bars + 24 + 8 * s; };
+  auto dq_staged = [&](int s) { return bars + 24 + 8 * s; };
   const uint32_t s_full = bars + 40, p_full = bars + 48, dv_done = bars + 56, ds_full = bars + 64;
   const uint32_t dq_full = bars + 72, dq_drained = bars + 80, dp_full = bars + 88, s_free = bars + 96;
 
@@ -414,7 +414,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     mbar_init(kv_full, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(qd_full(s), 1);
-      mbar_init(qd_empty(s), 1);
+      mbar_init(dq_staged(s), 8);
     }
     mbar_init(s_full, 1);
     mbar_init(p_full, 8);
@@ -447,17 +447,31 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       tma_load_4d(sK + AT_HALF, &tk, kv_full, 64, kv0, hk, b);
       tma_load_4d(sV, &tv, kv_full, 0, kv0, hk, b);
       tma_load_4d(sV + AT_HALF, &tv, kv_full, 64, kv0, hk, b);
-      for (int it = 0; it < n; ++it) {
+      // Stage s (Q and dO of query block `it`) is recycled in two steps: once dK and dQ of that block
+      // are done, the softmax warps spill dQ (fp32, 64 KB) over the two tiles; this thread adds it to
+      // the global accumulator with four TMA reductions and only then loads block it + 2.
+      for (int it = 0; it < n + 2; ++it) {
         const int s = it & 1;
+        if (it >= 2) {
+          const int j = it - 2;
+          if (!mbar_wait(dq_staged(s), (j >> 1) & 1, &abort_flag, p.status, 0x21)) break;
+          const int hj = hk * group + j / nq;
+          const int qj = (i0 + j % nq) * 128;
+#pragma unroll
+          for (int cb = 0; cb < 4; ++cb) tma_reduce_add_4d(&tdq, sQ(s) + cb * AT_HALF, cb * 32, qj, hj, b);
+          tma_store_commit();
+          tma_store_wait_read<0>();
+        }
+        if (it >= n) continue;
         const int h = hk * group + it / nq;
         const int q0 = (i0 + it % nq) * 128;
-        if (!mbar_wait(qd_empty(s), ((it >> 1) & 1) ^ 1, &abort_flag, p.status, 0x21)) break;
         mbar_arrive_expect_tx(qd_full(s), 2 * AT_TILE);
         tma_load_4d(sQ(s), &tq, qd_full(s), 0, q0, h, b);
         tma_load_4d(sQ(s) + AT_HALF, &tq, qd_full(s), 64, q0, h, b);
         tma_load_4d(sdO(s), &tdo, qd_full(s), 0, q0, h, b);
         tma_load_4d(sdO(s) + AT_HALF, &tdo, qd_full(s), 64, q0, h, b);
       }
+      tma_store_wait<0>();
     }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -506,7 +520,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         // dQ[q, d] = dS K, into the columns that held dP
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma_f16(tdP, desc_k(sP, k), desc_mn(sK, k), IDESC_KM, k != 0);
-        umma_commit(qd_empty(s));
         umma_commit(dq_full);
         if (more) {
           ok = mbar_wait(dq_drained, it & 1, &abort_flag, p.status, 0x2A);
@@ -529,7 +542,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     const uint32_t col_off = ch * 64;
     const float sl2 = p.scale * LOG2E;
     bool ok = true;
-    float* prev_dqrow = nullptr;  // where the dQ half-row of the previous iteration goes (null: out of range)
 
     auto drain_dq = [&](int it_done, bool release) -> bool {
       if (!mbar_wait(dq_full, it_done & 1, &abort_flag, p.status, 0x29)) return false;
@@ -543,16 +555,22 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         __syncwarp();
         if (lane == 0) mbar_arrive(dq_drained);
       }
-      if (prev_dqrow) {
+      // dK(it_done) and dQ(it_done) have completed, so nothing reads Q / dO of that block any more:
+      // their 64 KB become four 128 x 32 fp32 boxes (128-byte swizzled rows) for the TMA reduction.
+      const uint32_t stage = sQ(it_done & 1);
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc)
+      for (int cc = 0; cc < 2; ++cc) {
+        const uint32_t box = stage + (2 * ch + cc) * AT_HALF + r * 128;
 #pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            float4 v = make_float4(__uint_as_float(qv[cc][4 * g]), __uint_as_float(qv[cc][4 * g + 1]),
-                                   __uint_as_float(qv[cc][4 * g + 2]), __uint_as_float(qv[cc][4 * g + 3]));
-            atomicAdd(reinterpret_cast<float4*>(prev_dqrow + cc * 32 + g * 4), v);
-          }
+        for (int g = 0; g < 8; ++g) {
+          const uint32_t dst = box + ((static_cast<uint32_t>(g) ^ static_cast<uint32_t>(r & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(qv[cc][4 * g]),
+                       "r"(qv[cc][4 * g + 1]), "r"(qv[cc][4 * g + 2]), "r"(qv[cc][4 * g + 3]) : "memory");
+        }
       }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dq_staged(it_done & 1));
       return true;
     };
 
@@ -623,7 +641,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         ok = drain_dq(it - 1, true);
         if (!ok) break;
       }
-      prev_dqrow = row_ok ? p.dq_acc + (((long long)b * p.S + q_idx) * p.H + h) * 128 + col_off : nullptr;
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc)
         st_tile_row32(sP, r, 2 * ch + cc, *reinterpret_cast<const uint32_t(*)[16]>(&pkP[cc * 16]));
@@ -752,7 +769,11 @@ extern "C" int lb_attn_bwd(const LbAttnArgs* a, void* stream) {
   if (!a->delta || !a->dq_acc || !a->lse) return 4;
   if (a->B <= 0 || a->S <= 0) return 0;
   cudaStream_t st = (cudaStream_t)stream;
-  CUtensorMap tq, tk, tv, tdo;
+  CUtensorMap tq, tk, tv, tdo, tdq;
+  // dq_acc [B, S, H, 128] fp32, reduced into in boxes of 32 columns (one 128-byte swizzle row) x 128 rows
+  if (make_tmap_4d(&tdq, a->dq_acc, 4, 128, a->S, (long long)a->H * 128, a->H, 128, a->B, (long long)a->S * a->H * 128,
+                   32, 128))
+    return 14;
   if (make_qkv_map(&tq, a->q, a->B, a->S, a->H, a->q_sb, a->q_ss, a->q_sh)) return 10;
   if (make_qkv_map(&tk, a->k, a->B, a->S, a->Hkv, a->k_sb, a->k_ss, a->k_sh)) return 11;
   if (make_qkv_map(&tv, a->v, a->B, a->S, a->Hkv, a->v_sb, a->v_ss, a->v_sh)) return 12;
@@ -777,7 +798,7 @@ extern "C" int lb_attn_bwd(const LbAttnArgs* a, void* stream) {
     attr = true;
   }
   dim3 grid((a->S + 127) / 128, a->Hkv, a->B);
-  attn_bwd_kernel<<<grid, BWD_THREADS, BWD_SMEM, st>>>(tq, tk, tv, tdo, p);
+  attn_bwd_kernel<<<grid, BWD_THREADS, BWD_SMEM, st>>>(tq, tk, tv, tdo, tdq, p);
   long long total = rows * 16;
   int blocks = (int)((total + 255) / 256 < (long long)num_sms() * 8 ? (total + 255) / 256 : (long long)num_sms() * 8);
   attn_dq_store_kernel<<<blocks, 256, 0, st>>>(a->dq_acc, (__nv_bfloat16*)a->dq, a->B, a->S, a->H, a->q_sb, a->q_ss, a->q_sh);
