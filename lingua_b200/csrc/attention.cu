@@ -5,15 +5,15 @@
 // Replaces the SDPA / xformers / flex_attention calls of lingua/transformer.py:374-404 and
 // the mask builders of lingua/transformer.py:142-217.
 //
-// Forward, one CTA per (128-query block, head, batch): warp 0 streams K/V tiles with TMA
-// through a 2-stage ring, one thread of warp 1 issues S = Q K^T into one of two TMEM
-// buffers and O += P V, warps 2-5 (one thread per query row) run the online softmax on S
-// straight out of TMEM, write P as bf16 into a swizzled shared-memory tile for the second
-// MMA, and rescale the TMEM-resident O only when a row maximum grew by more than 2^8.
+// Forward, one CTA per (pair of 128-query blocks, head, batch): warp 0 streams K and V tiles
+// with TMA, one thread of warp 1 issues S = Q K^T and O += P V for both query tiles in turn, two
+// groups of four warps (one thread per query row) run the online softmax on S straight out of
+// TMEM, write P back into TMEM as the A operand of the second MMA, and rescale the TMEM-resident
+// O only when a row maximum grew by more than 2^8.
 //
 // Backward, one CTA per (128-key block, kv head, batch), looping over the query blocks that
 // can see it: S and dP are recomputed on the tensor cores, dV and dK accumulate in TMEM for
-// the whole loop, and dQ tiles are reduced into an fp32 scratch buffer with vector atomics.
+// the whole loop, and dQ tiles are added to an fp32 scratch buffer with TMA reductions.
 #include "common.cuh"
 #include "lingua_b200.h"
 
@@ -67,47 +67,69 @@ struct AttnParams {
 };
 
 // ============================================================================ forward
-constexpr int FWD_SMEM = AT_TILE /*Q*/ + 4 * AT_TILE /*K,V x 2 stages*/ + AT_TILE /*P*/ + 1024 + 256;
+// One CTA owns two consecutive 128-query tiles of one head and streams the K / V tiles both of
+// them need through a 2-stage ring (each K / V tile is fetched once for 256 queries). Each query
+// tile has its own S and O accumulators in tensor memory (4 x 128 columns); the eight softmax
+// warps handle the tiles alternately, and the MMA thread interleaves them the same way:
+//     ... O0 += P0 V(j) | S0 = Q0 K(j+1)^T | O1 += P1 V(j) | S1 = Q1 K(j+1)^T ...
+// so the tensor pipe works on one tile while the other tile's softmax runs. P never touches
+// shared memory: it is written as bf16 pairs over the first 64 columns of its S and read from
+// there as the A operand of the second MMA.
+constexpr int FWD_THREADS = 320;  // TMA warp, MMA warp, 8 softmax warps
+constexpr int FWD_SMEM = 6 * AT_TILE /*Q0, Q1, K x 2, V x 2*/ + 1024 + 256;
 
-__global__ void __launch_bounds__(AT_THREADS, 1)
+__global__ void __launch_bounds__(FWD_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                 const __grid_constant__ CUtensorMap tv, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ int abort_flag;
   __shared__ uint32_t tmem_slot;
+  __shared__ float xchg[2][128][2];  // row maximum / row sum halves exchanged between partner warps
   const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t sQ = sbase;
-  auto sK = [&](int s) { return sbase + AT_TILE + s * 2 * AT_TILE; };
-  auto sV = [&](int s) { return sbase + 2 * AT_TILE + s * 2 * AT_TILE; };
-  const uint32_t sP = sbase + 5 * AT_TILE;
+  auto sQ = [&](int t) { return sbase + t * AT_TILE; };
+  auto sK = [&](int s) { return sbase + 2 * AT_TILE + s * 2 * AT_TILE; };
+  auto sV = [&](int s) { return sbase + 3 * AT_TILE + s * 2 * AT_TILE; };
   const uint32_t bars = sbase + 6 * AT_TILE;
   const uint32_t q_full = bars;
   auto k_full = [&](int s) { return bars + 8 + 8 * s; };
   auto v_full = [&](int s) { return bars + 24 + 8 * s; };
   auto kv_empty = [&](int s) { return bars + 40 + 8 * s; };
-  auto s_full = [&](int s) { return bars + 56 + 8 * s; };
-  auto s_empty = [&](int s) { return bars + 72 + 8 * s; };
-  const uint32_t p_full = bars + 88;
-  const uint32_t o_done = bars + 96;
+  auto s_full = [&](int t) { return bars + 56 + 8 * t; };
+  auto p_full = [&](int t) { return bars + 72 + 8 * t; };
+  auto o_done = [&](int t) { return bars + 88 + 8 * t; };
+  auto pair_bar = [&](int q) { return bars + 104 + 8 * q; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nqb = (p.S + 127) / 128;
-  const int qb = nqb - 1 - blockIdx.x;  // longest rows first
+  const int npair = (nqb + 1) / 2;
+  const int pair = npair - 1 - blockIdx.x;  // longest rows first
   const int h = blockIdx.y, b = blockIdx.z;
   const int hk = h / (p.H / p.Hkv);
 
-  // kv block range [j0, j1]
-  const int row_first = qb * 128;
-  const int row_last = min(qb * 128 + 127, p.S - 1);
-  int lo_first = p.doc_start ? p.doc_start[(long long)b * p.S + row_first] : 0;
-  int lo_last = p.doc_start ? p.doc_start[(long long)b * p.S + row_last] : 0;
-  if (p.window > 0) {
-    lo_first = max(lo_first, row_first - p.window + 1);
-    lo_last = max(lo_last, row_last - p.window + 1);
-  }
-  const int j0 = lo_first / 128;
-  const int j1 = p.causal ? qb : nqb - 1;
-  const int n = j1 - j0 + 1;
+  // kv block range [j0, j1] of each query tile; a tile past the end of the sequence has none
+  auto tile_range = [&](int qb, int& j0, int& j1, int& lo_last_out) {
+    j0 = 1; j1 = 0; lo_last_out = 0;
+    if (qb >= nqb) return;
+    const int row_first = qb * 128;
+    const int row_last = min(qb * 128 + 127, p.S - 1);
+    int lo_first = p.doc_start ? p.doc_start[(long long)b * p.S + row_first] : 0;
+    int lo_last = p.doc_start ? p.doc_start[(long long)b * p.S + row_last] : 0;
+    if (p.window > 0) {
+      lo_first = max(lo_first, row_first - p.window + 1);
+      lo_last = max(lo_last, row_last - p.window + 1);
+    }
+    j0 = lo_first / 128;
+    j1 = p.causal ? qb : nqb - 1;
+    lo_last_out = lo_last;
+  };
+  int a_j0, a_j1, a_lo, b_j0, b_j1, b_lo;
+  tile_range(2 * pair, a_j0, a_j1, a_lo);
+  tile_range(2 * pair + 1, b_j0, b_j1, b_lo);
+  const bool two = b_j1 >= b_j0;
+  const int jlo = two ? min(a_j0, b_j0) : a_j0;
+  const int jhi = two ? max(a_j1, b_j1) : a_j1;
+  const int n = jhi - jlo + 1;
+  auto active = [&](int t, int j) { return t ? (j >= b_j0 && j <= b_j1) : (j >= a_j0 && j <= a_j1); };
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -117,10 +139,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       mbar_init(v_full(s), 1);
       mbar_init(kv_empty(s), 1);
       mbar_init(s_full(s), 1);
-      mbar_init(s_empty(s), 4);
+      mbar_init(p_full(s), 8);
+      mbar_init(o_done(s), 1);
     }
-    mbar_init(p_full, 4);
-    mbar_init(o_done, 1);
+    for (int q = 0; q < 4; ++q) mbar_init(pair_bar(q), 64);
     fence_mbar_init();
     tma_prefetch_desc(&tq);
     tma_prefetch_desc(&tk);
@@ -134,15 +156,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
-  const uint32_t tS0 = tmem, tO = tmem + 256;
+  auto tS = [&](int t) { return tmem + t * 128; };
+  auto tO = [&](int t) { return tmem + 256 + t * 128; };
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_arrive_expect_tx(q_full, AT_TILE);
-      tma_load_4d(sQ, &tq, q_full, 0, row_first, h, b);
-      tma_load_4d(sQ + AT_HALF, &tq, q_full, 64, row_first, h, b);
+      mbar_arrive_expect_tx(q_full, two ? 2 * AT_TILE : AT_TILE);
+      for (int t = 0; t < (two ? 2 : 1); ++t) {
+        tma_load_4d(sQ(t), &tq, q_full, 0, (2 * pair + t) * 128, h, b);
+        tma_load_4d(sQ(t) + AT_HALF, &tq, q_full, 64, (2 * pair + t) * 128, h, b);
+      }
       for (int it = 0; it < n; ++it) {
-        const int s = it & 1, kv0 = (j0 + it) * 128;
+        const int s = it & 1, kv0 = (jlo + it) * 128;
         if (!mbar_wait(kv_empty(s), ((it >> 1) & 1) ^ 1, &abort_flag, p.status, 0x11)) break;
         mbar_arrive_expect_tx(k_full(s), AT_TILE);
         tma_load_4d(sK(s), &tk, k_full(s), 0, kv0, hk, b);
@@ -154,72 +179,126 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      bool ok = mbar_wait(q_full, 0, &abort_flag, p.status, 0x12) &&
+      // MMAs of one thread run in issue order: S_t(j+1) overwrites P_t(j) only after O_t += P_t V(j)
+      // has read it, and a commit after S_t(j+1) also covers that product.
+      auto issue_s = [&](int t, int s) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_f16(tS(t), desc_k(sQ(t), k), desc_k(sK(s), k), IDESC_KK, k != 0);
+        umma_commit(s_full(t));
+      };
+      uint32_t n_pv0 = 0, n_pv1 = 0;
+      auto issue_pv = [&](int t, int s, int j) -> bool {
+        uint32_t& cnt = t ? n_pv1 : n_pv0;
+        if (!mbar_wait(p_full(t), cnt & 1, &abort_flag, p.status, 0x17)) return false;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_f16_ts(tO(t), tS(t) + k * 8, desc_mn(sV(s), k), IDESC_KM, (cnt | k) != 0);
+        ++cnt;
+        if (j == (t ? b_j1 : a_j1)) umma_commit(o_done(t));
+        return true;
+      };
+      bool ok = n > 0 && mbar_wait(q_full, 0, &abort_flag, p.status, 0x12) &&
                 mbar_wait(k_full(0), 0, &abort_flag, p.status, 0x13);
       if (ok) {
         tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < 8; ++k) umma_f16(tS0, desc_k(sQ, k), desc_k(sK(0), k), IDESC_KK, k != 0);
-        umma_commit(s_full(0));
+        if (active(0, jlo)) issue_s(0, 0);
+        if (active(1, jlo)) issue_s(1, 0);
       }
       for (int it = 0; ok && it < n; ++it) {
-        if (it + 1 < n) {
-          const int b1 = (it + 1) & 1;
-          const uint32_t ph = ((it + 1) >> 1) & 1;
-          ok = mbar_wait(k_full(b1), ph, &abort_flag, p.status, 0x14) &&
-               mbar_wait(s_empty(b1), ph ^ 1, &abort_flag, p.status, 0x15);
+        const int j = jlo + it, s = it & 1, s1 = s ^ 1;
+        const bool more = it + 1 < n;
+        const uint32_t ph = (it >> 1) & 1, ph1 = ((it + 1) >> 1) & 1;
+        bool k_ready = false;
+        if (active(0, j) || active(1, j)) {
+          ok = mbar_wait(v_full(s), ph, &abort_flag, p.status, 0x16);
           if (!ok) break;
-          tc_fence_after();
-#pragma unroll
-          for (int k = 0; k < 8; ++k)
-            umma_f16(tS0 + b1 * 128, desc_k(sQ, k), desc_k(sK(b1), k), IDESC_KK, k != 0);
-          umma_commit(s_full(b1));
         }
-        const int s = it & 1;
-        ok = mbar_wait(v_full(s), (it >> 1) & 1, &abort_flag, p.status, 0x16) &&
-             mbar_wait(p_full, it & 1, &abort_flag, p.status, 0x17);
-        if (!ok) break;
-        tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < 8; ++k)
-          umma_f16(tO, desc_k(sP, k), desc_mn(sV(s), k), IDESC_KM, (it | k) != 0);
+        if (active(0, j)) {
+          ok = issue_pv(0, s, j);
+          if (!ok) break;
+        }
+        if (more && active(0, j + 1)) {
+          ok = mbar_wait(k_full(s1), ph1, &abort_flag, p.status, 0x14);
+          if (!ok) break;
+          k_ready = true;
+          tc_fence_after();
+          issue_s(0, s1);
+        }
+        if (active(1, j)) {
+          ok = issue_pv(1, s, j);
+          if (!ok) break;
+        }
         umma_commit(kv_empty(s));
-        umma_commit(o_done);
+        if (more && active(1, j + 1)) {
+          if (!k_ready) {
+            ok = mbar_wait(k_full(s1), ph1, &abort_flag, p.status, 0x15);
+            if (!ok) break;
+            tc_fence_after();
+          }
+          issue_s(1, s1);
+        }
       }
     }
   } else {
     // ---------------------------------------------------------------- softmax warps
+    // All eight warps work on one query tile at a time, in the order the MMA thread issues the
+    // S products (S0(j), S1(j), S0(j+1), ...). Two warps share each quarter of the TMEM lanes:
+    // both own the same 32 query rows and `ch` selects which 64 of the 128 key columns a thread
+    // handles, so one softmax step is half as long as with one thread per row; the tensor pipe
+    // meanwhile runs the other tile's products.
     const int quarter = warp & 3;
+    const int ch = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;
-    const int q_idx = qb * 128 + r;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     const float sl2 = p.scale * LOG2E;
-    int lo = 0;
-    if (p.doc_start) lo = p.doc_start[(long long)b * p.S + min(q_idx, p.S - 1)];
-    if (p.window > 0) lo = max(lo, q_idx - p.window + 1);
-    const int hi = p.causal ? min(q_idx, p.S - 1) : p.S - 1;  // last visible key
-    float m_used = -INFINITY, l = 0.f;
+    // partner warps meet on an mbarrier (64 arrivals) so that this wait is bounded like every other
+    uint32_t xph = 0;
+    auto pair_sync = [&]() -> bool {
+      mbar_arrive(pair_bar(quarter));
+      const bool got = mbar_wait(pair_bar(quarter), xph, &abort_flag, p.status, 0x1C);
+      xph ^= 1u;
+      return got;
+    };
+    int lo0 = 0, lo1 = 0;
+    {
+      const int q0 = 2 * pair * 128 + r, q1 = q0 + 128;
+      if (p.doc_start) {
+        lo0 = p.doc_start[(long long)b * p.S + min(q0, p.S - 1)];
+        lo1 = p.doc_start[(long long)b * p.S + min(q1, p.S - 1)];
+      }
+      if (p.window > 0) {
+        lo0 = max(lo0, q0 - p.window + 1);
+        lo1 = max(lo1, q1 - p.window + 1);
+      }
+    }
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    uint32_t cnt0 = 0, cnt1 = 0;
     bool ok = true;
-    for (int it = 0; it < n; ++it) {
-      const int j = j0 + it, buf = it & 1;
-      const int kv0 = j * 128;
-      ok = mbar_wait(s_full(buf), (it >> 1) & 1, &abort_flag, p.status, 0x18);
+    for (int step = 0; step < 2 * n && ok; ++step) {
+      const int t = step & 1, j = jlo + (step >> 1);
+      if (!active(t, j)) continue;
+      const int qb = 2 * pair + t;
+      const int q_idx = qb * 128 + r;
+      const int lo = t ? lo1 : lo0;
+      const int hi = p.causal ? min(q_idx, p.S - 1) : p.S - 1;  // last visible key
+      const int lo_last = t ? b_lo : a_lo;
+      const uint32_t cnt = t ? cnt1 : cnt0;
+      float m_used = t ? m1 : m0, l = t ? l1 : l0;
+      const int kv0 = j * 128 + ch * 64;
+      // s_full was committed after O += P V of this tile's previous step was issued: O is quiescent
+      ok = mbar_wait(s_full(t), cnt & 1, &abort_flag, p.status, 0x18);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t tS = tS0 + buf * 128 + lane_off;
-      const bool need_mask = (p.causal && j == qb) || (kv0 < lo_last) || (kv0 + 128 > p.S);
-      // all 128 scores of this row in registers: one TMEM round trip, then the buffer is free
-      uint32_t sv[4][32];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, sv[c]);
+      const bool need_mask = (p.causal && j == qb) || (j * 128 < lo_last) || (j * 128 + 128 > p.S);
+      const uint32_t tSt = tS(t) + lane_off, tOt = tO(t) + lane_off + ch * 64;
+      uint32_t sv[2][32];
+      tmem_ld32(tSt + ch * 64, sv[0]);
+      tmem_ld32(tSt + ch * 64 + 32, sv[1]);
       tmem_wait_ld();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(s_empty(buf));
       float mx = -INFINITY;
       if (need_mask) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
             const int kv = kv0 + c * 32 + e;
@@ -228,64 +307,96 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
           }
       } else {
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(sv[c][e]));
       }
-      mx *= sl2;
+      // the other half of the row lives in the partner warp; this barrier also orders its TMEM
+      // reads of S before this warp's P stores into the same columns
+      xchg[t][r][ch] = mx;
+      ok = pair_sync();
+      if (!ok) break;
+      mx = fmaxf(mx, xchg[t][r][ch ^ 1]) * sl2;
       const float m_new = fmaxf(m_used, mx);
-      if (it == 0) {
+      if (cnt == 0) {
         m_used = m_new;
       } else {
         const bool need = m_new > m_used + 8.f;
-        // P's buffer and O are both free once the previous P V product has completed.
-        ok = mbar_wait(o_done, (it - 1) & 1, &abort_flag, p.status, 0x19);
-        if (!ok) break;
         if (__any_sync(0xFFFFFFFFu, need)) {
-          tc_fence_after();
           const float f = need ? exp2f(m_used - m_new) : 1.f;
 #pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < 2; ++c) {
             uint32_t rr[32];
-            tmem_ld32(tO + lane_off + c * 32, rr);
+            tmem_ld32(tOt + c * 32, rr);
             tmem_wait_ld();
 #pragma unroll
             for (int e = 0; e < 32; ++e) rr[e] = __float_as_uint(__uint_as_float(rr[e]) * f);
-            tmem_st32(tO + lane_off + c * 32, rr);
+            tmem_st32(tOt + c * 32, rr);
           }
-          tmem_wait_st();
           l *= f;
           if (need) m_used = m_new;
         }
       }
       const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
+      // P = exp2(S * scale - m): this thread's 64 scores -> 32 packed columns [32 ch, 32 ch + 32)
+      uint32_t pk[32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t pk[16];
+      for (int c = 0; c < 2; ++c) {
+        if (need_mask) {
 #pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          // masked scores are -inf and give exactly 0
-          const float p0 = exp2f(__uint_as_float(sv[c][e]) * sl2 - m_eff);
-          const float p1 = exp2f(__uint_as_float(sv[c][e + 1]) * sl2 - m_eff);
-          l += p0 + p1;
-          pk[e >> 1] = pack_bf16(p0, p1);
+          for (int e = 0; e < 32; e += 2) {
+            // masked scores are -inf and give exactly 0
+            const float p0 = exp2f(__uint_as_float(sv[c][e]) * sl2 - m_eff);
+            const float p1 = exp2f(__uint_as_float(sv[c][e + 1]) * sl2 - m_eff);
+            l += p0 + p1;
+            pk[c * 16 + (e >> 1)] = pack_bf16(p0, p1);
+          }
+        } else {
+          // every fourth exponential runs on the FMA pipe so that the MUFU unit is not the limit
+#pragma unroll
+          for (int e = 0; e < 32; e += 4) {
+            const float p0 = exp2f(__uint_as_float(sv[c][e]) * sl2 - m_eff);
+            const float p1 = exp2f(__uint_as_float(sv[c][e + 1]) * sl2 - m_eff);
+            const float p2 = exp2f(__uint_as_float(sv[c][e + 2]) * sl2 - m_eff);
+            const float p3 = exp2_poly(__uint_as_float(sv[c][e + 3]) * sl2 - m_eff);
+            l += (p0 + p1) + (p2 + p3);
+            pk[c * 16 + (e >> 1)] = pack_bf16(p0, p1);
+            pk[c * 16 + (e >> 1) + 1] = pack_bf16(p2, p3);
+          }
         }
-        st_tile_row32(sP, r, c, pk);
       }
-      fence_proxy_async_smem();
+      tmem_st32(tSt + ch * 32, pk);
+      tmem_wait_st();
+      tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
+      if (lane == 0) mbar_arrive(p_full(t));
+      if (t) { m1 = m_used; l1 = l; cnt1 = cnt + 1; } else { m0 = m_used; l0 = l; cnt0 = cnt + 1; }
     }
-    if (ok && n > 0) ok = mbar_wait(o_done, (n - 1) & 1, &abort_flag, p.status, 0x1A);
-    if (ok) {
-      tc_fence_after();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* orow = p.O + (((long long)b * p.S + q_idx) * p.H + h) * 128;
+    // epilogue: each thread normalises and stores 64 of the 128 output columns of its row
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+    for (int t = 0; t < 2 && ok; ++t) {
+      const int qb = 2 * pair + t;
+      if (qb >= nqb) break;
+      const int q_idx = qb * 128 + r;
+      const uint32_t cnt = t ? cnt1 : cnt0;
+      const float m_used = t ? m1 : m0;
+      float l = t ? l1 : l0;
+      if (cnt > 0) {
+        ok = mbar_wait(o_done(t), 0, &abort_flag, p.status, 0x1A);
+        if (!ok) break;
+      }
+      tc_fence_after();
+      xchg[t][r][ch] = l;
+      ok = pair_sync();
+      if (!ok) break;
+      l += xchg[t][r][ch ^ 1];
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* orow = p.O + (((long long)b * p.S + q_idx) * p.H + h) * 128 + ch * 64;
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
         uint32_t rr[32];
-        if (n > 0) {
-          tmem_ld32(tO + lane_off + c * 32, rr);
+        if (cnt > 0) {
+          tmem_ld32(tO(t) + lane_off + ch * 64 + c * 32, rr);
           tmem_wait_ld();
         } else {
 #pragma unroll
@@ -303,7 +414,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
           }
         }
       }
-      if (q_idx < p.S && p.lse) {
+      if (ch == 0 && q_idx < p.S && p.lse) {
         const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
         p.lse[((long long)b * p.H + h) * p.S + q_idx] = l > 0.f ? (m_eff + log2f(l)) * LN2 : INFINITY;
       }
@@ -754,8 +865,8 @@ extern "C" int lb_attn_fwd(const LbAttnArgs* a, void* stream) {
       return 20;
     attr = true;
   }
-  dim3 grid((a->S + 127) / 128, a->H, a->B);
-  attn_fwd_kernel<<<grid, AT_THREADS, FWD_SMEM, (cudaStream_t)stream>>>(tq, tk, tv, p);
+  dim3 grid(((a->S + 127) / 128 + 1) / 2, a->H, a->B);
+  attn_fwd_kernel<<<grid, FWD_THREADS, FWD_SMEM, (cudaStream_t)stream>>>(tq, tk, tv, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;
