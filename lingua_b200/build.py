@@ -27,6 +27,7 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC",
     "--expt-relaxed-constexpr",
     "-Xptxas", "-v",
+    *os.environ.get("LB_EXTRA_NVCC_FLAGS", "").split(),  # e.g. -DLB_ATTN_TRACE for the timing trace of attention.cu
 ]
 
 

@@ -51,6 +51,16 @@ __device__ __forceinline__ void st_tile_row32(uint32_t tile, int r, int c, const
   }
 }
 
+// Optional timing trace (compile with -DLB_ATTN_TRACE): CTA (0,0,0) of the forward kernel records
+// clock64() at fixed points of its softmax and MMA loops; lb_attn_trace_read copies them out.
+#ifdef LB_ATTN_TRACE
+__device__ long long g_attn_trace[4096];
+#define LB_TRACE(slot) \
+  do { if (trace_on) g_attn_trace[(slot) & 4095] = clock64(); } while (0)
+#else
+#define LB_TRACE(slot) do { } while (0)
+#endif
+
 struct AttnParams {
   int B, S, H, Hkv;
   int causal, window;
@@ -100,6 +110,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   auto pair_bar = [&](int q) { return bars + 104 + 8 * q; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef LB_ATTN_TRACE
+  const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x == 32 || threadIdx.x == 64);
+#endif
   const int nqb = (p.S + 127) / 128;
   const int npair = (nqb + 1) / 2;
   const int pair = npair - 1 - blockIdx.x;  // longest rows first
@@ -213,21 +226,26 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
           ok = mbar_wait(v_full(s), ph, &abort_flag, p.status, 0x16);
           if (!ok) break;
         }
+        LB_TRACE(2048 + it * 8 + 0);
         if (active(0, j)) {
           ok = issue_pv(0, s, j);
           if (!ok) break;
         }
+        LB_TRACE(2048 + it * 8 + 1);
         if (more && active(0, j + 1)) {
           ok = mbar_wait(k_full(s1), ph1, &abort_flag, p.status, 0x14);
           if (!ok) break;
           k_ready = true;
           tc_fence_after();
+          LB_TRACE(2048 + it * 8 + 2);
           issue_s(0, s1);
         }
+        LB_TRACE(2048 + it * 8 + 3);
         if (active(1, j)) {
           ok = issue_pv(1, s, j);
           if (!ok) break;
         }
+        LB_TRACE(2048 + it * 8 + 4);
         umma_commit(kv_empty(s));
         if (more && active(1, j + 1)) {
           if (!k_ready) {
@@ -237,6 +255,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
           }
           issue_s(1, s1);
         }
+        LB_TRACE(2048 + it * 8 + 5);
       }
     }
   } else {
@@ -286,15 +305,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       float m_used = t ? m1 : m0, l = t ? l1 : l0;
       const int kv0 = j * 128 + ch * 64;
       // s_full was committed after O += P V of this tile's previous step was issued: O is quiescent
+      LB_TRACE(step * 8 + 0);
       ok = mbar_wait(s_full(t), cnt & 1, &abort_flag, p.status, 0x18);
       if (!ok) break;
       tc_fence_after();
+      LB_TRACE(step * 8 + 1);
       const bool need_mask = (p.causal && j == qb) || (j * 128 < lo_last) || (j * 128 + 128 > p.S);
       const uint32_t tSt = tS(t) + lane_off, tOt = tO(t) + lane_off + ch * 64;
       uint32_t sv[2][32];
       tmem_ld32(tSt + ch * 64, sv[0]);
       tmem_ld32(tSt + ch * 64 + 32, sv[1]);
       tmem_wait_ld();
+      LB_TRACE(step * 8 + 2);
       float mx = -INFINITY;
       if (need_mask) {
 #pragma unroll
@@ -306,16 +328,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
             mx = fmaxf(mx, __uint_as_float(sv[c][e]));
           }
       } else {
+        // four independent chains instead of one serial one
+        float mxa[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
         for (int c = 0; c < 2; ++c)
 #pragma unroll
-          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(sv[c][e]));
+          for (int e = 0; e < 32; e += 2)
+            mxa[(e >> 1) & 3] = fmax3(mxa[(e >> 1) & 3], __uint_as_float(sv[c][e]), __uint_as_float(sv[c][e + 1]));
+        mx = fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3]));
       }
       // the other half of the row lives in the partner warp; this barrier also orders its TMEM
       // reads of S before this warp's P stores into the same columns
       xchg[t][r][ch] = mx;
       ok = pair_sync();
       if (!ok) break;
+      LB_TRACE(step * 8 + 3);
       mx = fmaxf(mx, xchg[t][r][ch ^ 1]) * sl2;
       const float m_new = fmaxf(m_used, mx);
       if (cnt == 0) {
@@ -352,24 +379,42 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
             pk[c * 16 + (e >> 1)] = pack_bf16(p0, p1);
           }
         } else {
-          // every fourth exponential runs on the FMA pipe so that the MUFU unit is not the limit
+          // packed fp32 pairs for the scale / subtract and the row sum; two of every eight
+          // exponentials run on the FMA pipe so that the MUFU unit is not the limit
+          const uint64_t sl2_2 = pack_f2(sl2, sl2), negm2 = pack_f2(-m_eff, -m_eff);
+          uint64_t ls2 = 0ull;
 #pragma unroll
-          for (int e = 0; e < 32; e += 4) {
-            const float p0 = exp2f(__uint_as_float(sv[c][e]) * sl2 - m_eff);
-            const float p1 = exp2f(__uint_as_float(sv[c][e + 1]) * sl2 - m_eff);
-            const float p2 = exp2f(__uint_as_float(sv[c][e + 2]) * sl2 - m_eff);
-            const float p3 = exp2_poly(__uint_as_float(sv[c][e + 3]) * sl2 - m_eff);
-            l += (p0 + p1) + (p2 + p3);
+          for (int e = 0; e < 32; e += 8) {
+            const uint64_t x01 = ffma2(pack_u2(sv[c][e], sv[c][e + 1]), sl2_2, negm2);
+            const uint64_t x23 = ffma2(pack_u2(sv[c][e + 2], sv[c][e + 3]), sl2_2, negm2);
+            const uint64_t x45 = ffma2(pack_u2(sv[c][e + 4], sv[c][e + 5]), sl2_2, negm2);
+            const uint64_t x67 = ffma2(pack_u2(sv[c][e + 6], sv[c][e + 7]), sl2_2, negm2);
+            float a0, a1, a2, a3, a4, a5, q6, q7;
+            unpack_f2(x01, a0, a1);
+            unpack_f2(x23, a2, a3);
+            unpack_f2(x45, a4, a5);
+            const float p0 = exp2f(a0), p1 = exp2f(a1), p2 = exp2f(a2), p3 = exp2f(a3), p4 = exp2f(a4), p5 = exp2f(a5);
+            const uint64_t p67 = exp2_poly2(x67);
+            unpack_f2(p67, q6, q7);
+            ls2 = fadd2(ls2, fadd2(fadd2(pack_f2(p0, p1), pack_f2(p2, p3)), fadd2(pack_f2(p4, p5), p67)));
             pk[c * 16 + (e >> 1)] = pack_bf16(p0, p1);
             pk[c * 16 + (e >> 1) + 1] = pack_bf16(p2, p3);
+            pk[c * 16 + (e >> 1) + 2] = pack_bf16(p4, p5);
+            pk[c * 16 + (e >> 1) + 3] = pack_bf16(q6, q7);
           }
+          float s0, s1;
+          unpack_f2(ls2, s0, s1);
+          l += s0 + s1;
         }
       }
+      LB_TRACE(step * 8 + 4);
       tmem_st32(tSt + ch * 32, pk);
       tmem_wait_st();
+      LB_TRACE(step * 8 + 5);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full(t));
+      LB_TRACE(step * 8 + 6);
       if (t) { m1 = m_used; l1 = l; cnt1 = cnt + 1; } else { m0 = m_used; l0 = l; cnt0 = cnt + 1; }
     }
     // epilogue: each thread normalises and stores 64 of the 128 output columns of its row
@@ -951,3 +996,10 @@ extern "C" int lb_attn_bwd_noalloc(const LbAttnArgs* a, void* stream) {
   b.delta = g_attn_bwd_scratch_addr[dev] + NOALLOC_MAX_ROWS * 128;
   return lb_attn_bwd(&b, stream);  // clears dq_acc with a memset on `stream`, then launches
 }
+
+#ifdef LB_ATTN_TRACE
+extern "C" int lb_attn_trace_read(long long* host, int n) {
+  if (n > 4096) n = 4096;
+  return (int)cudaMemcpyFromSymbol(host, lb::g_attn_trace, sizeof(long long) * n);
+}
+#endif

@@ -282,9 +282,65 @@ __device__ __forceinline__ float exp2_poly(float x) {
   p = fmaf(p, f, 0.99992894f);
   return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
 }
+// Packed fp32 pairs (sm_100 executes fma / add / mul on two fp32 lanes of a 64-bit register in
+// one instruction) and the three-input maximum.
+__device__ __forceinline__ uint64_t pack_f2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ uint64_t pack_u2(uint32_t lo, uint32_t hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ void unpack_u2(uint64_t v, uint32_t& lo, uint32_t& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t fadd2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+// exp2_poly on a pair.
+__device__ __forceinline__ uint64_t exp2_poly2(uint64_t x2) {
+  float x0, x1;
+  unpack_f2(x2, x0, x1);
+  x2 = pack_f2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
+  const uint64_t magic = pack_f2(12582912.f, 12582912.f), nmagic = pack_f2(-12582912.f, -12582912.f);
+  const uint64_t t = fadd2(x2, magic);
+  const uint64_t fl = fadd2(t, nmagic);
+  const uint64_t f = ffma2(fl, pack_f2(-1.f, -1.f), x2);
+  uint64_t p = ffma2(f, pack_f2(0.05508868f, 0.05508868f), pack_f2(0.24260405f, 0.24260405f));
+  p = ffma2(p, f, pack_f2(0.69327624f, 0.69327624f));
+  p = ffma2(p, f, pack_f2(0.99992894f, 0.99992894f));
+  uint32_t p0, p1, t0, t1;
+  unpack_u2(p, p0, p1);
+  unpack_u2(t, t0, t1);
+  return pack_u2(p0 + (t0 << 23), p1 + (t1 << 23));
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
+}
+// Same result up to the tie rule (half away from zero instead of half to even), but on the
+// integer pipe: the float -> bf16 conversion instruction shares the MUFU's issue port, which is
+// the scarce unit in the softmax loops.
+__device__ __forceinline__ uint32_t pack_bf16_alu(float lo, float hi) {
+  return __byte_perm(__float_as_uint(lo) + 0x8000u, __float_as_uint(hi) + 0x8000u, 0x7632);
 }
 
 }  // namespace lb
