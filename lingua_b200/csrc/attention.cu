@@ -545,11 +545,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   const uint32_t bars = sbase + 7 * AT_TILE;
   const uint32_t kv_full = bars;
   auto qd_full = [&](int s) { return bars + 8 + 8 * s; };
-  auto dq_staged = [&](int s) { return bars + 24 + 8 * s; };
+  auto dq_staged = [&](int s, int half) { return bars + 120 + 16 * s + 8 * half; };  // half 0: over Q, 1: over dO
   const uint32_t s_full = bars + 40, p_full = bars + 48, dv_done = bars + 56, ds_full = bars + 64;
   const uint32_t dq_full = bars + 72, dq_drained = bars + 80, dp_full = bars + 88, s_free = bars + 96;
+  auto do_full = [&](int s) { return bars + 104 + 8 * s; };  // dO of a stage lands separately from Q
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef LB_ATTN_TRACE
+  const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x == 0 || threadIdx.x == 32 || threadIdx.x == 64);
+#endif
   const int nqb = (p.S + 127) / 128;
   const int jb = blockIdx.x;  // kv block
   const int hk = blockIdx.y, b = blockIdx.z;
@@ -570,7 +574,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     mbar_init(kv_full, 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(qd_full(s), 1);
-      mbar_init(dq_staged(s), 8);
+      mbar_init(do_full(s), 1);
+      mbar_init(dq_staged(s, 0), 4);
+      mbar_init(dq_staged(s, 1), 4);
     }
     mbar_init(s_full, 1);
     mbar_init(p_full, 8);
@@ -610,22 +616,35 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         const int s = it & 1;
         if (it >= 2) {
           const int j = it - 2;
-          if (!mbar_wait(dq_staged(s), (j >> 1) & 1, &abort_flag, p.status, 0x21)) break;
+          // dQ of block j: columns [0,64) were spilled over Q's tile, [64,128) over dO's. Each half is
+          // reduced as soon as it is there; the Q tile can be reloaded once the first half has been read.
+          LB_TRACE(3072 + it * 4 + 0);
           const int hj = hk * group + j / nq;
           const int qj = (i0 + j % nq) * 128;
-#pragma unroll
-          for (int cb = 0; cb < 4; ++cb) tma_reduce_add_4d(&tdq, sQ(s) + cb * AT_HALF, cb * 32, qj, hj, b);
+          if (!mbar_wait(dq_staged(s, 0), (j >> 1) & 1, &abort_flag, p.status, 0x21)) break;
+          tma_reduce_add_4d(&tdq, sQ(s), 0, qj, hj, b);
+          tma_reduce_add_4d(&tdq, sQ(s) + AT_HALF, 32, qj, hj, b);
           tma_store_commit();
-          tma_store_wait_read<0>();
+          LB_TRACE(3072 + it * 4 + 1);
+          if (!mbar_wait(dq_staged(s, 1), (j >> 1) & 1, &abort_flag, p.status, 0x2D)) break;
+          tma_reduce_add_4d(&tdq, sdO(s), 64, qj, hj, b);
+          tma_reduce_add_4d(&tdq, sdO(s) + AT_HALF, 96, qj, hj, b);
+          tma_store_commit();
+          LB_TRACE(3072 + it * 4 + 2);
+          tma_store_wait_read<1>();
+          LB_TRACE(3072 + it * 4 + 3);
         }
         if (it >= n) continue;
         const int h = hk * group + it / nq;
         const int q0 = (i0 + it % nq) * 128;
-        mbar_arrive_expect_tx(qd_full(s), 2 * AT_TILE);
+        // Q first: S of the next block only needs Q, dO is needed later (dP, dV)
+        mbar_arrive_expect_tx(qd_full(s), AT_TILE);
         tma_load_4d(sQ(s), &tq, qd_full(s), 0, q0, h, b);
         tma_load_4d(sQ(s) + AT_HALF, &tq, qd_full(s), 64, q0, h, b);
-        tma_load_4d(sdO(s), &tdo, qd_full(s), 0, q0, h, b);
-        tma_load_4d(sdO(s) + AT_HALF, &tdo, qd_full(s), 64, q0, h, b);
+        if (it >= 2) tma_store_wait_read<0>();
+        mbar_arrive_expect_tx(do_full(s), AT_TILE);
+        tma_load_4d(sdO(s), &tdo, do_full(s), 0, q0, h, b);
+        tma_load_4d(sdO(s) + AT_HALF, &tdo, do_full(s), 64, q0, h, b);
       }
       tma_store_wait<0>();
     }
@@ -644,47 +663,61 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
 #pragma unroll
           for (int k = 0; k < 8; ++k) umma_f16(tS, desc_k(sQ(0), k), desc_k(sK, k), IDESC_KK, k != 0);
           umma_commit(s_full);
+          ok = mbar_wait(do_full(0), 0, &abort_flag, p.status, 0x2C);
+          if (ok) {
+            tc_fence_after();
 #pragma unroll
-          for (int k = 0; k < 8; ++k) umma_f16(tdP, desc_k(sdO(0), k), desc_k(sV, k), IDESC_KK, k != 0);
-          umma_commit(dp_full);
+            for (int k = 0; k < 8; ++k) umma_f16(tdP, desc_k(sdO(0), k), desc_k(sV, k), IDESC_KK, k != 0);
+            umma_commit(dp_full);
+          }
         }
       }
       for (int it = 0; ok && it < n; ++it) {
         const int s = it & 1, s1 = s ^ 1;
         const bool more = it + 1 < n;
+        LB_TRACE(2048 + it * 16 + 0);
         ok = mbar_wait(p_full, it & 1, &abort_flag, p.status, 0x25);
         if (!ok) break;
         tc_fence_after();
+        LB_TRACE(2048 + it * 16 + 1);
         // dV[kv, d] += P^T dO : both operands read with one 128-byte row per query
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma_f16(tdV, desc_mn(sP, k), desc_mn(sdO(s), k), IDESC_MM, (it | k) != 0);
         umma_commit(dv_done);
+        LB_TRACE(2048 + it * 16 + 2);
         if (more) {
           ok = mbar_wait(qd_full(s1), ((it + 1) >> 1) & 1, &abort_flag, p.status, 0x23) &&
                mbar_wait(s_free, it & 1, &abort_flag, p.status, 0x24);
           if (!ok) break;
           tc_fence_after();
+          LB_TRACE(2048 + it * 16 + 3);
 #pragma unroll
           for (int k = 0; k < 8; ++k) umma_f16(tS, desc_k(sQ(s1), k), desc_k(sK, k), IDESC_KK, k != 0);
           umma_commit(s_full);
         }
+        LB_TRACE(2048 + it * 16 + 4);
         ok = mbar_wait(ds_full, it & 1, &abort_flag, p.status, 0x26);
         if (!ok) break;
         tc_fence_after();
+        LB_TRACE(2048 + it * 16 + 5);
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma_f16(tdK, desc_mn(sP, k), desc_mn(sQ(s), k), IDESC_MM, (it | k) != 0);
         // dQ[q, d] = dS K, into the columns that held dP
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma_f16(tdP, desc_k(sP, k), desc_mn(sK, k), IDESC_KM, k != 0);
         umma_commit(dq_full);
+        LB_TRACE(2048 + it * 16 + 6);
         if (more) {
-          ok = mbar_wait(dq_drained, it & 1, &abort_flag, p.status, 0x2A);
+          ok = mbar_wait(dq_drained, it & 1, &abort_flag, p.status, 0x2A) &&
+               mbar_wait(do_full(s1), ((it + 1) >> 1) & 1, &abort_flag, p.status, 0x2C);
           if (!ok) break;
           tc_fence_after();
+          LB_TRACE(2048 + it * 16 + 7);
 #pragma unroll
           for (int k = 0; k < 8; ++k) umma_f16(tdP, desc_k(sdO(s1), k), desc_k(sV, k), IDESC_KK, k != 0);
           umma_commit(dp_full);
         }
+        LB_TRACE(2048 + it * 16 + 8);
       }
     }
   } else {
@@ -726,7 +759,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       }
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(dq_staged(it_done & 1));
+      if (lane == 0) mbar_arrive(dq_staged(it_done & 1, ch));
       return true;
     };
 
@@ -763,9 +796,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       }
       const bool need_mask = (p.causal && ib == jb) || (kv0 < lo_blk) || (kv0 + 128 > p.S) || (ib * 128 + 128 > p.S);
 
+      LB_TRACE(it * 16 + 0);
       ok = mbar_wait(s_full, it & 1, &abort_flag, p.status, 0x27);
       if (!ok) break;
       tc_fence_after();
+      LB_TRACE(it * 16 + 1);
       // P = exp(S - lse), packed to bf16 in registers; S's TMEM columns are released right away
       uint32_t pkP[32];
       {
@@ -776,57 +811,89 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(s_free);
+        LB_TRACE(it * 16 + 2);
+        if (need_mask) {
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
+          for (int cc = 0; cc < 2; ++cc) {
 #pragma unroll
-          for (int e = 0; e < 32; e += 2) {
-            float p0 = exp2f(__uint_as_float(sv[cc][e]) * sl2 - lse2);
-            float p1 = exp2f(__uint_as_float(sv[cc][e + 1]) * sl2 - lse2);
-            if (need_mask) {
+            for (int e = 0; e < 32; e += 2) {
+              float p0 = exp2f(__uint_as_float(sv[cc][e]) * sl2 - lse2);
+              float p1 = exp2f(__uint_as_float(sv[cc][e + 1]) * sl2 - lse2);
               const int kv = kv0 + col_off + cc * 32 + e;
               if (!row_ok || kv < lo || kv > hi) p0 = 0.f;
               if (!row_ok || kv + 1 < lo || kv + 1 > hi) p1 = 0.f;
+              pkP[cc * 16 + (e >> 1)] = pack_bf16(p0, p1);
             }
-            pkP[cc * 16 + (e >> 1)] = pack_bf16(p0, p1);
+          }
+        } else {
+          // interior block: packed fp32 pairs for the scale / subtract, and two of every eight
+          // exponentials on the FMA pipe
+          const uint64_t sl2_2 = pack_f2(sl2, sl2), nl2 = pack_f2(-lse2, -lse2);
+#pragma unroll
+          for (int cc = 0; cc < 2; ++cc) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 8) {
+              const uint64_t x01 = ffma2(pack_u2(sv[cc][e], sv[cc][e + 1]), sl2_2, nl2);
+              const uint64_t x23 = ffma2(pack_u2(sv[cc][e + 2], sv[cc][e + 3]), sl2_2, nl2);
+              const uint64_t x45 = ffma2(pack_u2(sv[cc][e + 4], sv[cc][e + 5]), sl2_2, nl2);
+              const uint64_t x67 = ffma2(pack_u2(sv[cc][e + 6], sv[cc][e + 7]), sl2_2, nl2);
+              float a0, a1, a2, a3, a4, a5, q6, q7;
+              unpack_f2(x01, a0, a1);
+              unpack_f2(x23, a2, a3);
+              unpack_f2(x45, a4, a5);
+              unpack_f2(exp2_poly2(x67), q6, q7);
+              pkP[cc * 16 + (e >> 1)] = pack_bf16(exp2f(a0), exp2f(a1));
+              pkP[cc * 16 + (e >> 1) + 1] = pack_bf16(exp2f(a2), exp2f(a3));
+              pkP[cc * 16 + (e >> 1) + 2] = pack_bf16(exp2f(a4), exp2f(a5));
+              pkP[cc * 16 + (e >> 1) + 3] = pack_bf16(q6, q7);
+            }
           }
         }
       }
       // The shared P|dS tile is free once dK(i-1) and dQ(i-1) have completed; reading dQ(i-1) out
       // here also lets the tensor cores start dP(i).
+      LB_TRACE(it * 16 + 3);
       if (it > 0) {
         ok = drain_dq(it - 1, true);
         if (!ok) break;
       }
+      LB_TRACE(it * 16 + 4);
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc)
         st_tile_row32(sP, r, 2 * ch + cc, *reinterpret_cast<const uint32_t(*)[16]>(&pkP[cc * 16]));
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
+      LB_TRACE(it * 16 + 5);
 
       // dS = P * (dP - delta) * scale
       ok = mbar_wait(dp_full, it & 1, &abort_flag, p.status, 0x2B);
       if (!ok) break;
       tc_fence_after();
+      LB_TRACE(it * 16 + 6);
       {
         uint32_t dd[2][32];
         tmem_ld32(tdP + lane_off + col_off, dd[0]);
         tmem_ld32(tdP + lane_off + col_off + 32, dd[1]);
         tmem_wait_ld();
+        const uint64_t sc2 = pack_f2(p.scale, p.scale), ndl2 = pack_f2(-dlt, -dlt);
 #pragma unroll
         for (int cc = 0; cc < 2; ++cc) {
 #pragma unroll
           for (int e = 0; e < 32; e += 2) {
             const uint32_t pp = pkP[cc * 16 + (e >> 1)];
-            const float p0 = __uint_as_float(pp << 16), p1 = __uint_as_float(pp & 0xFFFF0000u);
-            const float d0 = p0 * (__uint_as_float(dd[cc][e]) - dlt) * p.scale;
-            const float d1 = p1 * (__uint_as_float(dd[cc][e + 1]) - dlt) * p.scale;
+            const uint64_t ps = fmul2(pack_u2(pp << 16, pp & 0xFFFF0000u), sc2);
+            const uint64_t dm = fadd2(pack_u2(dd[cc][e], dd[cc][e + 1]), ndl2);
+            float d0, d1;
+            unpack_f2(fmul2(ps, dm), d0, d1);
             pkP[cc * 16 + (e >> 1)] = pack_bf16(d0, d1);
           }
         }
       }
+      LB_TRACE(it * 16 + 7);
       ok = mbar_wait(dv_done, it & 1, &abort_flag, p.status, 0x28);
       if (!ok) break;
+      LB_TRACE(it * 16 + 8);
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc)
         st_tile_row32(sP, r, 2 * ch + cc, *reinterpret_cast<const uint32_t(*)[16]>(&pkP[cc * 16]));
@@ -834,6 +901,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(ds_full);
+      LB_TRACE(it * 16 + 9);
     }
     if (ok && n > 0) ok = drain_dq(n - 1, false);
     // epilogue: dK (warps with ch == 0) and dV (ch == 1) rows of this key block; every MMA has
