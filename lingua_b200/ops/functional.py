@@ -238,16 +238,27 @@ def ce_fwd(logits: torch.Tensor, target: torch.Tensor) -> Tuple[torch.Tensor, to
     return loss, lse
 
 
-def ce_bwd(logits, target, lse, scale: float, gscale: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16):
-    """dlogits = (softmax - onehot) * scale * gscale[0]; rows with target < 0 get zeros."""
+def ce_bwd(logits, target, lse, scale: float, gscale: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16,
+           out: Optional[torch.Tensor] = None):
+    """dlogits = (softmax - onehot) * scale * gscale[0]; rows with target < 0 get zeros.
+
+    ``out``: optional [rows, V] bf16 destination (unit stride along V, row pitch a multiple of 8)."""
     if not logits.is_cuda:
         p = torch.exp(logits.float() - lse.unsqueeze(1))
         valid = (target >= 0).unsqueeze(1)
         p.scatter_add_(1, target.clamp(min=0).unsqueeze(1), -torch.ones_like(p[:, :1]))
         g = scale * (gscale.float().reshape(()) if gscale is not None else 1.0)
-        return (p * valid * g).to(out_dtype)
+        res = (p * valid * g).to(out_dtype)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
     rows, V = logits.shape
-    d = torch.empty(rows, (V + 7) // 8 * 8, dtype=torch.bfloat16, device=logits.device)[:, :V]
+    if out is not None:
+        assert out.shape == (rows, V) and out.dtype == torch.bfloat16 and out.stride(1) == 1 and out.stride(0) % 8 == 0
+        d = out
+    else:
+        d = torch.empty(rows, (V + 7) // 8 * 8, dtype=torch.bfloat16, device=logits.device)[:, :V]
     _lib.check(_L().lb_ce_bwd(logits.data_ptr(), target.data_ptr(), lse.data_ptr(), _ptr(gscale), scale,
                               d.data_ptr(), rows, V, logits.stride(0), d.stride(0), _lib.stream_ptr()), "lb_ce_bwd")
     return d

@@ -315,6 +315,10 @@ class EmbeddingFn(torch.autograd.Function):
         return None, buf.to(table.dtype)
 
 
+# gradients of the logits are kept for a whole step (bf16) when they take no more than this
+_DLOGITS_LIMIT_BYTES = 6 << 30
+
+
 class LinearCrossEntropyFn(torch.autograd.Function):
     """mean_i CE(y_i W^T, target_i) over rows with target >= 0, without ever holding more than
     ``chunk`` rows of logits (the loss of lingua/transformer.py:51-56 applied to
@@ -353,6 +357,30 @@ class LinearCrossEntropyFn(torch.autograd.Function):
         dy = torch.empty_like(y)
         has_mg = hasattr(w, "main_grad")
         dw_acc = None
+        V = wd.shape[0]
+        Vp = (V + 7) // 8 * 8
+        if M > chunk and M * Vp * 2 <= _DLOGITS_LIMIT_BYTES:
+            # The logits stay chunked (fp32), their gradients are kept for all rows in bf16, so that the
+            # two gradient products are one GEMM each instead of one per chunk: the weight gradient then
+            # is written once instead of being read and re-written per chunk.
+            dl_all = torch.empty(M, Vp, dtype=torch.bfloat16, device=y.device)[:, :V]
+            for r0 in range(0, M, chunk):
+                r1 = min(M, r0 + chunk)
+                logits = gemm(y[r0:r1], wd, out_dtype=torch.float32)
+                loss_c, lse_c = F.ce_fwd(logits, tgt[r0:r1])
+                total += loss_c.sum()
+                F.ce_bwd(logits, tgt[r0:r1], lse_c, 1.0, gscale, out=dl_all[r0:r1])
+                del logits
+            mm_nn(dl_all, wd, out=dy)
+            if w.requires_grad:
+                if has_mg:
+                    mm_tn(dl_all, y, out=w.main_grad, accumulate=getattr(w, "grad_written", False))
+                    w.grad_written = True
+                else:
+                    dw_acc = mm_tn(dl_all, y, out_dtype=torch.float32)
+            del dl_all
+            ctx.save_for_backward(dy, dw_acc)
+            return total / n_valid
         for r0 in range(0, M, chunk):
             r1 = min(M, r0 + chunk)
             logits = gemm(y[r0:r1], wd, out_dtype=torch.float32)

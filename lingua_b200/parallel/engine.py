@@ -98,7 +98,9 @@ class ShardedEngine:
         self.compute_dtype = compute_dtype
         self.is_cuda = self.device.type == "cuda"
         self.step_count = 0
-        self.comm_stream = torch.cuda.Stream(self.device) if (self.is_cuda and self.world > 1) else None
+        # side stream: gradient reduce-scatter / parameter all-gather, and each group's share of the
+        # gradient norm, all of which overlap the backward pass of the groups that are still running
+        self.comm_stream = torch.cuda.Stream(self.device) if self.is_cuda else None
 
         taken = set()
         self.groups: List[ParamGroup] = []
@@ -113,6 +115,7 @@ class ShardedEngine:
         if rest:
             self._add_group("", rest)
         self.sumsq = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self.sumsq_parts = torch.zeros(len(self.groups), dtype=torch.float32, device=self.device)  # one per group
         self.n_params = sum(g.numel for g in self.groups)
 
     def _add_group(self, path: str, ps: List[Tuple[str, nn.Parameter]]) -> None:
@@ -184,29 +187,33 @@ class ShardedEngine:
             return
         g.reduced = True
         self._flush_autograd_grads(g)
-        if self.world == 1:
-            return
+        part = self.sumsq_parts[gi:gi + 1]
         if self.comm_stream is not None:
             self.comm_stream.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(self.comm_stream):
-                dist.reduce_scatter_tensor(g.grad_shard, g.grad, op=dist.ReduceOp.AVG, group=self.pg)
+                if self.world > 1:
+                    dist.reduce_scatter_tensor(g.grad_shard, g.grad, op=dist.ReduceOp.AVG, group=self.pg)
+                part.zero_()
+                F.sumsq(g.grad_shard, part)
                 g.grads_ready = torch.cuda.Event()
                 g.grads_ready.record(self.comm_stream)
-        else:
+            return
+        if self.world > 1:
             dist.all_reduce(g.grad, op=dist.ReduceOp.SUM, group=self.pg)
             g.grad_shard.copy_(g.grad[g.shard_slice]).div_(self.world)
+        part.zero_()
+        F.sumsq(g.grad_shard, part)
 
     def step(self, lr: float, grad_mul: float = 1.0) -> torch.Tensor:
         """Finish gradient reduction, clip by global norm, AdamW on the owned slices, re-gather.
         Returns the (pre-clip) gradient norm as a device tensor."""
         for gi in range(len(self.groups) - 1, -1, -1):
             self.reduce_group(gi)
-        self.sumsq.zero_()
         for g in self.groups:
             if g.grads_ready is not None:
                 torch.cuda.current_stream().wait_event(g.grads_ready)
                 g.grads_ready = None
-            F.sumsq(g.grad_shard, self.sumsq)
+        torch.sum(self.sumsq_parts, dim=0, keepdim=True, out=self.sumsq)
         if self.world > 1:
             dist.all_reduce(self.sumsq, op=dist.ReduceOp.SUM, group=self.pg)
         self.step_count += 1
@@ -245,7 +252,7 @@ class ShardedEngine:
         the group's gathered weights, its backward (which runs after every op of the module has
         been differentiated) starts the group's gradient reduce-scatter."""
         gi = self.group_of_module.get(module_path)
-        if gi is None or self.world == 1:
+        if gi is None or (self.world == 1 and self.comm_stream is None):
             return tensors
         self.wait_params(gi)
         live = [t for t in tensors if t is not None]
