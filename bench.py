@@ -197,12 +197,34 @@ def main() -> None:
 
             # the reference's 7B config trains without activation checkpointing; a single GPU holding the
             # whole 7B optimiser state has no room for that, so there the cheap activations are recomputed
-            sac = a.sac == "on" or (a.sac == "auto" and world == 1 and a.model == "7b")
-            extra["selective_activation_checkpointing"] = sac
-            tr = Trainer(LMTransformerArgs(**mcfg), DistributedArgs(dp_shard=world, fsdp_type="full_shard",
-                                                                    selective_activation_checkpointing=sac),
-                         OptimArgs(lr=1e-3, warmup=2000, clip=1.0), total_steps=100000, device=dev)
+            # "auto": like the reference's 7B config, no activation checkpointing if the step fits in
+            # memory (every rank must agree), else recompute the cheap activations
             dev_batches = [views(h).to(dev) for h in host]
+            tr = None
+            for sac in ([a.sac == "on"] if a.sac != "auto" else [False, True]):
+                fits = 1
+                try:
+                    tr = Trainer(LMTransformerArgs(**mcfg),
+                                 DistributedArgs(dp_shard=world, fsdp_type="full_shard",
+                                                 selective_activation_checkpointing=sac),
+                                 OptimArgs(lr=1e-3, warmup=2000, clip=1.0), total_steps=100000, device=dev)
+                    tr.train_step_async(dev_batches[0])  # first step: allocator growth
+                    torch.cuda.synchronize()
+                except torch.OutOfMemoryError:
+                    fits = 0
+                if world > 1:
+                    t_ok = torch.tensor([fits], device=dev)
+                    dist.all_reduce(t_ok, op=dist.ReduceOp.MIN)
+                    fits = int(t_ok.item())
+                if fits:
+                    break
+                tr = None
+                import gc
+                gc.collect()
+                torch.cuda.empty_cache()
+            if tr is None:
+                raise torch.OutOfMemoryError("the training step does not fit with or without activation recomputation")
+            extra["selective_activation_checkpointing"] = sac
             host_batches = [views(h).contiguous().pin_memory() for h in host]
 
             def dev_step(i):
@@ -294,6 +316,7 @@ def main() -> None:
         "wps_per_gpu": round(value / world, 1),
         "mfu_of_measured_sustained_peak": round(value / world * fpt / (peak_tf * 1e12), 4),
         "tflops_per_gpu": round(value / world * fpt / 1e12, 1),
+        "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
         "clocks": clocks,
         "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "ms_per_step": round(ms_e2e, 3),
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
