@@ -38,7 +38,21 @@ MODELS = {
     # apps/main/configs/llama_1B.yaml
     "1b": dict(dim=2048, n_layers=25, n_heads=16, vocab_size=128256, max_seqlen=4096),
 }
-BATCH = {"7b": 2, "1b": 4}
+# The other model families (ours only: the third-party kernels their reference code needs are not installable
+# offline). Sizes follow the 1B-class configs of apps/mamba/configs and apps/fastRNN/*/configs.
+OTHER_MODELS = {
+    "mamba_1b": ("lingua_b200.models.mamba", "LMMamba", "LMMambaArgs",
+                 dict(dim=2048, n_layers=48, n_heads=64, state_dim=128, n_groups=1, conv_size=4, ssm_chunk_size=256,
+                      vocab_size=128256)),
+    "hawk_1b": ("lingua_b200.models.fastrnn", "LMHawk", "LMHawkArgs",
+                dict(dim=2048, n_layers=24, n_heads=16, conv_size=4, lru_dim_multiplier=1.0, ffn_dim_multiplier=1.125,
+                     vocab_size=128256)),
+    "mingru_1b": ("lingua_b200.models.fastrnn", "LMMinGRU", "LMMinGRUArgs",
+                  dict(dim=2048, n_layers=24, n_heads=16, conv_size=4, vocab_size=128256)),
+    "minlstm_1b": ("lingua_b200.models.fastrnn", "LMMinLSTM", "LMMinLSTMArgs",
+                   dict(dim=2048, n_layers=24, n_heads=16, conv_size=4, vocab_size=128256)),
+}
+BATCH = {"7b": 2, "1b": 4, **{k: 4 for k in OTHER_MODELS}}
 SEQ = 4096
 
 
@@ -129,7 +143,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--model", default="7b", choices=list(MODELS))
+    ap.add_argument("--model", default="7b", choices=list(MODELS) + list(OTHER_MODELS))
     ap.add_argument("--ref-eager", action="store_true", help="reference arm without torch.compile")
     ap.add_argument("--sac", default="auto", choices=["auto", "on", "off"],
                     help="recompute cheap activations in backward (auto: only where memory needs it)")
@@ -174,9 +188,15 @@ def main() -> None:
         os.environ.setdefault("LOCAL_RANK", "0")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
-    mcfg = MODELS[a.model]
+    other = OTHER_MODELS.get(a.model)
+    mcfg = other[3] if other else MODELS[a.model]
     B = BATCH[a.model]
-    fpt = flops_per_token(mcfg)
+    fpt = flops_per_token(mcfg) if not other else 0.0  # filled in from the parameter count below
+    if other and a.impl != "ours":
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "n_gpus": a.gpus,
+                              "unavailable": "the reference's mamba_ssm / causal_conv1d / accelerated_scan kernels are not installable offline"}))
+        return
     dev = torch.device("cuda", local_rank)
     gen = torch.Generator().manual_seed(1234 + rank)
     n_host = 4  # distinct host batches, cycled
@@ -204,10 +224,21 @@ def main() -> None:
             for sac in ([a.sac == "on"] if a.sac != "auto" else [False, True]):
                 fits = 1
                 try:
-                    tr = Trainer(LMTransformerArgs(**mcfg),
+                    if other:
+                        import importlib
+
+                        mod = importlib.import_module(other[0])
+                        margs, kw = getattr(mod, other[2])(**mcfg), dict(model_cls=getattr(mod, other[1]),
+                                                                        grouping_plan=mod.build_fsdp_grouping_plan(
+                                                                            getattr(mod, other[2])(**mcfg)))
+                    else:
+                        margs, kw = LMTransformerArgs(**mcfg), {}
+                    tr = Trainer(margs,
                                  DistributedArgs(dp_shard=world, fsdp_type="full_shard",
                                                  selective_activation_checkpointing=sac),
-                                 OptimArgs(lr=1e-3, warmup=2000, clip=1.0), total_steps=100000, device=dev)
+                                 OptimArgs(lr=1e-3, warmup=2000, clip=1.0), total_steps=100000, device=dev, **kw)
+                    if other:  # 6 * non-embedding parameters (the reference logs no FLOPS for these models)
+                        fpt = 6.0 * (tr.engine.n_params - mcfg["vocab_size"] * mcfg["dim"])
                     tr.train_step_async(dev_batches[0])  # first step: allocator growth
                     torch.cuda.synchronize()
                 except torch.OutOfMemoryError:
@@ -304,12 +335,13 @@ def main() -> None:
     peak_tf = peaks.get("bf16_tflops_sustained") or 1400.0
     out = {
         "metric": "training tokens/s (wps summed over GPUs), Llama-7B FSDP bf16" if a.model == "7b"
+        else f"training tokens/s (wps summed over GPUs), {a.model} FSDP bf16" if other
         else "training tokens/s (wps summed over GPUs), Llama-1B FSDP bf16",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup,
         "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic uniform-random token ids, random-init weights",
         "impl": a.impl,
-        "config": {"model": f"llama_{a.model}", "global_batch": B * world, "seq_len": SEQ,
+        "config": {"model": a.model if other else f"llama_{a.model}", "global_batch": B * world, "seq_len": SEQ,
                    "parallelism": f"fsdp{world}", "tokens_per_gpu_per_step": B * SEQ,
                    "l2": "working set (>= 15 GB of weights re-read every step) exceeds the 126 MB L2; no explicit flush",
                    "optimizer": "AdamW fp32 states, clip 1.0, inside the timed region", **extra},

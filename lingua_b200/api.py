@@ -66,7 +66,12 @@ class Trainer:
         inputs, labels = batch[:, :, 0].contiguous(), batch[:, :, 1].contiguous()
         if self.acc_step == 0:
             self.engine.zero_grad()
-        loss = self.model(inputs, labels, doc_start=doc_start, doc_end=doc_end)
+        kw = {}
+        if doc_start is not None:
+            kw["doc_start"] = doc_start
+        if doc_end is not None:
+            kw["doc_end"] = doc_end
+        loss = self.model(inputs, labels, **kw)
         (loss / self.grad_acc_steps if self.grad_acc_steps > 1 else loss).backward()
         self.acc_step = (self.acc_step + 1) % self.grad_acc_steps
         if self.acc_step == 0:

@@ -12,6 +12,7 @@
 // dozen steps over a tiny array) and then replays its own steps with the right carry. Work is
 // (batch x chunks x channels) threads, reads are coalesced across channels.
 #include "common.cuh"
+#include "conv1d_vec.cuh"
 #include "lingua_b200.h"
 
 namespace lb {
@@ -216,10 +217,23 @@ extern "C" int lb_conv1d_fwd(const void* x, const void* w, const int* doc_start,
                              int W, long long ldx, long long ldy, int act, void* stream) {
   const long long total = (long long)B * S * C;
   if (total == 0) return 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (C % 8 == 0 && ldx % 8 == 0 && ldy % 8 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 &&
+      reinterpret_cast<uintptr_t>(y) % 16 == 0 && W >= 2 && W <= 4) {
+    const long long n_rows = (long long)B * S;
+    dim3 vgrid((C / 8 + 127) / 128, (unsigned)((n_rows + CONV_ROWS - 1) / CONV_ROWS));
+    switch (W) {
+      case 2: conv1d_fwd_vec_kernel<2><<<vgrid, 128, 0, st>>>((const bf16*)x, (const bf16*)w, doc_start, (bf16*)y, n_rows, S, C, ldx, ldy, act); break;
+      case 3: conv1d_fwd_vec_kernel<3><<<vgrid, 128, 0, st>>>((const bf16*)x, (const bf16*)w, doc_start, (bf16*)y, n_rows, S, C, ldx, ldy, act); break;
+      default: conv1d_fwd_vec_kernel<4><<<vgrid, 128, 0, st>>>((const bf16*)x, (const bf16*)w, doc_start, (bf16*)y, n_rows, S, C, ldx, ldy, act); break;
+    }
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    cudaError_t ev = cudaGetLastError();
+    return ev == cudaSuccess ? 0 : 400 + (int)ev;
+  }
   long long nb = (total + 255) / 256;
   const long long cap = (long long)num_sms() * 16;
   int grid = (int)(nb < cap ? nb : cap);
-  cudaStream_t st = (cudaStream_t)stream;
   switch (W) {
     case 2: conv1d_fwd_kernel<2><<<grid, 256, 0, st>>>((const bf16*)x, (const bf16*)w, doc_start, (bf16*)y, B, S, C, ldx, ldy, act); break;
     case 3: conv1d_fwd_kernel<3><<<grid, 256, 0, st>>>((const bf16*)x, (const bf16*)w, doc_start, (bf16*)y, B, S, C, ldx, ldy, act); break;
@@ -236,9 +250,22 @@ extern "C" int lb_conv1d_bwd(const void* x, const void* w, const int* doc_start,
                              int B, int S, int C, int W, long long ldx, long long ldy, long long lddx, int act,
                              void* stream) {
   if ((long long)B * S * C == 0) return 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (C % 8 == 0 && ldx % 8 == 0 && ldy % 8 == 0 && lddx % 8 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 &&
+      reinterpret_cast<uintptr_t>(dy) % 16 == 0 && reinterpret_cast<uintptr_t>(dx) % 16 == 0 && W >= 2 && W <= 4) {
+    const long long n_rows = (long long)B * S;
+    dim3 vgrid((C / 8 + 127) / 128, (unsigned)((n_rows + CONV_ROWS - 1) / CONV_ROWS));
+    switch (W) {
+      case 2: conv1d_bwd_vec_kernel<2><<<vgrid, 128, 0, st>>>((const bf16*)x, (const bf16*)w, doc_start, (const bf16*)dy, (bf16*)dx, dw, n_rows, S, C, ldx, ldy, lddx, act); break;
+      case 3: conv1d_bwd_vec_kernel<3><<<vgrid, 128, 0, st>>>((const bf16*)x, (const bf16*)w, doc_start, (const bf16*)dy, (bf16*)dx, dw, n_rows, S, C, ldx, ldy, lddx, act); break;
+      default: conv1d_bwd_vec_kernel<4><<<vgrid, 128, 0, st>>>((const bf16*)x, (const bf16*)w, doc_start, (const bf16*)dy, (bf16*)dx, dw, n_rows, S, C, ldx, ldy, lddx, act); break;
+    }
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    cudaError_t ev = cudaGetLastError();
+    return ev == cudaSuccess ? 0 : 400 + (int)ev;
+  }
   const int rows_per_thread = 64;
   dim3 grid((C + 127) / 128, (unsigned)(((long long)B * S + rows_per_thread - 1) / rows_per_thread));
-  cudaStream_t st = (cudaStream_t)stream;
   switch (W) {
     case 2: conv1d_bwd_kernel<2><<<grid, 128, 0, st>>>((const bf16*)x, (const bf16*)w, doc_start, (const bf16*)dy, (bf16*)dx, dw, B, S, C, ldx, ldy, lddx, act, rows_per_thread); break;
     case 3: conv1d_bwd_kernel<3><<<grid, 128, 0, st>>>((const bf16*)x, (const bf16*)w, doc_start, (const bf16*)dy, (bf16*)dx, dw, B, S, C, ldx, ldy, lddx, act, rows_per_thread); break;

@@ -63,9 +63,10 @@ def _close(a, b, tol=3e-2):
 @pytest.mark.gpu
 @pytest.mark.parametrize("W", [2, 3, 4])
 @pytest.mark.parametrize("with_docs", [False, True])
-def test_conv1d_kernels(W, with_docs):
+@pytest.mark.parametrize("C", [264, 100])  # 8-channel vector kernels / scalar kernels
+def test_conv1d_kernels(W, with_docs, C):
     torch.manual_seed(0)
-    B, S, C = 2, 300, 264
+    B, S = 2, 300
     buf = torch.randn(B, S, C + 40, device="cuda", dtype=torch.bfloat16)
     x = buf[:, :, 8:8 + C]  # strided rows, as a slice of a wider projection
     w = torch.randn(C, W, device="cuda", dtype=torch.bfloat16)
