@@ -44,6 +44,78 @@ def _native(t: torch.Tensor) -> bool:
     return t.is_cuda and t.dtype == torch.bfloat16
 
 
+def _lib_ssd():
+    import ctypes as C
+
+    from . import _lib
+
+    lib = _lib.load()
+    if not getattr(lib, "_ssd_declared", False):
+        lib.lb_ssd_decay_fwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
+                                         C.c_int, C.c_int, C.c_void_p]
+        lib.lb_ssd_decay_fwd.restype = C.c_int
+        lib.lb_ssd_decay_bwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                         C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
+        lib.lb_ssd_decay_bwd.restype = C.c_int
+        lib._ssd_declared = True
+    return lib
+
+
+def decay_weights_ref(scores, cs, doc):
+    """W[b,c,h,l,s] = scores[b,c,g(h),l,s] * exp(cs[b,h,c,l] - cs[b,h,c,s]) for s <= l in the same document."""
+    b, nc, g, L, _ = scores.shape
+    h = cs.shape[1]
+    seg = cs.unsqueeze(-1) - cs.unsqueeze(-2)  # b h c l s
+    tri = torch.tril(torch.ones(L, L, dtype=torch.bool, device=scores.device))
+    kern = torch.where(tri, torch.exp(seg.masked_fill(~tri, 0.0)), torch.zeros((), device=scores.device))
+    if doc is not None:
+        kern = kern * (doc.unsqueeze(-1) == doc.unsqueeze(-2)).unsqueeze(1)
+    return scores.float().repeat_interleave(h // g, dim=2) * kern.permute(0, 2, 1, 3, 4)
+
+
+class SsdDecayFn(torch.autograd.Function):
+    """(scores bf16 [b, nc, g, L, L], cs fp32 [b, h, nc, L], doc int32 [b, nc, L] | None) -> W bf16 [b, nc, h, L, L].
+
+    One kernel each way (``csrc/ssd.cu``): nothing of size [b, h, nc, L, L] other than W and its gradient exists."""
+
+    @staticmethod
+    def forward(ctx, scores, cs, doc):
+        from . import _lib
+
+        b, nc, g, L, _ = scores.shape
+        h = cs.shape[1]
+        scores, cs = scores.contiguous(), cs.contiguous()
+        doc = doc.contiguous() if doc is not None else None
+        w = torch.empty(b, nc, h, L, L, dtype=torch.bfloat16, device=scores.device)
+        _lib.check(_lib_ssd().lb_ssd_decay_fwd(scores.data_ptr(), cs.data_ptr(), None if doc is None else doc.data_ptr(),
+                                               w.data_ptr(), b, h, g, nc, L, _lib.stream_ptr()), "lb_ssd_decay_fwd")
+        ctx.save_for_backward(scores, cs, doc)
+        return w
+
+    @staticmethod
+    def backward(ctx, dw):
+        from . import _lib
+
+        scores, cs, doc = ctx.saved_tensors
+        b, nc, g, L, _ = scores.shape
+        h = cs.shape[1]
+        dw = dw.contiguous()
+        dscores = torch.zeros(scores.shape, dtype=torch.float32, device=scores.device)
+        dcs = torch.zeros_like(cs)
+        _lib.check(_lib_ssd().lb_ssd_decay_bwd(dw.data_ptr(), scores.data_ptr(), cs.data_ptr(),
+                                               None if doc is None else doc.data_ptr(), dscores.data_ptr(),
+                                               dcs.data_ptr(), b, h, g, nc, L, _lib.stream_ptr()), "lb_ssd_decay_bwd")
+        return dscores.to(scores.dtype), dcs, None
+
+
+def decay_weights(scores, cs, doc):
+    """bf16 W for the intra-chunk product; fused kernel on CUDA bf16, PyTorch otherwise."""
+    L = scores.shape[-1]
+    if _native(scores) and L % 8 == 0 and L <= 512:
+        return SsdDecayFn.apply(scores, cs.float(), None if doc is None else doc.int())
+    return decay_weights_ref(scores, cs, doc).to(scores.dtype)
+
+
 def bmm_nt(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     """Batched ``a @ b^T``; the native kernel needs contiguous rows whose length is a multiple of 8."""
     if _native(a) and _native(b) and a.shape[-1] % 8 == 0 and a.shape[-2] % 8 == 0 and b.shape[-2] % 8 == 0:
@@ -51,6 +123,29 @@ def bmm_nt(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
         a3 = a.reshape(-1, *a.shape[-2:]).contiguous()
         b3 = b.reshape(-1, *b.shape[-2:]).contiguous()
         return BmmFn.apply(a3, b3).view(*lead, a.shape[-2], b.shape[-2])
+    return torch.matmul(a, b.transpose(-1, -2))
+
+
+def _tma_ok(t: torch.Tensor) -> bool:
+    if not _native(t) or t.data_ptr() % 16:
+        return False
+    st = t.stride()
+    if st[-1] == 1:
+        lead = [st[-2]] + list(st[:-2])
+    elif st[-2] == 1:
+        lead = [st[-1]] + list(st[:-2])
+    else:
+        return False
+    return all(v % 8 == 0 for v in lead)
+
+
+def mm_views(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """``a @ b^T`` for 4-D strided views a [b0, b1, M, K], b [b0, b1, N, K] without copying them when the
+    tcgen05 GEMM can read them in place (unit stride along M/N or K, 16-byte aligned pitches)."""
+    if _tma_ok(a) and _tma_ok(b) and a.shape[-2] % 8 == 0 and b.shape[-2] % 8 == 0 and a.shape[-1] % 8 == 0:
+        return BmmFn.apply(a, b)
+    if a.is_cuda and a.dtype == torch.bfloat16:
+        return bmm_nt(a, b)
     return torch.matmul(a, b.transpose(-1, -2))
 
 
@@ -112,25 +207,22 @@ def ssd_chunked(x, dt, A, B, C, D=None, chunk: int = 256, doc_start: Optional[to
         prev_last = torch.cat([torch.full_like(doc[:, :1, -1], -1), doc[:, :-1, -1]], dim=1)  # b c
         from_prev = doc == prev_last.unsqueeze(-1)  # token continues the document carried in
         cont = doc[:, :, -1] == prev_last  # whole chunk continues it
-    # 1) inside a chunk: scores = C B^T (per group), kernel = exp(cs_l - cs_s) for l >= s
-    scores = bmm_nt(Cc.permute(0, 1, 3, 2, 4).reshape(b * nc, g, L, n), Bc.permute(0, 1, 3, 2, 4).reshape(b * nc, g, L, n))
-    scores = scores.view(b, nc, g, L, L).float()
-    seg = cs.unsqueeze(-1) - cs.unsqueeze(-2)  # b h c l s
-    tri = torch.tril(torch.ones(L, L, dtype=torch.bool, device=x.device))
-    kern = torch.where(tri, torch.exp(seg.masked_fill(~tri, 0.0)), torch.zeros((), device=x.device))
-    if doc_start is not None:
-        kern = kern * same.unsqueeze(1)
-    w = (scores.repeat_interleave(rep, dim=2).permute(0, 2, 1, 3, 4) * kern).to(cdt)  # b h c l s
-    xh = xdt.permute(0, 3, 1, 4, 2)  # b h c p l  ([N=p, K=l] operand)
-    y_diag = bmm_nt(w.reshape(b * h, nc, L, L), xh.reshape(b * h, nc, p, L))  # b*h c l p
-    # 2) state contributed by each chunk: sum_l exp(cs_last - cs_l) B_l (dt x)_l^T
+    hp = rep * p  # rows of one group's heads folded into one matrix dimension
+    # 1) inside a chunk: scores = C B^T (per group), W = scores o decay kernel (lower triangle, same document)
+    Cg = Cc.permute(0, 1, 3, 2, 4).reshape(b * nc, g, L, n)  # views: (b, nc) merge without a copy
+    Bg = Bc.permute(0, 1, 3, 2, 4).reshape(b * nc, g, L, n)
+    scores = mm_views(Cg, Bg)  # [b*nc, g, L, L]
+    w = decay_weights(scores.view(b, nc, g, L, L), cs, doc if doc_start is not None else None)  # b c h l s
+    xh = xdt.permute(0, 1, 3, 4, 2).reshape(b * nc, h, p, L)  # [N=p, K=l] operand, read in place
+    y_diag = mm_views(w.reshape(b * nc, h, L, L), xh)  # [b*nc, h, L, p]
+    # 2) state contributed by each chunk: sum_l exp(cs_last - cs_l) B_l (dt x)_l^T, all heads of a group at once
     decay_to_end = torch.exp(cs[..., -1:] - cs)  # b h c l
     if doc_start is not None:
         decay_to_end = decay_to_end * same_as_last.unsqueeze(1)
     xw = (xdt.float() * decay_to_end.permute(0, 2, 3, 1).unsqueeze(-1)).to(cdt)  # b c l h p
-    Bh = Bc.repeat_interleave(rep, dim=3)  # b c l h n
-    chunk_states = bmm_nt(xw.permute(0, 3, 1, 4, 2).reshape(b * h, nc, p, L),
-                          Bh.permute(0, 3, 1, 4, 2).reshape(b * h, nc, n, L)).view(b, h, nc, p, n).float()
+    xw_g = xw.view(b * nc, L, g, hp).permute(0, 2, 3, 1)  # [b*nc, g, M=hp, K=l]
+    Bt = Bc.reshape(b * nc, L, g, n).permute(0, 2, 3, 1)  # [b*nc, g, N=n, K=l]
+    chunk_states = mm_views(xw_g, Bt).view(b, nc, h, p, n).float()
     # 3) carry the state over chunks (nc sequential steps on small tensors)
     chunk_decay = torch.exp(cs[..., -1])  # b h c
     if doc_start is not None:
@@ -139,16 +231,17 @@ def ssd_chunked(x, dt, A, B, C, D=None, chunk: int = 256, doc_start: Optional[to
     carried = []
     for c in range(nc):
         carried.append(state)
-        state = chunk_decay[:, :, c].view(b, h, 1, 1) * state + chunk_states[:, :, c]
-    prev_states = torch.stack(carried, dim=2).to(cdt)  # b h c p n
+        state = chunk_decay[:, :, c].view(b, h, 1, 1) * state + chunk_states[:, c]
+    prev_states = torch.stack(carried, dim=1).to(cdt)  # b c h p n
     # 4) contribution of the carried state: (C_l . state) * exp(cs_l)
-    Ch = Cc.repeat_interleave(rep, dim=3).permute(0, 3, 1, 2, 4)  # b h c l n
-    y_off = bmm_nt(Ch.reshape(b * h, nc, L, n), prev_states.reshape(b * h, nc, p, n)).view(b, h, nc, L, p).float()
+    y_off = mm_views(Cg, prev_states.view(b * nc, g, hp, n))  # [b*nc, g, L, hp]
     out_decay = torch.exp(cs)
     if doc_start is not None:
         out_decay = out_decay * from_prev.unsqueeze(1)
-    y = y_diag.view(b, h, nc, L, p).float() + y_off * out_decay.unsqueeze(-1)
-    y = y.permute(0, 2, 3, 1, 4).reshape(b, sp, h, p)
+    y = (y_diag.view(b, nc, h, L, p).permute(0, 1, 3, 2, 4).float()
+         + y_off.view(b, nc, g, L, rep, p).permute(0, 1, 3, 2, 4, 5).reshape(b, nc, L, h, p).float()
+         * out_decay.permute(0, 2, 3, 1).unsqueeze(-1))
+    y = y.reshape(b, sp, h, p)
     if D is not None:
         y = y + D.float().view(1, 1, h, -1) * x.float()
     return y[:, :s].to(cdt), state

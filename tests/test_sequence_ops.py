@@ -104,3 +104,34 @@ def test_scan_kernels(S, with_docs):
     hr.backward(dh.float())
     _close(bg.grad, br.grad, 4e-2)
     _close(ag.grad, ar.grad, 4e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("L,g,with_docs", [(256, 1, False), (64, 2, True), (128, 4, True)])
+def test_ssd_decay_kernels(L, g, with_docs):
+    """Fused W = (C B^T) o decay-kernel and its backward vs the PyTorch statement."""
+    from lingua_b200.ops import ssd as SSD
+
+    torch.manual_seed(5)
+    b, nc, h = 2, 3, 4
+    scores = (torch.randn(b, nc, g, L, L, device="cuda") * 0.5).bfloat16()
+    cs = -torch.rand(b, h, nc, L, device="cuda").cumsum(-1) * 0.05
+    doc = None
+    if with_docs:
+        starts = torch.zeros(b, nc * L, dtype=torch.int32, device="cuda")
+        starts[:, L // 3:] = L // 3
+        starts[:, L + 5:] = L + 5
+        doc = starts.view(b, nc, L)
+    s1 = scores.clone().requires_grad_(True)
+    c1 = cs.clone().requires_grad_(True)
+    s2 = scores.float().requires_grad_(True)
+    c2 = cs.clone().requires_grad_(True)
+    w = SSD.decay_weights(s1, c1, doc)
+    wr = SSD.decay_weights_ref(s2, c2, doc)
+    assert w.dtype == torch.bfloat16 and w.shape == (b, nc, h, L, L)
+    _close(w, wr, 1e-2)
+    dw = torch.randn_like(wr)
+    w.backward(dw.bfloat16())
+    wr.backward(dw.bfloat16().float())
+    _close(s1.grad, s2.grad, 2e-2)
+    _close(c1.grad, c2.grad, 2e-2)
