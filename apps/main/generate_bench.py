@@ -30,6 +30,7 @@ def main(argv=None):
     ap.add_argument("--batch", type=int, default=32)
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--new", type=int, default=256)
+    ap.add_argument("--eager", action="store_true", help="do not replay the decode step as a CUDA graph")
     a = ap.parse_args(argv)
     dev = torch.device("cuda")
     args = LMTransformerArgs(**MODELS[a.model])
@@ -42,7 +43,8 @@ def main(argv=None):
     model.eval()
     tok = build_tokenizer("bytes")
     cfg = PackedCausalTransformerGeneratorArgs(temperature=0.0, max_gen_len=a.new, max_prompt_len=a.prompt,
-                                               max_tokens=a.batch * (a.prompt + a.new))
+                                               max_tokens=a.batch * (a.prompt + a.new),
+                                               reduce_generation_overhead=not a.eager)
     gen = PackedCausalTransformerGenerator(cfg, model, tok)
     g = torch.Generator().manual_seed(1)
     prompts = ["".join(chr(97 + int(c)) for c in torch.randint(0, 26, (a.prompt - 1,), generator=g)) for _ in range(a.batch)]
@@ -77,7 +79,7 @@ def main(argv=None):
         "prompt_tokens": a.prompt, "new_tokens": a.new, "ms_total": round(ms, 1), "ms_prefill": round(ms_prefill, 1),
         "tokens_per_s_end_to_end": round(n_new / ms * 1e3, 1),
         "tokens_per_s_decode": round(n_new / max(ms - ms_prefill, 1e-3) * 1e3, 1),
-        "ms_per_decode_step": round((ms - ms_prefill) / a.new, 3), "dtype": "bf16",
+        "ms_per_decode_step": round((ms - ms_prefill) / a.new, 3), "cuda_graph": not a.eager, "dtype": "bf16",
         "data": "random prompts, random-init weights"}))
 
 

@@ -166,7 +166,7 @@ class PackedCausalTransformerGeneratorArgs:
     max_prompt_len: Optional[int] = None
     until: List[str] = field(default_factory=list)
     compile_prefilling: bool = False  # accepted for config compatibility
-    reduce_generation_overhead: bool = False  # accepted for config compatibility
+    reduce_generation_overhead: bool = False  # replay the decode step as a CUDA graph (launch-bound otherwise)
     show_progress: bool = False
     dtype: Optional[str] = "bf16"
     device: Optional[str] = "cuda"
@@ -185,6 +185,11 @@ class PackedCausalTransformerGenerator:
         self.plan = CachePlan()
         self.padded_doc_start = None
         self.current_tok_id = None
+        # decode step as a CUDA graph (the reference gets the same effect from torch.compile's
+        # "reduce-overhead" mode, apps/main/generate.py:175-180)
+        self.use_graph = bool(cfg.reduce_generation_overhead)
+        self._graph = None
+        self._eager_steps = 0
 
     # ---- cache management (overridden by the state-space / recurrent generators)
     def clear_cache(self):
@@ -220,6 +225,7 @@ class PackedCausalTransformerGenerator:
         pl.start = self.padded_doc_start.int().contiguous()
         self.current_tok_id = lengths.clone()
         pl.len = (self.current_tok_id + 1).int().contiguous()
+        self._graph, self._eager_steps = None, 0  # new cache plan tensors: a captured step is stale
 
     def prefill(self, tokens: torch.Tensor, lengths: torch.Tensor):
         self.setup_prefilling(lengths)
@@ -228,10 +234,35 @@ class PackedCausalTransformerGenerator:
         return out
 
     def generate_next_token(self, current_token: torch.Tensor):
+        if self.use_graph and current_token.is_cuda:
+            return self._graphed_next_token(current_token)
         self.plan.len = (self.current_tok_id + 1).int().contiguous()
         out = self.model(current_token, tok_idx=self.current_tok_id.view(1, -1))
         self.current_tok_id += 1
         return out
+
+    def _graphed_next_token(self, current_token: torch.Tensor):
+        """Two eager steps (lazy initialisation of kernels and allocator), then the step is captured once with
+        static input / position / length tensors and replayed; the returned logits live in the graph's pool."""
+        if self._graph is None:
+            if self._eager_steps < 2:
+                self._eager_steps += 1
+                self.plan.len = (self.current_tok_id + 1).int().contiguous()
+                out = self.model(current_token, tok_idx=self.current_tok_id.view(1, -1))
+                self.current_tok_id += 1
+                return out
+            self._g_token = current_token.clone()
+            self.plan.len = (self.current_tok_id + 1).int().contiguous()
+            graph = torch.cuda.CUDAGraph()
+            torch.cuda.synchronize()
+            with torch.cuda.graph(graph):
+                self.plan.len.copy_((self.current_tok_id + 1).int())
+                out = self.model(self._g_token, tok_idx=self.current_tok_id.view(1, -1))
+                self.current_tok_id += 1
+            self._graph, self._g_out = graph, out
+        self._g_token.copy_(current_token)
+        self._graph.replay()
+        return self._g_out
 
     @torch.inference_mode()
     def generate(self, prompts: List[str]):

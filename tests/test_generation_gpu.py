@@ -50,3 +50,21 @@ def test_generate_api_runs_greedy():
                                            ByteTokenizer())
     texts, lls, greedy = gen.generate(["first prompt", "second"])
     assert len(texts) == 2 and len(lls[0]) == len("first prompt") and all(torch.isfinite(l).all() for l in lls)
+
+
+def test_graph_replayed_decode_matches_eager():
+    torch.manual_seed(2)
+    args = LMTransformerArgs(dim=256, n_layers=2, n_heads=2, vocab_size=258, max_seqlen=128)
+    model = LMTransformer(args)
+    model.init_weights()
+    model = model.cuda().bfloat16().eval()
+    model.rope_embeddings.reset_parameters()
+    prompts = ["a first prompt", "second", "and a third one"]
+    outs = []
+    for graph in (False, True):
+        gen = PackedCausalTransformerGenerator(
+            PackedCausalTransformerGeneratorArgs(max_gen_len=12, max_tokens=512, reduce_generation_overhead=graph),
+            model, ByteTokenizer())
+        outs.append(gen.generate(prompts)[0])
+        outs.append(gen.generate(prompts[:2])[0])  # second call: new batch shape, graph is rebuilt
+    assert outs[0] == outs[2] and outs[1] == outs[3]
