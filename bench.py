@@ -145,6 +145,8 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="7b", choices=list(MODELS) + list(OTHER_MODELS))
     ap.add_argument("--ref-eager", action="store_true", help="reference arm without torch.compile")
+    ap.add_argument("--float8", action="store_true",
+                    help="ours only: row-wise e4m3 forward / input-gradient products in the blocks (reported as dtype fp8)")
     ap.add_argument("--sac", default="auto", choices=["auto", "on", "off"],
                     help="recompute cheap activations in backward (auto: only where memory needs it)")
     a = ap.parse_args()
@@ -235,7 +237,8 @@ def main() -> None:
                         margs, kw = LMTransformerArgs(**mcfg), {}
                     tr = Trainer(margs,
                                  DistributedArgs(dp_shard=world, fsdp_type="full_shard",
-                                                 selective_activation_checkpointing=sac),
+                                                 selective_activation_checkpointing=sac,
+                                                 float8_recipe="rowwise" if a.float8 else None),
                                  OptimArgs(lr=1e-3, warmup=2000, clip=1.0), total_steps=100000, device=dev, **kw)
                     if other:  # 6 * non-embedding parameters (the reference logs no FLOPS for these models)
                         fpt = 6.0 * (tr.engine.n_params - mcfg["vocab_size"] * mcfg["dim"])
@@ -339,7 +342,7 @@ def main() -> None:
         else "training tokens/s (wps summed over GPUs), Llama-1B FSDP bf16",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup,
         "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic uniform-random token ids, random-init weights",
+        "dtype": "fp8 (e4m3 row-wise fwd / dgrad, bf16 wgrad)" if a.float8 else "bf16", "data": "synthetic uniform-random token ids, random-init weights",
         "impl": a.impl,
         "config": {"model": a.model if other else f"llama_{a.model}", "global_batch": B * world, "seq_len": SEQ,
                    "parallelism": f"fsdp{world}", "tokens_per_gpu_per_step": B * SEQ,

@@ -371,7 +371,10 @@ extern "C" int lb_gemm(const LbGemmArgs* args, void* stream) {
   if (a.force_bn == 512 || (a.force_bn == 0 && a.M >= 256 && a.N >= 256 && tiles2 >= num_sms() / 2))
     return gemm2_dispatch(a, s);
   // Narrow outputs use the 128-wide tile so that small N does not waste half of every MMA.
-  const bool narrow = a.N <= 128 || a.force_bn == 128;
+  // So do few-row problems (decode steps): they stream the weight once, and twice as many tiles keep
+  // twice as many SMs pulling on memory.
+  const long long tiles256 = (long long)((a.M + 127) / 128) * ((a.N + 255) / 256) * a.nb0 * a.nb1;
+  const bool narrow = a.N <= 128 || a.force_bn == 128 || (a.force_bn == 0 && a.M <= 128 && tiles256 < num_sms());
   if (a.out_dtype == LB_BF16)
     return narrow ? dispatch_major<128, 2, __nv_bfloat16>(a, s) : dispatch_major<256, 2, __nv_bfloat16>(a, s);
   if (a.out_dtype == LB_F32)

@@ -295,8 +295,10 @@ class PackedCausalTransformerGenerator:
                 for i, tok in enumerate(nxt.squeeze(0).tolist()):
                     if not is_done[i]:
                         generated[i].append(tok)
-                        tail = self.tokenizer.decode(generated[i][-self.max_until_size:])
-                        is_done[i] = any(e in tail for e in self.until) or tok == self.tokenizer.eos_id
+                        is_done[i] = tok == self.tokenizer.eos_id
+                        if self.until and not is_done[i]:
+                            tail = self.tokenizer.decode(generated[i][-self.max_until_size:])
+                            is_done[i] = any(e in tail for e in self.until)
                 if all(is_done):
                     break
                 current = nxt
