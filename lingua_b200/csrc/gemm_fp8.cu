@@ -269,6 +269,46 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int K, uin
   }
 }
 
+// Rows longer than the register budget of quant_rows_kernel: two passes over the row (the second one
+// hits L2).
+__global__ void __launch_bounds__(Q_THREADS)
+quant_rows_long_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int K, uint8_t* __restrict__ out,
+                       long long ldo, float* __restrict__ scale) {
+  const long long row = blockIdx.x;
+  const int nvec = K / 8;
+  float amax = 0.f;
+  for (int v = threadIdx.x; v < nvec; v += Q_THREADS) {
+    const uint4 q = *reinterpret_cast<const uint4*>(x + row * ldx + v * 8);
+    const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(b[j]);
+      amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+    }
+  }
+  __shared__ float red[Q_THREADS / 32];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < Q_THREADS / 32; ++i) amax = fmaxf(amax, red[i]);
+  const float sc = fmaxf(amax, AMAX_EPS) / E4M3_MAX;
+  const float inv = 1.f / sc;
+  if (threadIdx.x == 0) scale[row] = sc;
+  for (int v = threadIdx.x; v < nvec; v += Q_THREADS) {
+    const uint4 q = *reinterpret_cast<const uint4*>(x + row * ldx + v * 8);
+    const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&q);
+    const float2 f0 = __bfloat1622float2(b[0]), f1 = __bfloat1622float2(b[1]);
+    const float2 f2 = __bfloat1622float2(b[2]), f3 = __bfloat1622float2(b[3]);
+    uint2 o;
+    o.x = cvt_e4m3x4(f0.x * inv, f0.y * inv, f1.x * inv, f1.y * inv);
+    o.y = cvt_e4m3x4(f2.x * inv, f2.y * inv, f3.x * inv, f3.y * inv);
+    *reinterpret_cast<uint2*>(out + row * ldo + v * 8) = o;
+  }
+}
+
 // out[k, n] = e4m3(w[n, k] / *scale). 64 x 64 tiles through shared memory.
 __global__ void __launch_bounds__(256)
 quant_transpose_kernel(const __nv_bfloat16* __restrict__ w, int N, int K, const float* __restrict__ scale,
@@ -308,9 +348,13 @@ extern "C" int lb_gemm_fp8(const LbGemmFp8Args* a, void* stream) {
 extern "C" int lb_quant_rows(const void* x, long long ldx, long long rows, int K, void* out, long long ldo,
                              float* scale, void* stream) {
   if (!x || !out || !scale || rows <= 0) return 1;
-  if (K % 8 != 0 || K > 8 * lb::f8::Q_THREADS * lb::f8::Q_MAXV || ldx % 8 != 0 || ldo % 8 != 0) return 2;
-  lb::f8::quant_rows_kernel<<<(unsigned)rows, lb::f8::Q_THREADS, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<const __nv_bfloat16*>(x), ldx, K, reinterpret_cast<uint8_t*>(out), ldo, scale);
+  if (K % 8 != 0 || ldx % 8 != 0 || ldo % 8 != 0) return 2;
+  if (K > 8 * lb::f8::Q_THREADS * lb::f8::Q_MAXV)
+    lb::f8::quant_rows_long_kernel<<<(unsigned)rows, lb::f8::Q_THREADS, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const __nv_bfloat16*>(x), ldx, K, reinterpret_cast<uint8_t*>(out), ldo, scale);
+  else
+    lb::f8::quant_rows_kernel<<<(unsigned)rows, lb::f8::Q_THREADS, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const __nv_bfloat16*>(x), ldx, K, reinterpret_cast<uint8_t*>(out), ldo, scale);
   lb::g_launches.fetch_add(1, std::memory_order_relaxed);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;

@@ -60,8 +60,8 @@ def _native(t: torch.Tensor) -> bool:
 
 
 def supported(K: int, N: int) -> bool:
-    """Shapes the float8 kernels take: K (reduction) and N (output) multiples of 16, K <= 16384."""
-    return K % 16 == 0 and N % 16 == 0 and K <= 16384 and N <= 16384 * 8
+    """Shapes the float8 kernels take: K (reduction) and N (output) multiples of 16."""
+    return K % 16 == 0 and N % 16 == 0
 
 
 # ------------------------------------------------------------------ quantisation

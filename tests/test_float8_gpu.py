@@ -13,7 +13,7 @@ pytestmark = pytest.mark.gpu
 bf = torch.bfloat16
 
 
-@pytest.mark.parametrize("rows,K", [(64, 128), (300, 4096), (17, 11008), (8, 16384)])
+@pytest.mark.parametrize("rows,K", [(64, 128), (300, 4096), (17, 11008), (8, 16384), (5, 22016)])
 def test_quant_rows_matches_reference(rows, K):
     torch.manual_seed(0)
     x = (torch.randn(rows, K, device="cuda") * torch.logspace(-2, 2, rows, device="cuda")[:, None]).to(bf)
