@@ -38,6 +38,7 @@ class DistributedArgs:
     dp_replicate: int = 1  # replicas of that group (outer data-parallel dim)
     tp_size: int = 1
     fused_tp_forward: bool = True  # no-grad TP passes use the fused all-gather / reduce-scatter GEMMs
+    p2p_param_gather: bool = True  # parameter all-gather by NVLink copy engines instead of NCCL kernels
     selective_activation_checkpointing: bool = False
     compile: bool = False
     fsdp_type: str = "no_shard"
@@ -340,7 +341,8 @@ def parallelize_model(model, mesh: Mesh, model_args, distributed_args: Distribut
     dtype = DTYPES[distributed_args.model_dtype] if device.type == "cuda" else torch.float32
     assert distributed_args.fsdp_type in ("full_shard", "no_shard")
     pg = mesh.group("dp") if mesh.size("dp") > 1 else False
-    engine = ShardedEngine(model, fsdp_grouping_plan, process_group=pg, compute_dtype=dtype, optim=optim, device=device)
+    engine = ShardedEngine(model, fsdp_grouping_plan, process_group=pg, compute_dtype=dtype, optim=optim, device=device,
+                           p2p_gather=distributed_args.p2p_param_gather)
     for buf_owner in model.modules():
         for name, buf in list(buf_owner._buffers.items()):
             if buf is not None and buf.device.type == "meta":

@@ -44,8 +44,9 @@ class ParamGroup:
     """One flat buffer worth of parameters."""
 
     def __init__(self, name: str, params: List[Tuple[str, nn.Parameter]], world: int, rank: int,
-                 compute_dtype: torch.dtype, device: torch.device):
+                 compute_dtype: torch.dtype, device: torch.device, alloc_full: Optional[Callable] = None):
         self.name, self.params = name, params
+        self.peer_full: Optional[List[torch.Tensor]] = None  # every rank's ``full`` buffer, when peer-visible
         self.world, self.rank = world, rank
         align = 64 * world  # every shard starts on a 256-byte boundary in fp32
         self.offsets: Dict[str, Tuple[int, int]] = {}
@@ -57,7 +58,8 @@ class ParamGroup:
         self.numel = off
         self.padded = (off + align - 1) // align * align
         self.shard_numel = self.padded // world
-        self.full = torch.zeros(self.padded, dtype=compute_dtype, device=device)
+        self.full = (alloc_full(self.padded) if alloc_full is not None
+                     else torch.zeros(self.padded, dtype=compute_dtype, device=device))
         self.grad = torch.zeros(self.padded, dtype=torch.float32, device=device)
         s0 = rank * self.shard_numel
         self.shard_slice = slice(s0, s0 + self.shard_numel)
@@ -88,7 +90,7 @@ class ParamGroup:
 class ShardedEngine:
     def __init__(self, model: nn.Module, plan: Sequence[Tuple[str, bool]], process_group=None,
                  compute_dtype: torch.dtype = torch.bfloat16, optim: Optional[EngineOptim] = None,
-                 device: Optional[torch.device] = None):
+                 device: Optional[torch.device] = None, p2p_gather: bool = True):
         self.model = model
         self.pg = process_group
         self.world = dist.get_world_size(process_group) if (dist.is_initialized() and process_group is not False) else 1
@@ -100,7 +102,30 @@ class ShardedEngine:
         self.step_count = 0
         # side stream: gradient reduce-scatter / parameter all-gather, and each group's share of the
         # gradient norm, all of which overlap the backward pass of the groups that are still running
-        self.comm_stream = torch.cuda.Stream(self.device) if self.is_cuda else None
+        self.comm_stream = torch.cuda.Stream(self.device, priority=-1) if self.is_cuda else None
+        # Parameter all-gather over NVLink by the copy engines: the compute-dtype buffers live in peer-visible
+        # (symmetric) memory, every rank pushes its freshly updated slice into the peers' buffers with plain
+        # device-to-device copies and a small barrier kernel confirms arrival. No SM runs a communication
+        # kernel while the next forward pass is computing. Falls back to NCCL when the group has no peer access.
+        self._symm = None
+        self._pad_ptrs: Optional[List[int]] = None
+        self._barrier_epoch = 0
+        if self.is_cuda and self.world > 1 and p2p_gather:
+            try:
+                import torch.distributed._symmetric_memory as sm
+
+                pad = sm.empty(8, dtype=torch.int32, device=self.device)
+                pad.zero_()
+                hdl = sm.rendezvous(pad, group=self.pg if self.pg is not None else dist.group.WORLD)
+                self._symm, self._pad = sm, pad
+                self._pad_ptrs = [int(p) for p in hdl.buffer_ptrs]
+                torch.cuda.synchronize(self.device)
+                dist.barrier(group=self.pg)  # every pad is zero before the first barrier kernel runs
+            except Exception as e:  # no peer access inside this group: NCCL all-gather
+                import logging
+
+                logging.getLogger(__name__).warning("peer-to-peer parameter gather disabled: %s", e)
+                self._symm = None
 
         taken = set()
         self.groups: List[ParamGroup] = []
@@ -120,7 +145,22 @@ class ShardedEngine:
 
     def _add_group(self, path: str, ps: List[Tuple[str, nn.Parameter]]) -> None:
         self.group_of_module[path] = len(self.groups)
-        g = ParamGroup(path, ps, self.world, self.rank, self.compute_dtype, self.device)
+        alloc = None
+        if self._symm is not None:
+            def alloc(n):
+                t = self._symm.empty(n, dtype=self.compute_dtype, device=self.device)
+                t.zero_()
+                return t
+        g = ParamGroup(path, ps, self.world, self.rank, self.compute_dtype, self.device, alloc_full=alloc)
+        if self._symm is not None:
+            try:
+                hdl = self._symm.rendezvous(g.full, group=self.pg if self.pg is not None else dist.group.WORLD)
+                g.peer_full = [hdl.get_buffer(r, (g.padded,), self.compute_dtype) for r in range(self.world)]
+            except Exception as e:  # this group then uses the NCCL all-gather
+                import logging
+
+                logging.getLogger(__name__).warning("no peer view of group %s: %s", path, e)
+                g.peer_full = None
         self.groups.append(g)
         for fqn, new_p in g.params:
             owner_path, _, attr = fqn.rpartition(".")
@@ -222,8 +262,8 @@ class ShardedEngine:
             F.adamw_step(g.master, g.exp_avg, g.exp_avg_sq, g.grad_shard, g.full[g.shard_slice],
                          step=self.step_count, lr=lr, beta1=o.beta1, beta2=o.beta2, eps=o.eps, wd=o.weight_decay,
                          sumsq_t=self.sumsq, max_norm=o.clip, grad_mul=grad_mul)
-        if self.world > 1:
-            self.gather_params()
+            if self.world > 1:
+                self._gather_group(g)  # overlaps the AdamW launches of the groups that follow
         return self.sumsq.sqrt() * grad_mul
 
     def gather_params(self) -> None:
@@ -231,16 +271,35 @@ class ShardedEngine:
         the first layers of the next forward are ready first)."""
         if self.world == 1:
             return
+        for g in self.groups:
+            self._gather_group(g)
+
+    def _gather_group(self, g: ParamGroup) -> None:
+        """In-place all-gather of one group (every rank's slice already sits at its place in ``g.full``);
+        on CUDA it runs on the side stream after everything queued so far on the compute stream."""
         if self.comm_stream is not None:
-            self.comm_stream.wait_stream(torch.cuda.current_stream())
+            done = torch.cuda.Event()
+            done.record(torch.cuda.current_stream())
+            self.comm_stream.wait_event(done)
             with torch.cuda.stream(self.comm_stream):
-                for g in self.groups:
-                    dist.all_gather_into_tensor(g.full, g.full[g.shard_slice].clone(), group=self.pg)
-                    g.params_ready = torch.cuda.Event()
-                    g.params_ready.record(self.comm_stream)
+                if g.peer_full is not None:
+                    mine = g.full[g.shard_slice]
+                    for k in range(1, self.world):  # start with the next rank so that links are used evenly
+                        r = (self.rank + k) % self.world
+                        g.peer_full[r][g.shard_slice].copy_(mine, non_blocking=True)
+                    self._peer_barrier()  # every rank's pushes, mine included, have landed
+                else:
+                    dist.all_gather_into_tensor(g.full, g.full[g.shard_slice], group=self.pg)
+                g.params_ready = torch.cuda.Event()
+                g.params_ready.record(self.comm_stream)
         else:
-            for g in self.groups:
-                dist.all_gather_into_tensor(g.full, g.full[g.shard_slice].clone(), group=self.pg)
+            dist.all_gather_into_tensor(g.full, g.full[g.shard_slice].clone(), group=self.pg)
+
+    def _peer_barrier(self) -> None:
+        from .tp_fused import peer_barrier
+
+        self._barrier_epoch += 1
+        peer_barrier(self._pad_ptrs, self.rank, self._barrier_epoch)
 
     def wait_all_params(self) -> None:
         for gi in range(len(self.groups)):

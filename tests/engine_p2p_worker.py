@@ -1,0 +1,62 @@
+"""One rank of the multi-GPU check of the sharded engine: parameter all-gather through NVLink copy engines
+(symmetric memory) must give exactly the training trajectory of the NCCL all-gather. Started by torchrun from
+test_tp_fused_multigpu.py."""
+import os
+import sys
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
+
+from lingua_b200.api import Trainer  # noqa: E402
+from lingua_b200.distributed import DistributedArgs  # noqa: E402
+from lingua_b200.models.transformer import LMTransformerArgs  # noqa: E402
+from lingua_b200.ops import _lib  # noqa: E402
+from lingua_b200.optim import OptimArgs  # noqa: E402
+
+
+def run(p2p: bool, rank: int, world: int, dev):
+    args = LMTransformerArgs(dim=512, n_layers=3, n_heads=4, vocab_size=1024, max_seqlen=256)
+    tr = Trainer(args, DistributedArgs(dp_shard=world, fsdp_type="full_shard", p2p_param_gather=p2p),
+                 OptimArgs(lr=3e-3, warmup=1, clip=1.0), total_steps=100, device=dev)
+    assert (tr.engine.groups[0].peer_full is not None) == p2p
+    g = torch.Generator().manual_seed(100 + rank)
+    losses = []
+    for _ in range(5):
+        tok = torch.randint(0, 1024, (2, 257), generator=g)
+        batch = torch.stack((tok[:, :-1], tok[:, 1:]), dim=-1)
+        losses.append(tr.train_step(batch))
+    tr.engine.wait_all_params()
+    torch.cuda.synchronize()
+    _lib.check_status()
+    # every rank holds the same gathered parameters
+    for grp in tr.engine.groups:
+        s = grp.full.float().sum().reshape(1)
+        lo, hi = s.clone(), s.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        assert lo.item() == hi.item(), f"group {grp.name} differs between ranks"
+    sums = [grp.full.float().sum().item() for grp in tr.engine.groups]
+    return losses, sums
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    dist.init_process_group("nccl", device_id=dev)
+    l_p2p, s_p2p = run(True, rank, world, dev)
+    l_nccl, s_nccl = run(False, rank, world, dev)
+    assert l_p2p == l_nccl, (l_p2p, l_nccl)
+    assert s_p2p == s_nccl
+    assert l_p2p[-1] < l_p2p[0]
+    dist.barrier()
+    if rank == 0:
+        print("ENGINE_P2P_OK", l_p2p)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

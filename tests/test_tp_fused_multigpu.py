@@ -19,3 +19,12 @@ def test_fused_tp_two_ranks():
            "--master-addr", "127.0.0.1", "--master-port", "29653", str(worker)]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "TP_FUSED_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_engine_p2p_parameter_gather_two_ranks():
+    worker = Path(__file__).with_name("engine_p2p_worker.py")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", "29654", str(worker)]
+    r = subprocess.run(cmd, env=dict(os.environ), capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "ENGINE_P2P_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
