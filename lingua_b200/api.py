@@ -71,6 +71,7 @@ class Trainer:
             kw["doc_start"] = doc_start
         if doc_end is not None:
             kw["doc_end"] = doc_end
+        self.engine.defer_reduce = (self.acc_step + 1) % self.grad_acc_steps != 0
         loss = self.model(inputs, labels, **kw)
         (loss / self.grad_acc_steps if self.grad_acc_steps > 1 else loss).backward()
         self.acc_step = (self.acc_step + 1) % self.grad_acc_steps

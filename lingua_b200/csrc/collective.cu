@@ -157,3 +157,62 @@ extern "C" int lb_reduce_norm(const void* slots, int n_slots, long long slot_str
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;
 }
+
+// out[i] = scale * (own[i] + sum_s slots[s * slot_stride + i]); *sumsq += sum_i out[i]^2.
+// The reduce half of a reduce-scatter whose transfer half was done by the copy engines (every peer pushed its
+// fp32 gradient slice for this rank into one slot), fused with the squared-norm pass the optimiser needs.
+namespace lb {
+__global__ void __launch_bounds__(256)
+reduce_slots_kernel(const float* __restrict__ own, const float* __restrict__ slots, int n_slots, long long slot_stride,
+                    float* __restrict__ out, long long n, float scale, float* __restrict__ sumsq) {
+  float acc = 0.f;
+  const long long n4 = n / 4;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    float4 v = reinterpret_cast<const float4*>(own)[i];
+    for (int s = 0; s < n_slots; ++s) {
+      const float4 w = reinterpret_cast<const float4*>(slots + s * slot_stride)[i];
+      v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
+    }
+    v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
+    reinterpret_cast<float4*>(out)[i] = v;
+    acc += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  if (blockIdx.x == 0) {
+    for (long long i = n4 * 4 + threadIdx.x; i < n; i += blockDim.x) {
+      float v = own[i];
+      for (int s = 0; s < n_slots; ++s) v += slots[s * slot_stride + i];
+      v *= scale;
+      out[i] = v;
+      acc += v * v;
+    }
+  }
+  __shared__ float red[8];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0 && sumsq) {
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t += red[i];
+    atomicAdd(sumsq, t);
+  }
+}
+}  // namespace lb
+
+extern "C" int lb_reduce_slots(const float* own, const float* slots, int n_slots, long long slot_stride, float* out,
+                               long long n, float scale, float* sumsq, void* stream) {
+  if (!own || !out || n <= 0 || n_slots < 0 || (n_slots > 0 && !slots)) return 1;
+  if (reinterpret_cast<uintptr_t>(own) % 16 || reinterpret_cast<uintptr_t>(out) % 16 ||
+      reinterpret_cast<uintptr_t>(slots) % 16 || slot_stride % 4)
+    return 2;
+  long long blocks = (n / 4 + 255) / 256;
+  const long long cap = (long long)lb::num_sms() * 8;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  lb::reduce_slots_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      own, slots, n_slots, slot_stride, out, n, scale, sumsq);
+  lb::g_launches.fetch_add(1, std::memory_order_relaxed);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}

@@ -47,6 +47,8 @@ class ParamGroup:
                  compute_dtype: torch.dtype, device: torch.device, alloc_full: Optional[Callable] = None):
         self.name, self.params = name, params
         self.peer_full: Optional[List[torch.Tensor]] = None  # every rank's ``full`` buffer, when peer-visible
+        self.peer_stage: Optional[List[torch.Tensor]] = None  # every rank's reduce-scatter staging [world-1, shard]
+        self.rs_stage: Optional[torch.Tensor] = None
         self.world, self.rank = world, rank
         align = 64 * world  # every shard starts on a 256-byte boundary in fp32
         self.offsets: Dict[str, Tuple[int, int]] = {}
@@ -100,6 +102,9 @@ class ShardedEngine:
         self.compute_dtype = compute_dtype
         self.is_cuda = self.device.type == "cuda"
         self.step_count = 0
+        # True while micro-batches are still being accumulated: a group's backward must not start its
+        # gradient reduction before the last micro-batch has added its share
+        self.defer_reduce = False
         # side stream: gradient reduce-scatter / parameter all-gather, and each group's share of the
         # gradient norm, all of which overlap the backward pass of the groups that are still running
         self.comm_stream = torch.cuda.Stream(self.device, priority=-1) if self.is_cuda else None
@@ -156,11 +161,16 @@ class ShardedEngine:
             try:
                 hdl = self._symm.rendezvous(g.full, group=self.pg if self.pg is not None else dist.group.WORLD)
                 g.peer_full = [hdl.get_buffer(r, (g.padded,), self.compute_dtype) for r in range(self.world)]
-            except Exception as e:  # this group then uses the NCCL all-gather
+                # staging of the gradient reduce-scatter: slot k-1 of rank r receives the slice from rank r - k
+                g.rs_stage = self._symm.empty((self.world - 1) * g.shard_numel, dtype=torch.float32, device=self.device)
+                h2 = self._symm.rendezvous(g.rs_stage, group=self.pg if self.pg is not None else dist.group.WORLD)
+                g.peer_stage = [h2.get_buffer(r, (self.world - 1, g.shard_numel), torch.float32)
+                                for r in range(self.world)]
+            except Exception as e:  # this group then uses the NCCL collectives
                 import logging
 
                 logging.getLogger(__name__).warning("no peer view of group %s: %s", path, e)
-                g.peer_full = None
+                g.peer_full = g.peer_stage = None
         self.groups.append(g)
         for fqn, new_p in g.params:
             owner_path, _, attr = fqn.rpartition(".")
@@ -231,10 +241,21 @@ class ShardedEngine:
         if self.comm_stream is not None:
             self.comm_stream.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(self.comm_stream):
-                if self.world > 1:
-                    dist.reduce_scatter_tensor(g.grad_shard, g.grad, op=dist.ReduceOp.AVG, group=self.pg)
                 part.zero_()
-                F.sumsq(g.grad_shard, part)
+                if self.world > 1 and g.peer_stage is not None:
+                    # reduce-scatter by the copy engines: every rank pushes the slice owned by rank r into the
+                    # slot it has in r's staging buffer; after the barrier one kernel sums the slots with the
+                    # local slice, scales by 1 / world and accumulates the squared norm
+                    n = g.shard_numel
+                    for k in range(1, self.world):
+                        r = (self.rank + k) % self.world
+                        g.peer_stage[r][k - 1].copy_(g.grad[r * n:(r + 1) * n], non_blocking=True)
+                    self._peer_barrier()
+                    self._reduce_slots(g, part)
+                else:
+                    if self.world > 1:
+                        dist.reduce_scatter_tensor(g.grad_shard, g.grad, op=dist.ReduceOp.AVG, group=self.pg)
+                    F.sumsq(g.grad_shard, part)
                 g.grads_ready = torch.cuda.Event()
                 g.grads_ready.record(self.comm_stream)
             return
@@ -295,6 +316,23 @@ class ShardedEngine:
         else:
             dist.all_gather_into_tensor(g.full, g.full[g.shard_slice].clone(), group=self.pg)
 
+    def _reduce_slots(self, g: ParamGroup, part: torch.Tensor) -> None:
+        import ctypes as C
+
+        from ..ops import _lib
+
+        lib = _lib.load()
+        if not getattr(lib, "_reduce_slots_declared", False):
+            lib.lb_reduce_slots.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_longlong, C.c_void_p, C.c_longlong,
+                                            C.c_float, C.c_void_p, C.c_void_p]
+            lib.lb_reduce_slots.restype = C.c_int
+            lib._reduce_slots_declared = True
+        own = g.grad[g.shard_slice]
+        rc = lib.lb_reduce_slots(own.data_ptr(), g.rs_stage.data_ptr(), self.world - 1, g.shard_numel,
+                                 g.grad_shard.data_ptr(), g.shard_numel, 1.0 / self.world, part.data_ptr(),
+                                 _lib.stream_ptr())
+        _lib.check(rc, "lb_reduce_slots")
+
     def _peer_barrier(self) -> None:
         from .tp_fused import peer_barrier
 
@@ -340,5 +378,6 @@ class _Boundary(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, *grads):
-        ctx.engine.reduce_group(ctx.gi)
+        if not ctx.engine.defer_reduce:
+            ctx.engine.reduce_group(ctx.gi)
         return (None, None, *grads)

@@ -253,6 +253,7 @@ def run_training(args: TrainArgs, spec: ModelSpec) -> Dict[str, Any]:
                 with probe:
                     probe.metadata = {"it": train_state.step, "global_step": train_state.step, "loop": "lingua"}
                     saved_scale, model.loss_grad_scale = model.loss_grad_scale, None
+                    engine.defer_reduce = True  # these gradients are thrown away: no reduction
                     out = spec.loss_fn(model, input_ids[: max(1, bsz // 2)], labels[: max(1, bsz // 2)])
                     (out[0] if isinstance(out, tuple) else out).backward()
                     model.loss_grad_scale = saved_scale
@@ -260,6 +261,7 @@ def run_training(args: TrainArgs, spec: ModelSpec) -> Dict[str, Any]:
 
             if train_state.acc_step == (1 % args.grad_acc_steps) or args.grad_acc_steps == 1:
                 engine.zero_grad()
+            engine.defer_reduce = train_state.acc_step != 0  # reduce only after the last micro-batch
             out = spec.loss_fn(model, input_ids, labels)
             loss, extra_losses = out if isinstance(out, tuple) else (out, {})
             (loss / args.grad_acc_steps if args.grad_acc_steps > 1 else loss).backward()
