@@ -24,9 +24,9 @@ def run(p2p: bool, rank: int, world: int, dev):
     assert (tr.engine.groups[0].peer_full is not None) == p2p
     g = torch.Generator().manual_seed(100 + rank)
     losses = []
-    for _ in range(5):
-        tok = torch.randint(0, 1024, (2, 257), generator=g)
-        batch = torch.stack((tok[:, :-1], tok[:, 1:]), dim=-1)
+    tok = torch.randint(0, 1024, (2, 257), generator=g)  # one batch per rank, repeated: the loss must go down
+    batch = torch.stack((tok[:, :-1], tok[:, 1:]), dim=-1)
+    for _ in range(6):
         losses.append(tr.train_step(batch))
     tr.engine.wait_all_params()
     torch.cuda.synchronize()
