@@ -168,13 +168,15 @@ reduce_slots_kernel(const float* __restrict__ own, const float* __restrict__ slo
   float acc = 0.f;
   const long long n4 = n / 4;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
-    float4 v = reinterpret_cast<const float4*>(own)[i];
+    // streaming accesses (evict first): the kernel runs next to the backward GEMMs, whose operand tiles
+    // should stay in L2
+    float4 v = __ldcs(reinterpret_cast<const float4*>(own) + i);
     for (int s = 0; s < n_slots; ++s) {
-      const float4 w = reinterpret_cast<const float4*>(slots + s * slot_stride)[i];
+      const float4 w = __ldcs(reinterpret_cast<const float4*>(slots + s * slot_stride) + i);
       v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
     }
     v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
-    reinterpret_cast<float4*>(out)[i] = v;
+    __stcs(reinterpret_cast<float4*>(out) + i, v);
     acc += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
   }
   if (blockIdx.x == 0) {

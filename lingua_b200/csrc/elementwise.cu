@@ -459,7 +459,9 @@ __global__ void __launch_bounds__(512) sumsq_kernel(const float* __restrict__ g,
   const long long n4 = n / 4;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4;
        i += (long long)gridDim.x * blockDim.x) {
-    const float4 v = reinterpret_cast<const float4*>(g)[i];
+    // streaming load (evict first): this pass runs next to the GEMMs of the backward pass and must not
+    // push their operand tiles out of L2
+    const float4 v = __ldcs(reinterpret_cast<const float4*>(g) + i);
     s += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
   }
   if (blockIdx.x == 0)
