@@ -21,6 +21,7 @@ struct BarrierParams {
   int world, rank;
   uint32_t epoch;
   uint32_t* status;
+  unsigned long long limit_ns;
 };
 
 __global__ void peer_barrier_kernel(const BarrierParams p) {
@@ -38,7 +39,7 @@ __global__ void peer_barrier_kernel(const BarrierParams p) {
     if ((it & 0xFFu) == 0xFFu) {
       const uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      if (now - t0 > LB_WAIT_LIMIT_NS) {
+      if (now - t0 > p.limit_ns) {
         if (p.status) atomicOr(p.status, ST_TIMEOUT_FLAG | 7u);
         break;
       }
@@ -131,10 +132,21 @@ reduce_norm_kernel(const __nv_bfloat16* __restrict__ slots, int n_slots, long lo
 
 }  // namespace lb
 
+extern "C" int lb_peer_barrier_limit(void* const* pads, int world, int rank, uint32_t epoch, uint32_t* status,
+                                     unsigned long long limit_ns, void* stream);
+
 extern "C" int lb_peer_barrier(void* const* pads, int world, int rank, uint32_t epoch, uint32_t* status,
                                void* stream) {
+  return lb_peer_barrier_limit(pads, world, rank, epoch, status, LB_WAIT_LIMIT_NS, stream);
+}
+
+// Same with an explicit wait limit: ranks of a training job may drift apart by more than the default limit
+// (a slow data loader, a checkpoint write) without anything being wrong.
+extern "C" int lb_peer_barrier_limit(void* const* pads, int world, int rank, uint32_t epoch, uint32_t* status,
+                                     unsigned long long limit_ns, void* stream) {
   if (!pads || world < 1 || world > LB_MAX_PEERS || rank < 0 || rank >= world) return 1;
   lb::BarrierParams p;
+  p.limit_ns = limit_ns;
   for (int r = 0; r < LB_MAX_PEERS; ++r) p.pads[r] = reinterpret_cast<uint32_t*>(pads[r < world ? r : 0]);
   p.world = world; p.rank = rank; p.epoch = epoch; p.status = status;
   lb::peer_barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);

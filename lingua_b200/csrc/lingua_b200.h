@@ -132,6 +132,13 @@ int lb_gemm_tp(const LbTpGemmArgs* a, void* stream);
 // (uint32[world], zero before first use); epoch is the number of this barrier on these pads,
 // counted from 1 by every rank alike. Bounded wait: on timeout the status word is set.
 int lb_peer_barrier(void* const* pads, int world, int rank, uint32_t epoch, uint32_t* status, void* stream);
+// Same with the wait limit given in nanoseconds (the default is 2 s).
+int lb_peer_barrier_limit(void* const* pads, int world, int rank, uint32_t epoch, uint32_t* status,
+                          unsigned long long limit_ns, void* stream);
+// out[i] = scale * (own[i] + sum_s slots[s * slot_stride + i]), *sumsq += sum out[i]^2 (fp32, n elements):
+// the reduction half of a reduce-scatter whose slots were filled by peer copies.
+int lb_reduce_slots(const float* own, const float* slots, int n_slots, long long slot_stride, float* out,
+                    long long n, float scale, float* sumsq, void* stream);
 
 // h = resid + sum_s slots[s] (bf16 [rows, D] each, slot_stride elements apart), y = RMSNorm(h) * w.
 // resid, h_out, y_out (with w) and rstd_out are optional. D % 8 == 0, D <= 8192.

@@ -337,7 +337,8 @@ class ShardedEngine:
         from .tp_fused import peer_barrier
 
         self._barrier_epoch += 1
-        peer_barrier(self._pad_ptrs, self.rank, self._barrier_epoch)
+        # ranks of a training job drift (data loading, logging, checkpoints): generous but finite limit
+        peer_barrier(self._pad_ptrs, self.rank, self._barrier_epoch, limit_s=120.0)
 
     def wait_all_params(self) -> None:
         for gi in range(len(self.groups)):

@@ -58,6 +58,9 @@ def _lib_tp():
         lib.lb_gemm_tp.restype = C.c_int
         lib.lb_peer_barrier.argtypes = [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_uint32, C.c_void_p, C.c_void_p]
         lib.lb_peer_barrier.restype = C.c_int
+        lib.lb_peer_barrier_limit.argtypes = [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_uint32, C.c_void_p,
+                                              C.c_ulonglong, C.c_void_p]
+        lib.lb_peer_barrier_limit.restype = C.c_int
         lib.lb_reduce_norm.argtypes = [C.c_void_p, C.c_int, C.c_longlong, C.c_void_p, C.c_void_p, C.c_float,
                                        C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int, C.c_void_p]
         lib.lb_reduce_norm.restype = C.c_int
@@ -140,10 +143,11 @@ def reduce_norm(slots: torch.Tensor, resid: Optional[torch.Tensor], w: Optional[
     return h_out, (y_out if w is not None else None)
 
 
-def peer_barrier(pad_ptrs: Sequence[int], rank: int, epoch: int) -> None:
+def peer_barrier(pad_ptrs: Sequence[int], rank: int, epoch: int, limit_s: float = 2.0) -> None:
+    """All ranks meet; ``limit_s`` bounds the wait (on expiry the status word is set and the kernel returns)."""
     arr = (C.c_void_p * len(pad_ptrs))(*pad_ptrs)
-    rc = _lib_tp().lb_peer_barrier(arr, len(pad_ptrs), rank, epoch & 0xFFFFFFFF, _lib.status_word().data_ptr(),
-                                   _lib.stream_ptr())
+    rc = _lib_tp().lb_peer_barrier_limit(arr, len(pad_ptrs), rank, epoch & 0xFFFFFFFF, _lib.status_word().data_ptr(),
+                                         int(limit_s * 1e9), _lib.stream_ptr())
     _lib.check(rc, "lb_peer_barrier")
 
 
