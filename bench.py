@@ -223,7 +223,10 @@ def main() -> None:
             # memory (every rank must agree), else recompute the cheap activations
             dev_batches = [views(h).to(dev) for h in host]
             tr = None
-            for sac in ([a.sac == "on"] if a.sac != "auto" else [False, True]):
+            sacs = [a.sac == "on"] if a.sac != "auto" else [False, True]
+            # collectives through NVLink copy engines first; the NCCL path is the fallback if that set-up fails
+            trials = [(sac, p2p) for p2p in ((True, False) if world > 1 else (False,)) for sac in sacs]
+            for sac, p2p in trials:
                 fits = 1
                 try:
                     if other:
@@ -237,14 +240,20 @@ def main() -> None:
                         margs, kw = LMTransformerArgs(**mcfg), {}
                     tr = Trainer(margs,
                                  DistributedArgs(dp_shard=world, fsdp_type="full_shard",
-                                                 selective_activation_checkpointing=sac,
+                                                 selective_activation_checkpointing=sac, p2p_param_gather=p2p,
                                                  float8_recipe="rowwise" if a.float8 else None),
                                  OptimArgs(lr=1e-3, warmup=2000, clip=1.0), total_steps=100000, device=dev, **kw)
                     if other:  # 6 * non-embedding parameters (the reference logs no FLOPS for these models)
                         fpt = 6.0 * (tr.engine.n_params - mcfg["vocab_size"] * mcfg["dim"])
                     tr.train_step_async(dev_batches[0])  # first step: allocator growth
                     torch.cuda.synchronize()
+                    _lib.check_status()
                 except torch.OutOfMemoryError:
+                    fits = 0
+                except Exception as e:  # e.g. no peer access between the ranks
+                    if not p2p:
+                        raise
+                    extra["p2p_fallback"] = f"{type(e).__name__}: {str(e)[:120]}"
                     fits = 0
                 if world > 1:
                     t_ok = torch.tensor([fits], device=dev)
@@ -259,6 +268,8 @@ def main() -> None:
             if tr is None:
                 raise torch.OutOfMemoryError("the training step does not fit with or without activation recomputation")
             extra["selective_activation_checkpointing"] = sac
+            extra["collectives"] = ("nvlink copy engines + reduce kernel" if (world > 1 and tr.engine.groups[0].peer_full
+                                                                              is not None) else "nccl" if world > 1 else "none")
             host_batches = [views(h).contiguous().pin_memory() for h in host]
 
             def dev_step(i):
