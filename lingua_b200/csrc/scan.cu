@@ -101,108 +101,173 @@ __global__ void conv1d_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __n
 }
 
 // ------------------------------------------------------------------ linear recurrence
+// Every thread owns V adjacent channels (V = 2: one 4-byte load per tensor and step, a warp covers 128 bytes
+// per row; V = 1 for odd channel counts).
+template <int V>
+__device__ __forceinline__ void ldv(const __nv_bfloat16* p, float (&f)[V]) {
+  if (V == 2) {
+    const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+    f[0] = v.x;
+    f[V - 1] = v.y;
+  } else {
+    f[0] = __bfloat162float(*p);
+  }
+}
+template <int V>
+__device__ __forceinline__ void stv(__nv_bfloat16* p, const float (&f)[V]) {
+  if (V == 2)
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(f[0], f[V - 1]);
+  else
+    *p = __float2bfloat16(f[0]);
+}
+
 // Forward pass 1: per (b, chunk, c): A = prod a, H = local end state (zero carry). A document
 // start inside the chunk cuts the product (a is taken as 0 at the first token of a document).
+template <int V>
 __global__ void scan_reduce_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ bb,
                                    const int* __restrict__ doc_start, float* __restrict__ agg_a,
                                    float* __restrict__ agg_h, int B, int S, int C, int n_chunks, int reverse,
                                    const __nv_bfloat16* __restrict__ shifted_a) {
-  const long long total = (long long)B * n_chunks * C;
+  const int CV = C / V;
+  const long long total = (long long)B * n_chunks * CV;
   const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   if (i >= total) return;
-  const int c = i % C;
-  const long long bk = i / C;
+  const int c = (i % CV) * V;
+  const long long bk = i / CV;
   const int k = bk % n_chunks;
   const int b = bk / n_chunks;
   const int s0 = k * SCAN_CHUNK, s1 = min(S, s0 + SCAN_CHUNK);
-  float A = 1.f, H = 0.f;
+  float A[V], H[V];
+#pragma unroll
+  for (int v = 0; v < V; ++v) { A[v] = 1.f; H[v] = 0.f; }
   if (!reverse) {
     for (int s = s0; s < s1; ++s) {
       const long long idx = ((long long)b * S + s) * C + c;
-      float av = bf2f(a[idx]);
-      if (doc_start && doc_start[(long long)b * S + s] == s) av = 0.f;
-      H = av * H + bf2f(bb[idx]);
-      A *= av;
+      float av[V], bv[V];
+      ldv<V>(a + idx, av);
+      ldv<V>(bb + idx, bv);
+      const bool cut = doc_start && doc_start[(long long)b * S + s] == s;
+#pragma unroll
+      for (int v = 0; v < V; ++v) {
+        const float x = cut ? 0.f : av[v];
+        H[v] = x * H[v] + bv[v];
+        A[v] *= x;
+      }
     }
   } else {
     // reverse recurrence g_s = dh_s + a_{s+1} g_{s+1}: coefficient of step s is a_{s+1} (0 past the
     // end or when s+1 starts a new document)
     for (int s = s1 - 1; s >= s0; --s) {
       const long long idx = ((long long)b * S + s) * C + c;
-      float av = 0.f;
-      if (s + 1 < S && !(doc_start && doc_start[(long long)b * S + s + 1] == s + 1))
-        av = bf2f(shifted_a[idx + C]);
-      H = av * H + bf2f(bb[idx]);
-      A *= av;
+      float av[V], bv[V];
+#pragma unroll
+      for (int v = 0; v < V; ++v) av[v] = 0.f;
+      if (s + 1 < S && !(doc_start && doc_start[(long long)b * S + s + 1] == s + 1)) ldv<V>(shifted_a + idx + C, av);
+      ldv<V>(bb + idx, bv);
+#pragma unroll
+      for (int v = 0; v < V; ++v) {
+        H[v] = av[v] * H[v] + bv[v];
+        A[v] *= av[v];
+      }
     }
   }
-  agg_a[i] = A;
-  agg_h[i] = H;
+  const long long o = bk * C + c;
+#pragma unroll
+  for (int v = 0; v < V; ++v) {
+    agg_a[o + v] = A[v];
+    agg_h[o + v] = H[v];
+  }
 }
 
 // Forward pass 2: fold the aggregates of the earlier chunks into a carry, then replay.
 // mode 0: h (bf16) out. Optionally h0 [B, C] initial state and h_last [B, C] final state.
+template <int V>
 __global__ void scan_apply_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ bb,
                                   const int* __restrict__ doc_start, const float* __restrict__ agg_a,
                                   const float* __restrict__ agg_h, const float* __restrict__ h0,
                                   __nv_bfloat16* __restrict__ h, float* __restrict__ h_last, int B, int S, int C,
                                   int n_chunks) {
-  const long long total = (long long)B * n_chunks * C;
+  const int CV = C / V;
+  const long long total = (long long)B * n_chunks * CV;
   const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   if (i >= total) return;
-  const int c = i % C;
-  const long long bk = i / C;
+  const int c = (i % CV) * V;
+  const long long bk = i / CV;
   const int k = bk % n_chunks;
   const int b = bk / n_chunks;
-  float carry = h0 ? h0[(long long)b * C + c] : 0.f;
+  float H[V];
+#pragma unroll
+  for (int v = 0; v < V; ++v) H[v] = h0 ? h0[(long long)b * C + c + v] : 0.f;
   for (int kk = 0; kk < k; ++kk) {
     const long long j = ((long long)b * n_chunks + kk) * C + c;
-    carry = agg_a[j] * carry + agg_h[j];
+#pragma unroll
+    for (int v = 0; v < V; ++v) H[v] = agg_a[j + v] * H[v] + agg_h[j + v];
   }
   const int s0 = k * SCAN_CHUNK, s1 = min(S, s0 + SCAN_CHUNK);
-  float H = carry;
   for (int s = s0; s < s1; ++s) {
     const long long idx = ((long long)b * S + s) * C + c;
-    float av = bf2f(a[idx]);
-    if (doc_start && doc_start[(long long)b * S + s] == s) av = 0.f;
-    H = av * H + bf2f(bb[idx]);
-    h[idx] = __float2bfloat16(H);
+    float av[V], bv[V];
+    ldv<V>(a + idx, av);
+    ldv<V>(bb + idx, bv);
+    const bool cut = doc_start && doc_start[(long long)b * S + s] == s;
+#pragma unroll
+    for (int v = 0; v < V; ++v) H[v] = (cut ? 0.f : av[v]) * H[v] + bv[v];
+    stv<V>(h + idx, H);
   }
-  if (h_last && k == n_chunks - 1) h_last[(long long)b * C + c] = H;
+  if (h_last && k == n_chunks - 1) {
+#pragma unroll
+    for (int v = 0; v < V; ++v) h_last[(long long)b * C + c + v] = H[v];
+  }
 }
 
 // Backward pass 2: g_s = dh_s + a_{s+1} g_{s+1} (reverse); db_s = g_s; da_s = g_s * h_{s-1}
 // (h_{-1} = h0 or 0; 0 at a document start).
+template <int V>
 __global__ void scan_bwd_apply_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ h,
                                       const __nv_bfloat16* __restrict__ dh, const int* __restrict__ doc_start,
                                       const float* __restrict__ agg_a, const float* __restrict__ agg_h,
                                       const float* __restrict__ h0, __nv_bfloat16* __restrict__ da,
                                       __nv_bfloat16* __restrict__ db, int B, int S, int C, int n_chunks) {
-  const long long total = (long long)B * n_chunks * C;
+  const int CV = C / V;
+  const long long total = (long long)B * n_chunks * CV;
   const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   if (i >= total) return;
-  const int c = i % C;
-  const long long bk = i / C;
+  const int c = (i % CV) * V;
+  const long long bk = i / CV;
   const int k = bk % n_chunks;
   const int b = bk / n_chunks;
-  float carry = 0.f;
+  float G[V];
+#pragma unroll
+  for (int v = 0; v < V; ++v) G[v] = 0.f;
   for (int kk = n_chunks - 1; kk > k; --kk) {
     const long long j = ((long long)b * n_chunks + kk) * C + c;
-    carry = agg_a[j] * carry + agg_h[j];
+#pragma unroll
+    for (int v = 0; v < V; ++v) G[v] = agg_a[j + v] * G[v] + agg_h[j + v];
   }
   const int s0 = k * SCAN_CHUNK, s1 = min(S, s0 + SCAN_CHUNK);
-  float G = carry;
   for (int s = s1 - 1; s >= s0; --s) {
     const long long idx = ((long long)b * S + s) * C + c;
-    float av = 0.f;
-    if (s + 1 < S && !(doc_start && doc_start[(long long)b * S + s + 1] == s + 1)) av = bf2f(a[idx + C]);
-    G = av * G + bf2f(dh[idx]);
-    db[idx] = __float2bfloat16(G);
+    float av[V], dv[V], hp[V], o[V];
+#pragma unroll
+    for (int v = 0; v < V; ++v) { av[v] = 0.f; hp[v] = 0.f; }
+    if (s + 1 < S && !(doc_start && doc_start[(long long)b * S + s + 1] == s + 1)) ldv<V>(a + idx + C, av);
+    ldv<V>(dh + idx, dv);
+#pragma unroll
+    for (int v = 0; v < V; ++v) G[v] = av[v] * G[v] + dv[v];
+    stv<V>(db + idx, G);
     // forward took a_s = 0 at the first token of a document: no gradient flows into it
     const bool cut = doc_start && doc_start[(long long)b * S + s] == s;
-    float hprev = 0.f;
-    if (!cut) hprev = s > 0 ? bf2f(h[idx - C]) : (h0 ? h0[(long long)b * C + c] : 0.f);
-    da[idx] = __float2bfloat16(G * hprev);
+    if (!cut) {
+      if (s > 0) {
+        ldv<V>(h + idx - C, hp);
+      } else if (h0) {
+#pragma unroll
+        for (int v = 0; v < V; ++v) hp[v] = h0[(long long)b * C + c + v];
+      }
+    }
+#pragma unroll
+    for (int v = 0; v < V; ++v) o[v] = G[v] * hp[v];
+    stv<V>(da + idx, o);
   }
 }
 
@@ -287,10 +352,17 @@ extern "C" int lb_scan_fwd(const void* a, const void* b, const int* doc_start, c
   float* agg_a = scratch;
   float* agg_h = scratch + n;
   cudaStream_t st = (cudaStream_t)stream;
-  scan_reduce_kernel<<<blocks_for(n, 256), 256, 0, st>>>((const bf16*)a, (const bf16*)b, doc_start, agg_a, agg_h, B,
-                                                         S, C, n_chunks, 0, nullptr);
-  scan_apply_kernel<<<blocks_for(n, 256), 256, 0, st>>>((const bf16*)a, (const bf16*)b, doc_start, agg_a, agg_h, h0,
-                                                        (bf16*)h, h_last, B, S, C, n_chunks);
+  if (C % 2 == 0) {
+    scan_reduce_kernel<2><<<blocks_for(n / 2, 256), 256, 0, st>>>((const bf16*)a, (const bf16*)b, doc_start, agg_a,
+                                                                  agg_h, B, S, C, n_chunks, 0, nullptr);
+    scan_apply_kernel<2><<<blocks_for(n / 2, 256), 256, 0, st>>>((const bf16*)a, (const bf16*)b, doc_start, agg_a,
+                                                                 agg_h, h0, (bf16*)h, h_last, B, S, C, n_chunks);
+  } else {
+    scan_reduce_kernel<1><<<blocks_for(n, 256), 256, 0, st>>>((const bf16*)a, (const bf16*)b, doc_start, agg_a,
+                                                              agg_h, B, S, C, n_chunks, 0, nullptr);
+    scan_apply_kernel<1><<<blocks_for(n, 256), 256, 0, st>>>((const bf16*)a, (const bf16*)b, doc_start, agg_a, agg_h,
+                                                             h0, (bf16*)h, h_last, B, S, C, n_chunks);
+  }
   g_launches.fetch_add(2, std::memory_order_relaxed);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;
@@ -304,11 +376,19 @@ extern "C" int lb_scan_bwd(const void* a, const void* h, const void* dh, const i
   float* agg_a = scratch;
   float* agg_h = scratch + n;
   cudaStream_t st = (cudaStream_t)stream;
-  scan_reduce_kernel<<<blocks_for(n, 256), 256, 0, st>>>(nullptr, (const bf16*)dh, doc_start, agg_a, agg_h, B, S, C,
-                                                         n_chunks, 1, (const bf16*)a);
-  scan_bwd_apply_kernel<<<blocks_for(n, 256), 256, 0, st>>>((const bf16*)a, (const bf16*)h, (const bf16*)dh,
-                                                            doc_start, agg_a, agg_h, h0, (bf16*)da, (bf16*)db, B, S,
-                                                            C, n_chunks);
+  if (C % 2 == 0) {
+    scan_reduce_kernel<2><<<blocks_for(n / 2, 256), 256, 0, st>>>(nullptr, (const bf16*)dh, doc_start, agg_a, agg_h,
+                                                                  B, S, C, n_chunks, 1, (const bf16*)a);
+    scan_bwd_apply_kernel<2><<<blocks_for(n / 2, 256), 256, 0, st>>>((const bf16*)a, (const bf16*)h, (const bf16*)dh,
+                                                                     doc_start, agg_a, agg_h, h0, (bf16*)da,
+                                                                     (bf16*)db, B, S, C, n_chunks);
+  } else {
+    scan_reduce_kernel<1><<<blocks_for(n, 256), 256, 0, st>>>(nullptr, (const bf16*)dh, doc_start, agg_a, agg_h, B, S,
+                                                              C, n_chunks, 1, (const bf16*)a);
+    scan_bwd_apply_kernel<1><<<blocks_for(n, 256), 256, 0, st>>>((const bf16*)a, (const bf16*)h, (const bf16*)dh,
+                                                                 doc_start, agg_a, agg_h, h0, (bf16*)da, (bf16*)db, B,
+                                                                 S, C, n_chunks);
+  }
   g_launches.fetch_add(2, std::memory_order_relaxed);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;

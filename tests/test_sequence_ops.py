@@ -88,9 +88,10 @@ def test_conv1d_kernels(W, with_docs, C):
 @pytest.mark.gpu
 @pytest.mark.parametrize("S", [64, 200, 1024])
 @pytest.mark.parametrize("with_docs", [False, True])
-def test_scan_kernels(S, with_docs):
+@pytest.mark.parametrize("C", [136, 75])  # two channels per thread / one
+def test_scan_kernels(S, with_docs, C):
     torch.manual_seed(1)
-    B, C = 2, 136
+    B = 2
     a = torch.rand(B, S, C, device="cuda").mul(0.3).add(0.69).bfloat16()
     b = torch.randn(B, S, C, device="cuda", dtype=torch.bfloat16)
     ds = _docs(B, S, seed=3).cuda() if with_docs else None
