@@ -286,7 +286,7 @@ extern "C" int lb_conv1d_fwd(const void* x, const void* w, const int* doc_start,
   if (C % 8 == 0 && ldx % 8 == 0 && ldy % 8 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 &&
       reinterpret_cast<uintptr_t>(y) % 16 == 0 && W >= 2 && W <= 4) {
     const long long n_rows = (long long)B * S;
-    dim3 vgrid((C / 8 + 127) / 128, (unsigned)((n_rows + CONV_ROWS - 1) / CONV_ROWS));
+    dim3 vgrid((C / CONV_NV + 127) / 128, (unsigned)((n_rows + CONV_ROWS - 1) / CONV_ROWS));
     switch (W) {
       case 2: conv1d_fwd_vec_kernel<2><<<vgrid, 128, 0, st>>>((const bf16*)x, (const bf16*)w, doc_start, (bf16*)y, n_rows, S, C, ldx, ldy, act); break;
       case 3: conv1d_fwd_vec_kernel<3><<<vgrid, 128, 0, st>>>((const bf16*)x, (const bf16*)w, doc_start, (bf16*)y, n_rows, S, C, ldx, ldy, act); break;
@@ -319,7 +319,7 @@ extern "C" int lb_conv1d_bwd(const void* x, const void* w, const int* doc_start,
   if (C % 8 == 0 && ldx % 8 == 0 && ldy % 8 == 0 && lddx % 8 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 &&
       reinterpret_cast<uintptr_t>(dy) % 16 == 0 && reinterpret_cast<uintptr_t>(dx) % 16 == 0 && W >= 2 && W <= 4) {
     const long long n_rows = (long long)B * S;
-    dim3 vgrid((C / 8 + 127) / 128, (unsigned)((n_rows + CONV_ROWS - 1) / CONV_ROWS));
+    dim3 vgrid((C / CONV_NV + 127) / 128, (unsigned)((n_rows + CONV_ROWS - 1) / CONV_ROWS));
     switch (W) {
       case 2: conv1d_bwd_vec_kernel<2><<<vgrid, 128, 0, st>>>((const bf16*)x, (const bf16*)w, doc_start, (const bf16*)dy, (bf16*)dx, dw, n_rows, S, C, ldx, ldy, lddx, act); break;
       case 3: conv1d_bwd_vec_kernel<3><<<vgrid, 128, 0, st>>>((const bf16*)x, (const bf16*)w, doc_start, (const bf16*)dy, (bf16*)dx, dw, n_rows, S, C, ldx, ldy, lddx, act); break;
