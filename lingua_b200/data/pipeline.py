@@ -29,6 +29,7 @@ from typing import Any, Dict, Iterator, Optional
 import numpy as np
 
 from ..tokenizer import TokenizerArgs, build_tokenizer
+from .regex_cutting import RegexArgs
 
 logger = logging.getLogger()
 
@@ -85,8 +86,25 @@ def choose_source(source_to_iterator, source_to_state, root_dir, sources, rng_st
                         rng_state=rng.bit_generator.state)
 
 
-def tokenize(iterator, add_bos: bool, add_eos: bool, tokenizer_type: str, tokenizer_path: Optional[str] = None):
+LEVEL_SHIFT = 32  # a token and its pooling level travel through the pipeline as ``token | level << 32``
+
+
+def split_levels(batch):
+    """Undo the packing done by ``tokenize(..., regex=...)``: (token ids, pooling levels)."""
+    return batch & ((1 << LEVEL_SHIFT) - 1), batch >> LEVEL_SHIFT
+
+
+def tokenize(iterator, add_bos: bool, add_eos: bool, tokenizer_type: str, tokenizer_path: Optional[str] = None,
+             regex: Optional[dict] = None):
+    """Documents -> token lists. With ``regex`` (a pooling strategy, apps/aunet/data/data.py:231-253 of the
+    reference) the byte tokenizer is required and every token carries its pooling level in its upper bits;
+    the first token of a document (its <bos>) gets the deepest level found in that document."""
     tok = build_tokenizer(tokenizer_type, tokenizer_path)
+    pool = None
+    if regex:
+        from .regex_cutting import RegexArgs, RegexPool
+
+        pool = RegexPool(RegexArgs(strategy=dict(regex.get("strategy", regex))))
     for content, st in iterator:
         if "text" in content:
             text = content["text"]
@@ -94,8 +112,16 @@ def tokenize(iterator, add_bos: bool, add_eos: bool, tokenizer_type: str, tokeni
             text = content["content"]
         else:
             raise AssertionError("JSON line must contain either text or content key")
-        yield tok.encode(text, add_bos=add_bos, add_eos=add_eos), dict(
-            it_state=st, add_bos=add_bos, add_eos=add_eos, name=tokenizer_type, path=tokenizer_path)
+        tokens = tok.encode(text, add_bos=add_bos, add_eos=add_eos)
+        if pool is not None:
+            body = pool.text_levels(text)
+            levels = np.zeros(len(tokens), dtype=np.int64)
+            assert len(body) + int(add_bos) + int(add_eos) == len(tokens), "regex pooling needs the byte tokenizer"
+            levels[int(add_bos):int(add_bos) + len(body)] = body
+            levels[0] = max(body) if body and max(body) > 0 else pool.n_levels
+            tokens = (np.asarray(tokens, dtype=np.int64) | (levels << LEVEL_SHIFT)).tolist()
+        yield tokens, dict(it_state=st, add_bos=add_bos, add_eos=add_eos, name=tokenizer_type, path=tokenizer_path,
+                           **({"regex": regex} if regex else {}))
 
 
 # ----------------------------------------------------------------------------- packing
@@ -214,9 +240,11 @@ def init_choice_state(root_dir, sources, seed, rank, world_size, file_pattern):
 
 
 def init_state(root_dir, sources, batch_size, prefetch_size, seq_len, n_views, seed, rank, world_size, add_bos,
-               add_eos, tokenizer_name, tokenizer_path=None, file_pattern=TRAIN_DATA_FILE_PATTERN):
+               add_eos, tokenizer_name, tokenizer_path=None, file_pattern=TRAIN_DATA_FILE_PATTERN, regex=None):
     multi = init_choice_state(root_dir, sources, seed, rank, world_size, file_pattern)
     tok = dict(it_state=multi, add_bos=add_bos, add_eos=add_eos, name=tokenizer_name, path=tokenizer_path)
+    if regex:
+        tok["regex"] = regex
     pack = dict(start_token=0, it_state=tok, output_seq_len=seq_len, n_views=n_views, seq_len=0)
     rng_state = np.random.default_rng((seed + 1, rank, world_size)).bit_generator.state
     return dict(it_state=pack, seq_idx=0, rng_state=rng_state, batch_size=batch_size, prefetch_size=prefetch_size)
@@ -245,7 +273,8 @@ def build_dataloader(state: dict):
     multi = tok_state["it_state"]
     srcs = setup_sources(multi)
     it = choose_source(srcs, multi["source_to_state"], multi["root_dir"], multi["sources"], multi["rng_state"])
-    it = tokenize(it, tok_state["add_bos"], tok_state["add_eos"], tok_state["name"], tok_state["path"])
+    it = tokenize(it, tok_state["add_bos"], tok_state["add_eos"], tok_state["name"], tok_state["path"],
+                  tok_state.get("regex"))
     it = pack_tokens(it, pack_state)
     it = batch_and_shuffle_prefetched_sequences(it, state["batch_size"], state["prefetch_size"],
                                                 pack_state["output_seq_len"], pack_state["n_views"], state)
@@ -267,15 +296,22 @@ def synthetic_batches(state: dict):
     while True:
         rng = np.random.default_rng((cfg["seed"], cfg["rank"], cfg["world_size"], step))
         stream = rng.integers(0, vocab, size=(bs, sl + nv - 1), dtype=np.int64)
+        probs = cfg.get("level_probs")
+        if probs:  # pooling levels: level >= l with probability probs[l-1]; every row starts at the deepest level
+            u = rng.random(size=stream.shape)
+            levels = sum((u < p).astype(np.int64) for p in probs)
+            levels[:, 0] = len(probs)
+            stream = stream | (levels << LEVEL_SHIFT)
         batch = np.lib.stride_tricks.sliding_window_view(stream, nv, axis=1).copy()
         step += 1
         yield batch, {**state, "seq_idx": step}
 
 
-def init_synthetic_state(batch_size, seq_len, n_views, vocab_size, seed, rank, world_size):
-    return dict(it_state=None, seq_idx=0, rng_state=None, batch_size=batch_size, prefetch_size=1,
-                synthetic=dict(seq_len=seq_len, n_views=n_views, vocab_size=vocab_size, seed=seed, rank=rank,
-                               world_size=world_size))
+def init_synthetic_state(batch_size, seq_len, n_views, vocab_size, seed, rank, world_size, level_probs=None):
+    cfg = dict(seq_len=seq_len, n_views=n_views, vocab_size=vocab_size, seed=seed, rank=rank, world_size=world_size)
+    if level_probs:
+        cfg["level_probs"] = sorted((float(p) for p in level_probs), reverse=True)
+    return dict(it_state=None, seq_idx=0, rng_state=None, batch_size=batch_size, prefetch_size=1, synthetic=cfg)
 
 
 # ----------------------------------------------------------------------------- async
@@ -339,18 +375,24 @@ class DataArgs:
     load_async: bool = True
     prefetch_size: int = 64
     tokenizer: TokenizerArgs = field(default_factory=TokenizerArgs)
+    # hierarchical byte models: pooling strategy, one rule per level (apps/aunet/data/data.py:746 of the reference)
+    regex: Optional[RegexArgs] = None
 
 
 def init_dataloader_state_from_args(args: DataArgs, rank: int, world_size: int, vocab_size: Optional[int] = None):
     """``sources: {synthetic: 1.0}`` with no root_dir selects the uniform-random token source."""
     if args.root_dir is None and list(args.sources.keys()) == ["synthetic"]:
         assert vocab_size is not None and vocab_size > 0
+        probs = None
+        if args.regex is not None and args.regex.strategy:  # word-like boundary rates, thinning with depth
+            probs = [0.2 * 0.3 ** l for l in range(len(args.regex.strategy))]
         return init_synthetic_state(args.batch_size, args.seq_len, args.n_views, vocab_size, args.seed, rank,
-                                    world_size)
+                                    world_size, level_probs=probs)
+    regex = {"strategy": dict(args.regex.strategy)} if args.regex is not None and args.regex.strategy else None
     return init_state(root_dir=args.root_dir, sources=args.sources, seq_len=args.seq_len,
                       batch_size=args.batch_size, prefetch_size=args.prefetch_size, n_views=args.n_views,
                       seed=args.seed, rank=rank, world_size=world_size, tokenizer_name=args.tokenizer.name,
-                      tokenizer_path=args.tokenizer.path, add_bos=args.add_bos, add_eos=args.add_eos)
+                      tokenizer_path=args.tokenizer.path, add_bos=args.add_bos, add_eos=args.add_eos, regex=regex)
 
 
 def build_dataloader_from_args(args: DataArgs, state: Optional[dict] = None):

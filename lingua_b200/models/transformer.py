@@ -191,7 +191,10 @@ class Attention(nn.Module):
         if self.kv_cache is not None:
             out = self.wo(self.kv_cache.attend(q, k, v, tok_idx).reshape(B, S, -1))
             return ReduceFwd.apply(out, tpg) if tpg is not None else out
-        o = _attention_torch(q, k, v, causal, doc_start, window)
+        if q.is_cuda and q.dtype == torch.bfloat16 and doc_start is None and self.head_dim <= 128:
+            o = _attention_flash_padded(q, k, v, causal, window)
+        else:
+            o = _attention_torch(q, k, v, causal, doc_start, window)
         out = self.wo(o.reshape(B, S, self.n_heads * self.head_dim))
         return ReduceFwd.apply(out, tpg) if tpg is not None else out
 
@@ -200,6 +203,19 @@ class Attention(nn.Module):
         for w in (self.wq, self.wk, self.wv):
             _init_linear(w, std)
         _init_linear(self.wo, std / factor, std)
+
+
+def _attention_flash_padded(q, k, v, causal, window):
+    """The flash-attention kernel takes heads of width 128: narrower heads are zero-padded (the scores
+    do not change, the padded half of the output is zero and is dropped)."""
+    from ..ops.attention import attention
+
+    Dh = q.shape[-1]
+    if Dh < 128:
+        q, k, v = (TF.pad(t, (0, 128 - Dh)) for t in (q, k, v))
+    o = attention(q.contiguous(), k.contiguous(), v.contiguous(), causal=causal, window=window or 0,
+                  scale=1.0 / math.sqrt(Dh))
+    return o[..., :Dh]
 
 
 def _attention_torch(q, k, v, causal, doc_start, window):

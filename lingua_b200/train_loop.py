@@ -134,7 +134,11 @@ def validate_train_args(args: TrainArgs, output_size: int) -> None:
         assert d.dp_replicate * d.dp_shard * d.tp_size == get_world_size()
         if d.fsdp_type == "no_shard":
             assert d.dp_shard == 1 and d.dp_replicate == get_world_size()
-    args.model.max_seqlen = args.data.seq_len
+    if hasattr(args.model, "max_seqlens"):  # hierarchical model: stage 0 runs at the data sequence length
+        if args.model.max_seqlens[0] < 0:
+            args.model.max_seqlens[0] = args.data.seq_len
+    else:
+        args.model.max_seqlen = args.data.seq_len
     if d.tp_size > 1:
         logger.warning("Tensor parallelism is less exercised than the data-parallel path")
     assert args.probe_freq != args.profiling.mem_steps, "Don't profile during probe step"
@@ -296,7 +300,7 @@ def run_training(args: TrainArgs, spec: ModelSpec) -> Dict[str, Any]:
                     "memory": mem._asdict(),
                 }, sep="/")
                 to_sync = {"loss/out": float(loss)}
-                to_sync.update({f"loss/{k}": float(v) for k, v in extra_losses.items()})
+                to_sync.update({(k if "/" in k else f"loss/{k}"): float(v) for k, v in extra_losses.items()})
                 metrics.update(dist_mean_dict(to_sync))
                 if get_is_master():
                     metric_logger.log(metrics)
