@@ -186,7 +186,9 @@ def eval_on_val(generator, val_args: ValidationArgs, train_cfg: dict):
     return all_metrics
 
 
-def launch_eval(cfg: EvalArgs, generator_cls=PackedCausalTransformerGenerator, model_cls=None, model_args_cls=None):
+def launch_eval(cfg: EvalArgs, generator_cls=PackedCausalTransformerGenerator, model_cls=None, model_args_cls=None,
+                loader=None):
+    """``loader(consolidated_dir) -> (model, tokenizer, train config)`` replaces the default checkpoint loader."""
     if not dist.is_initialized():
         setup_torch_distributed(DistributedArgs())
     ck = Path(cfg.ckpt_dir)
@@ -204,7 +206,10 @@ def launch_eval(cfg: EvalArgs, generator_cls=PackedCausalTransformerGenerator, m
     kw = {}
     if model_cls is not None:
         kw = dict(model_cls=model_cls, model_args_cls=model_args_cls)
-    model, tokenizer, train_cfg = load_consolidated_model_and_tokenizer(str(consolidated), **kw)
+    if loader is not None:
+        model, tokenizer, train_cfg = loader(str(consolidated))
+    else:
+        model, tokenizer, train_cfg = load_consolidated_model_and_tokenizer(str(consolidated), **kw)
     model.eval()
     generator = generator_cls(cfg.generator, model, tokenizer)
     results = {"results": {}}

@@ -106,6 +106,7 @@ class CachePlan:
         self.doc_start = None  # prefill: [1, T] int32, in packed-token coordinates
         self.start = None  # decode: first cache slot of every sequence (int32)
         self.len = None  # decode: visible keys per sequence, current token included (int32)
+        self.window = 0  # prefill: sliding-window width (0 = none); decode callers shrink start / len instead
 
 
 class KVCache(nn.Module):
@@ -122,7 +123,7 @@ class KVCache(nn.Module):
         if pl.mode == "prefill":
             self.k_cache.index_copy_(0, pl.slots, k)
             self.v_cache.index_copy_(0, pl.slots, v)
-            o, _ = flash_fwd(q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0), True, pl.doc_start)
+            o, _ = flash_fwd(q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0), True, pl.doc_start, pl.window)
             return o.view(T, H * Dh)
         out = torch.empty(T, H, Dh, dtype=q.dtype, device=q.device)
         rc = _lib.load().lb_decode_attn(q.data_ptr(), k.data_ptr(), v.data_ptr(), self.k_cache.data_ptr(),
@@ -134,13 +135,15 @@ class KVCache(nn.Module):
 
     # ---- reference path: q/k/v are [1, T, heads, Dh]
     def attend(self, q, k, v, tok_idx=None):
-        from .models.transformer import _attention_torch
+        from .models.transformer import _attention_flash_padded, _attention_torch
 
         pl = self.plan
         if pl.mode == "prefill":
             self.k_cache.index_copy_(0, pl.slots, k[0].to(self.k_cache.dtype))
             self.v_cache.index_copy_(0, pl.slots, v[0].to(self.v_cache.dtype))
-            return _attention_torch(q, k, v, True, pl.doc_start, 0)
+            if q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] <= 128:
+                return _attention_flash_padded(q, k, v, True, pl.window, pl.doc_start)
+            return _attention_torch(q, k, v, True, pl.doc_start, pl.window)
         n = q.shape[1]
         slot = (pl.start + pl.len - 1).long()
         self.k_cache.index_copy_(0, slot, k[0].to(self.k_cache.dtype))

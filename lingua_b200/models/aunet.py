@@ -339,7 +339,9 @@ class HierarchicalTransformer(nn.Module):
         return masks, idcs, nb_toks
 
     def plan_levels(self, level_mask: torch.Tensor, seq_len: int):
-        caps = [seq_len] + [e.max_seqlen for e in self.encoders[1:]] + [self.trunk.max_seqlen]
+        caps = [seq_len]  # a stage is never longer than the one above it
+        for stage in (*self.encoders[1:], self.trunk):
+            caps.append(min(stage.max_seqlen, caps[-1]))
         masks, _, nb_toks = self.get_pool_mask(level_mask, caps, return_idcs=False, force_first=True)
         plans = [make_level_plan(m, caps[i], caps[i + 1], t.repeat, t.indexed_matmul)
                  for i, (m, t) in enumerate(zip(masks, self.transitions))]

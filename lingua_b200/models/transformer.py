@@ -205,7 +205,7 @@ class Attention(nn.Module):
         _init_linear(self.wo, std / factor, std)
 
 
-def _attention_flash_padded(q, k, v, causal, window):
+def _attention_flash_padded(q, k, v, causal, window, doc_start=None):
     """The flash-attention kernel takes heads of width 128: narrower heads are zero-padded (the scores
     do not change, the padded half of the output is zero and is dropped)."""
     from ..ops.attention import attention
@@ -213,8 +213,10 @@ def _attention_flash_padded(q, k, v, causal, window):
     Dh = q.shape[-1]
     if Dh < 128:
         q, k, v = (TF.pad(t, (0, 128 - Dh)) for t in (q, k, v))
-    o = attention(q.contiguous(), k.contiguous(), v.contiguous(), causal=causal, window=window or 0,
-                  scale=1.0 / math.sqrt(Dh))
+    if doc_start is not None:
+        doc_start = doc_start.reshape(q.shape[0], q.shape[1]).int().contiguous()
+    o = attention(q.contiguous(), k.contiguous(), v.contiguous(), causal=causal, doc_start=doc_start,
+                  window=window or 0, scale=1.0 / math.sqrt(Dh))
     return o[..., :Dh]
 
 

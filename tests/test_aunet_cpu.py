@@ -195,7 +195,13 @@ def test_train_app_end_to_end(tmp_path):
                data=dict(sources={"synthetic": 1.0}, batch_size=2, seq_len=64, load_async=False,
                          tokenizer=dict(name="bytes"), regex=dict(strategy={"word1": "1@1"})),
                checkpoint=dict(dump=dict(every=2, keep=1)), logging=dict(freq=1))
-    metrics = train(dataclass_from_dict(TrainArgs, cfg))
+    import multiprocessing as mp
+
+    method = mp.get_start_method(allow_none=True)
+    try:
+        metrics = train(dataclass_from_dict(TrainArgs, cfg))
+    finally:  # the job sets the worker start method for its data loader: leave the process as it was
+        mp.set_start_method(method, force=True)
     assert {"loss/out", "ce/out", "mask_loss/out", "nb_toks/enc_0"} <= set(metrics)
     assert 0 < metrics["nb_toks/enc_0"] <= 2 * 24 and metrics["loss/out"] > metrics["ce/out"]
     assert os.path.isdir(tmp_path / "run" / "checkpoints" / "0000000004")

@@ -1,0 +1,78 @@
+"""Hierarchical byte model on a B200: the indexed projection and the padded-head attention against fp32
+oracles, and the sharded-engine training path against the same model in fp32 on the CPU."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_indexed_matmul_bf16_vs_fp32_oracle():
+    from lingua_b200.ops.indexed_matmul import indexed_matmul, indexed_matmul_ref
+
+    torch.manual_seed(0)
+    dev = "cuda"
+    x = (torch.randn(4, 1024, 256, device=dev) * 0.5).bfloat16().requires_grad_()
+    w = (torch.randn(16, 128, 256, device=dev) * 0.06).bfloat16().requires_grad_()
+    idx = torch.randint(0, 16, (4, 1024), device=dev)
+    idx[idx == 7] = 3  # one bank entry without rows
+    y = indexed_matmul(x, w, idx)
+    yr = indexed_matmul_ref(x, w, idx)
+    assert (y.float() - yr).abs().max() < 0.03 * yr.abs().max()
+    g = torch.randn_like(y)
+    gx, gw = torch.autograd.grad(y, (x, w), g)
+    rx, rw = torch.autograd.grad(yr, (x, w), g.float())
+    assert (gx.float() - rx.float()).abs().max() < 0.03 * rx.abs().max()
+    assert (gw.float() - rw.float()).abs().max() < 0.03 * rw.abs().max() and gw[7].abs().max() == 0
+
+
+@pytest.mark.parametrize("head_dim,window", [(64, 0), (64, 96), (32, 40)])
+def test_narrow_heads_through_the_128_wide_kernel(head_dim, window):
+    from lingua_b200.models.transformer import _attention_flash_padded, _attention_torch
+
+    torch.manual_seed(1)
+    q, k, v = ((torch.randn(2, 384, 4, head_dim, device="cuda")).bfloat16().requires_grad_() for _ in range(3))
+    o = _attention_flash_padded(q, k, v, True, window)
+    ref = _attention_torch(q.float(), k.float(), v.float(), True, None, window)
+    assert o.shape == ref.shape and (o.float() - ref).abs().max() < 0.03
+    g = torch.randn_like(o)
+    got = torch.autograd.grad(o, (q, k, v), g)
+    want = torch.autograd.grad(ref, (q, k, v), g.float())
+    for a, b in zip(got, want):
+        assert (a.float() - b.float()).abs().max() < 0.05 * max(1.0, b.abs().max().item())
+
+
+def test_engine_training_step_matches_fp32():
+    import copy
+
+    from lingua_b200.models.aunet import HierarchicalArgs, HierarchicalTransformer, build_fsdp_grouping_plan
+    from lingua_b200.models.transformer import BaseTransformerArgs
+    from lingua_b200.parallel.engine import EngineOptim, ShardedEngine
+
+    args = HierarchicalArgs(dimensions=[128, 256], head_dims=[64, 128], layers=[1, 2], sliding_windows=[64, 128],
+                            max_seqlens=[256, 96], vocab_size=258, lambda_level=0.1,
+                            block=BaseTransformerArgs(multiple_of=64, norm_eps=1e-5))
+    torch.manual_seed(0)
+    ref = HierarchicalTransformer(args)
+    ref.init_weights()
+    model = copy.deepcopy(ref).cuda()
+    model._engine = engine = ShardedEngine(model, build_fsdp_grouping_plan(args), process_group=False,
+                                           compute_dtype=torch.bfloat16, optim=EngineOptim(),
+                                           device=torch.device("cuda"))
+    engine.sync_master()
+    ref = ref.cuda().float()
+    for (_, pr), (_, pn) in zip(ref.named_parameters(), model.named_parameters()):
+        pr.data.copy_(pn.data.float())  # same bf16-rounded weights: only the arithmetic differs
+    tok, tgt = torch.randint(0, 258, (2, 256), device="cuda"), torch.randint(0, 258, (2, 256), device="cuda")
+    lv = (torch.rand(2, 256, device="cuda") < 0.3).long()
+    l_ref, m_ref, nb_ref = ref(tok, lv, tgt, lv.roll(-1, 1))
+    (l_ref + 0.1 * m_ref).backward()
+    engine.zero_grad()
+    l, m, nb = model(tok, lv, tgt, lv.roll(-1, 1))
+    (l + 0.1 * m).backward()
+    assert abs(float(l) - float(l_ref)) < 0.03 and abs(float(m) - float(m_ref)) < 0.03
+    assert [int(a) for a in nb] == [int(b) for b in nb_ref]
+    gn = float(engine.step(1e-3))
+    gn_ref = math.sqrt(sum(float(p.grad.float().pow(2).sum()) for p in ref.parameters()))
+    assert abs(gn - gn_ref) < 0.05 * gn_ref
