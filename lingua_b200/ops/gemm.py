@@ -24,6 +24,19 @@ def _major_and_ld(t: torch.Tensor):
     raise ValueError("operand needs a unit stride in one of its last two dims")
 
 
+def _aligned(t: torch.Tensor) -> torch.Tensor:
+    """The kernel's TMA maps need row pitches that are multiples of 8 elements (16 bytes): an operand with a
+    ragged pitch (a [rows, 258] gradient, say) is copied once into a padded buffer and viewed at its own size."""
+    major, ld = _major_and_ld(t)
+    if ld % 8 == 0 or (t.shape[-2] == 1 and major == 0) or (t.shape[-1] == 1 and major == 1):
+        return t
+    src = t if major == 0 else t.transpose(-1, -2)
+    cols = src.shape[-1]
+    buf = torch.empty(*src.shape[:-1], (cols + 7) // 8 * 8, dtype=t.dtype, device=t.device)[..., :cols]
+    buf.copy_(src)
+    return buf if major == 0 else buf.transpose(-1, -2)
+
+
 def gemm_ref(a, b, out_dtype=torch.bfloat16, out=None, accumulate=False, alpha=1.0):
     r = torch.matmul(a.float(), b.float().transpose(-1, -2)) * alpha
     if out is not None:
@@ -60,6 +73,7 @@ def gemm(
         out = torch.empty(*batch, M, N8, dtype=out_dtype, device=a.device)[..., :N]
     else:
         assert out.shape[-2:] == (M, N) and out.stride(-1) == 1
+    a, b = _aligned(a), _aligned(b)
     a_major, lda = _major_and_ld(a)
     b_major, ldb = _major_and_ld(b)
     # A unit-extent dim can report any stride; normalise so the TMA stride rule holds.

@@ -17,7 +17,21 @@ from typing import List, Optional
 import torch
 import torch.nn as nn
 
-from .gemm import mm_nn, mm_nt, mm_tn
+from . import gemm as _g
+
+
+def _route(fn):
+    """bf16 goes to the tcgen05 GEMM; an fp32 reference model on the GPU uses the plain fp32 product."""
+    def run(a, b, **kw):
+        if a.is_cuda and a.dtype != torch.bfloat16:
+            at, bt = {"mm_nt": (a, b), "mm_nn": (a, b.transpose(-1, -2)),
+                      "mm_tn": (a.transpose(-1, -2), b.transpose(-1, -2))}[fn.__name__]
+            return _g.gemm_ref(at, bt, kw.get("out_dtype", a.dtype), kw.get("out"), kw.get("accumulate", False))
+        return fn(a, b, **kw)
+    return run
+
+
+mm_nt, mm_nn, mm_tn = _route(_g.mm_nt), _route(_g.mm_nn), _route(_g.mm_tn)
 
 
 @dataclass

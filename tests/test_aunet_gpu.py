@@ -27,6 +27,21 @@ def test_indexed_matmul_bf16_vs_fp32_oracle():
     assert (gw.float() - rw.float()).abs().max() < 0.03 * rw.abs().max() and gw[7].abs().max() == 0
 
 
+def test_gemm_operands_with_ragged_pitch():
+    """A byte-vocabulary head has 258 outputs: its gradient has a row pitch that TMA cannot address."""
+    from lingua_b200.ops.gemm import mm_nn, mm_tn
+
+    torch.manual_seed(2)
+    dy = (torch.randn(1000, 258, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(258, 512, device="cuda") * 0.1).bfloat16()
+    x = (torch.randn(1000, 512, device="cuda") * 0.5).bfloat16()
+    dx = mm_nn(dy, w)
+    assert (dx.float() - dy.float() @ w.float()).abs().max() < 0.05
+    dw = mm_tn(dy, x, out_dtype=torch.float32)
+    want = dy.float().t() @ x.float()
+    assert dw.shape == (258, 512) and (dw - want).abs().max() < 0.02 * want.abs().max()
+
+
 @pytest.mark.parametrize("head_dim,window", [(64, 0), (64, 96), (32, 40)])
 def test_narrow_heads_through_the_128_wide_kernel(head_dim, window):
     from lingua_b200.models.transformer import _attention_flash_padded, _attention_torch
