@@ -140,7 +140,8 @@ class CausalTransformer(BaseTransformer):
         cs = self.rope_embeddings()
         window = self.sliding_window or 0
         first = self.layers[0].attention
-        if _is_native(first.wq.weight) and h.dtype == torch.bfloat16 and self.head_dim == 128:
+        if _is_native(first.wq.weight) and h.dtype == torch.bfloat16 and self.head_dim <= 128 \
+                and self.head_dim % 8 == 0 and (first.kv_cache is None or self.head_dim == 128):
             x, pending = h.reshape(B * S, D), None
             pos = tok_idx.reshape(-1).int().contiguous() if tok_idx is not None else None
             for i, layer in enumerate(self.layers):

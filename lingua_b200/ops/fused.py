@@ -204,17 +204,25 @@ class NormLinearFn(torch.autograd.Function):
         return (dx, dx if ctx.has_res else None, dg, None, None, *dws)
 
 
+def _pad_heads(t: torch.Tensor, Dh: int) -> torch.Tensor:
+    """[..., heads, Dh] -> [..., heads, 128], zero-filled: the attention kernel takes heads of width 128.
+    Scores are unchanged (the softmax scale is passed explicitly) and the padded output half is zero."""
+    return t if Dh == 128 else torch.nn.functional.pad(t, (0, 128 - Dh))
+
+
 class RopeAttnFn(torch.autograd.Function):
-    """qkv [B*S, (H + 2 Hkv) * Dh] -> RoPE on q and k (in place) -> attention -> [B*S, H * Dh]."""
+    """qkv [B*S, (H + 2 Hkv) * Dh] -> RoPE on q and k (in place) -> attention -> [B*S, H * Dh]. Dh <= 128."""
 
     @staticmethod
     def forward(ctx, qkv, cs, B, S, H, Hkv, Dh, causal, doc_start, doc_end, window, pos, anchor=None):
         F.rope_(qkv, cs, H + Hkv, Dh, S, pos)
-        t = qkv.view(B, S, H + 2 * Hkv, Dh)
+        t = _pad_heads(qkv.view(B, S, H + 2 * Hkv, Dh), Dh)
         q, k, v = t[:, :, :H], t[:, :, H:H + Hkv], t[:, :, H + Hkv:]
         if _OBSERVER is not None and anchor is not None:
-            _OBSERVER.attention(anchor, q, k, causal, doc_start)
-        o, lse = flash_fwd(q, k, v, causal, doc_start, window)
+            _OBSERVER.attention(anchor, q[..., :Dh], k[..., :Dh], causal, doc_start)
+        o, lse = flash_fwd(q, k, v, causal, doc_start, window, Dh ** -0.5)
+        if Dh != 128:
+            o = o[..., :Dh].contiguous()
         ctx.save_for_backward(qkv, o, lse, cs, doc_start, doc_end, pos)
         ctx.cfg = (B, S, H, Hkv, Dh, causal, window)
         return o.view(B * S, H * Dh)
@@ -223,12 +231,13 @@ class RopeAttnFn(torch.autograd.Function):
     def backward(ctx, do):
         qkv, o, lse, cs, doc_start, doc_end, pos = ctx.saved_tensors
         B, S, H, Hkv, Dh, causal, window = ctx.cfg
-        t = qkv.view(B, S, H + 2 * Hkv, Dh)
+        t = _pad_heads(qkv.view(B, S, H + 2 * Hkv, Dh), Dh)
         q, k, v = t[:, :, :H], t[:, :, H:H + Hkv], t[:, :, H + Hkv:]
-        dqkv = torch.empty_like(qkv)
-        dt = dqkv.view(B, S, H + 2 * Hkv, Dh)
-        flash_bwd(do.contiguous().view(B, S, H, Dh), q, k, v, o, lse, dt[:, :, :H], dt[:, :, H:H + Hkv],
-                  dt[:, :, H + Hkv:], causal, doc_start, doc_end, window)
+        dt = torch.empty_like(t)
+        flash_bwd(_pad_heads(do.contiguous().view(B, S, H, Dh), Dh), q, k, v, _pad_heads(o.view(B, S, H, Dh), Dh), lse,
+                  dt[:, :, :H], dt[:, :, H:H + Hkv], dt[:, :, H + Hkv:], causal, doc_start, doc_end, window,
+                  Dh ** -0.5)
+        dqkv = dt.view(B * S, -1) if Dh == 128 else dt[..., :Dh].reshape(B * S, -1)
         F.rope_(dqkv, cs, H + Hkv, Dh, S, pos, backward=True)
         return (dqkv,) + (None,) * 12
 
