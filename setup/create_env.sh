@@ -4,6 +4,7 @@
 # this library needs PyTorch, numpy, pyyaml and - optionally - sentencepiece / tiktoken / pyarrow / pandas,
 # and builds its own kernels.)
 set -e
+python -m pip install -r requirements.txt || echo "optional packages missing (no package index?): continuing"
 python -c "import torch, yaml, numpy; print('torch', torch.__version__)"
 python -m lingua_b200.build            # nvcc -> lingua_b200/lib/liblingua_b200.so (sm_100a)
 g++ -O2 -std=c++17 -o setup/lineshuf setup/lineshuf.cpp
