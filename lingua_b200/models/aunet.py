@@ -253,11 +253,14 @@ class SimpleTransition(nn.Module):
         if hasattr(self, "up_norm"):
             x = self.up_norm(x)
         if self.repeat:
-            x = _gather_rows(x, plan.repeat_idx) if plan.repeat_idx is not None else x
+            rep = plan.repeat_idx
             if self.indexed_matmul:
+                # the position-independent map commutes with the repeat: apply it to the pooled rows, then
+                # repeat its narrow output; the indexed map reads the pooled rows through the repeat index
                 xi = self.indexed_norm(x) if hasattr(self, "indexed_norm") else x
-                return self._up_map(x) + self.indexed_linear(xi, plan.position, plan.groups)
-            return self._up_map(x + self.pos_encoding(plan.position).to(x.dtype))
+                rows = rep + torch.arange(x.shape[0], device=x.device).unsqueeze(1) * x.shape[1]
+                return _gather_rows(self._up_map(x), rep) + self.indexed_linear(xi, plan.position, plan.groups, rows)
+            return self._up_map(_gather_rows(x, rep) + self.pos_encoding(plan.position).to(x.dtype))
         keep = plan.mask.gather(1, plan.idx).to(x.dtype).unsqueeze(-1)  # filler positions contribute nothing
         out = torch.zeros_like(res)
         return out.scatter(1, plan.idx.unsqueeze(-1).expand(-1, -1, self.dim_in), keep * self._up_map(x))

@@ -64,21 +64,25 @@ def indexed_matmul_ref(x: torch.Tensor, w: torch.Tensor, indices: torch.Tensor) 
 
 
 class IndexedMatMulFn(torch.autograd.Function):
+    """``rows`` (optional, [T] int64): output row t reads input row ``rows[t]`` -- the repeat-upsampling gather
+    folded into the sort, so the repeated activations are never materialised in input order."""
+
     @staticmethod
-    def forward(ctx, x2d, w, plan: GroupPlan):
-        xs = x2d.index_select(0, plan.order)
+    def forward(ctx, x2d, w, plan: GroupPlan, rows=None):
+        src = plan.order if rows is None else rows.index_select(0, plan.order)
+        xs = x2d.index_select(0, src)
         ys = torch.empty(xs.shape[0], w.shape[1], dtype=x2d.dtype, device=x2d.device)
         for g, o, c in plan.segments:
             mm_nt(xs[o:o + c], w[g], out=ys[o:o + c], out_dtype=x2d.dtype)
         y = torch.empty_like(ys)
         y.index_copy_(0, plan.order, ys)
-        ctx.save_for_backward(xs, w)
-        ctx.plan = plan
+        ctx.save_for_backward(xs, w, src)
+        ctx.plan, ctx.n_in, ctx.permutation = plan, x2d.shape[0], rows is None
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        xs, w = ctx.saved_tensors
+        xs, w, src = ctx.saved_tensors
         plan: GroupPlan = ctx.plan
         dys = dy.index_select(0, plan.order)
         dxs = torch.empty_like(xs)
@@ -93,17 +97,23 @@ class IndexedMatMulFn(torch.autograd.Function):
                   out_dtype=torch.float32)
         if main is not None:
             w.grad_written = True
-        dx = torch.empty_like(dxs)
-        dx.index_copy_(0, plan.order, dxs)
-        return dx, (None if main is not None else dw.to(w.dtype)), None
+        if ctx.permutation:
+            dx = torch.empty_like(dxs)
+            dx.index_copy_(0, src, dxs)
+        else:  # several output rows per input row: sum them (fp32, then back to the activation dtype)
+            dx = torch.zeros(ctx.n_in, dxs.shape[1], dtype=torch.float32, device=dxs.device)
+            dx.index_add_(0, src, dxs.float())
+            dx = dx.to(dxs.dtype)
+        return dx, (None if main is not None else dw.to(w.dtype)), None, None
 
 
-def indexed_matmul(x: torch.Tensor, w: torch.Tensor, indices: torch.Tensor,
-                   plan: Optional[GroupPlan] = None) -> torch.Tensor:
-    """x [..., in], w [n, out, in], indices [...] in [0, n) -> [..., out]."""
+def indexed_matmul(x: torch.Tensor, w: torch.Tensor, indices: torch.Tensor, plan: Optional[GroupPlan] = None,
+                   rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x [..., in], w [n, out, in], indices [...] in [0, n) -> [..., out]. With ``rows`` (same shape as
+    ``indices``, values index the flattened rows of x) the result is ``x.flatten(0, -2)[rows] @ w[indices]^T``."""
     plan = plan or plan_groups(indices, w.shape[0])
-    y = IndexedMatMulFn.apply(x.reshape(-1, x.shape[-1]), w, plan)
-    return y.view(*x.shape[:-1], w.shape[1])
+    y = IndexedMatMulFn.apply(x.reshape(-1, x.shape[-1]), w, plan, None if rows is None else rows.reshape(-1))
+    return y.view(*indices.shape, w.shape[1])
 
 
 class IndexedMatMul(nn.Module):
@@ -112,8 +122,9 @@ class IndexedMatMul(nn.Module):
         self.num_linear, self.in_features, self.out_features = num_linear, in_features, out_features
         self.weight = nn.Parameter(torch.empty(num_linear, out_features, in_features))
 
-    def forward(self, x: torch.Tensor, indices: torch.Tensor, plan: Optional[GroupPlan] = None) -> torch.Tensor:
-        return indexed_matmul(x, self.weight, indices, plan)
+    def forward(self, x: torch.Tensor, indices: torch.Tensor, plan: Optional[GroupPlan] = None,
+                rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return indexed_matmul(x, self.weight, indices, plan, rows)
 
     def extra_repr(self) -> str:
         return f"num_linear={self.num_linear}, in_features={self.in_features}, out_features={self.out_features}"

@@ -141,6 +141,14 @@ def test_indexed_matmul_matches_gather_oracle():
     gx, gw = torch.autograd.grad(y, (x, w), g)
     rx, rw = torch.autograd.grad(yr, (x, w), g)
     assert torch.allclose(gx, rx, atol=1e-5) and torch.allclose(gw, rw, atol=1e-4) and gw[5].abs().max() == 0
+    # rows: every output row names the input row it reads (the repeat-upsampling gather folded in)
+    small = torch.randn(2, 9, 24, requires_grad=True)
+    rows = torch.randint(0, 18, (2, 37))
+    y2 = indexed_matmul(small, w, idx, rows=rows)
+    ref2 = indexed_matmul_ref(small.reshape(-1, 24)[rows.flatten()].view(2, 37, 24), w, idx)
+    assert y2.shape == (2, 37, 16) and torch.allclose(y2, ref2, atol=1e-5)
+    for a, b in zip(torch.autograd.grad(y2, (small, w), g), torch.autograd.grad(ref2, (small, w), g)):
+        assert torch.allclose(a, b, atol=1e-4)
     plan = plan_groups(idx, 6)
     assert plan.counts == torch.bincount(idx.flatten(), minlength=6).tolist()
     assert (idx.flatten()[plan.order].diff() >= 0).all()
