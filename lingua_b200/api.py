@@ -24,7 +24,9 @@ class Trainer:
     def __init__(self, model_args: LMTransformerArgs, dist_args: Optional[DistributedArgs] = None,
                  optim_args: Optional[OptimArgs] = None, total_steps: int = 1000, mesh: Optional[Mesh] = None,
                  grad_acc_steps: int = 1, device: Optional[torch.device] = None, model_cls=LMTransformer,
-                 grouping_plan=None):
+                 grouping_plan=None, loss_fn=None):
+        # loss_fn(model, inputs, labels) -> scalar loss, for models whose forward is not (tokens, targets)
+        self.loss_fn = loss_fn
         self.dist_args = dist_args or DistributedArgs()
         self.optim_args = optim_args or OptimArgs()
         self.mesh = mesh or get_device_mesh(self.dist_args)
@@ -72,7 +74,7 @@ class Trainer:
         if doc_end is not None:
             kw["doc_end"] = doc_end
         self.engine.defer_reduce = (self.acc_step + 1) % self.grad_acc_steps != 0
-        loss = self.model(inputs, labels, **kw)
+        loss = self.loss_fn(self.model, inputs, labels) if self.loss_fn else self.model(inputs, labels, **kw)
         (loss / self.grad_acc_steps if self.grad_acc_steps > 1 else loss).backward()
         self.acc_step = (self.acc_step + 1) % self.grad_acc_steps
         if self.acc_step == 0:

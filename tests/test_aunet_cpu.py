@@ -213,3 +213,25 @@ def test_train_app_end_to_end(tmp_path):
     assert {"loss/out", "ce/out", "mask_loss/out", "nb_toks/enc_0"} <= set(metrics)
     assert 0 < metrics["nb_toks/enc_0"] <= 2 * 24 and metrics["loss/out"] > metrics["ce/out"]
     assert os.path.isdir(tmp_path / "run" / "checkpoints" / "0000000004")
+
+
+def test_sharded_two_ranks_match_single_process():
+    """gloo, world size 2: the engine shards every block of every stage plus the root group (embeddings,
+    transitions, heads); the losses of three optimiser steps equal the single-process run."""
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    worker = str(Path(__file__).resolve().parent / "aunet_dist_worker.py")
+    env = dict(os.environ, OMP_NUM_THREADS="1", MASTER_ADDR="127.0.0.1")
+
+    def losses(cmd):
+        proc = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
+        assert proc.returncode == 0, proc.stderr[-2000:]
+        line = [l for l in proc.stdout.splitlines() if l.startswith("LOSSES ")][-1]
+        return json.loads(line[len("LOSSES "):])
+
+    one = losses([sys.executable, worker, "1", "3"])
+    two = losses([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+                  "127.0.0.1", "--master-port", "29641", worker, "2", "3"])
+    assert len(one) == 3 and all(abs(a - b) < 2e-4 * max(1.0, abs(a)) for a, b in zip(one, two)), (one, two)
