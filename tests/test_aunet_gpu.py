@@ -58,6 +58,48 @@ def test_narrow_heads_through_the_128_wide_kernel(head_dim, window):
         assert (a.float() - b.float()).abs().max() < 0.05 * max(1.0, b.abs().max().item())
 
 
+def test_generator_decoding_matches_full_forward_bf16():
+    """Prefill + byte-by-byte decoding against the one-pass forward: the trunk (heads of 128) runs the native
+    prefill and decode-attention kernels, the byte stage (heads of 64) the generic cached path."""
+    from lingua_b200.data.regex_cutting import RegexArgs, RegexPool
+    from lingua_b200.generation_aunet import (PackedHierarchicalCausalTransformerGenerator as Generator,
+                                              PackedHierarchicalCausalTransformerGeneratorArgs as GenArgs)
+    from lingua_b200.models.aunet import HierarchicalArgs, HierarchicalTransformer
+    from lingua_b200.models.transformer import BaseTransformerArgs
+    from lingua_b200.tokenizer import build_tokenizer
+
+    args = HierarchicalArgs(dimensions=[128, 256], head_dims=[64, 128], layers=[1, 2], sliding_windows=[32, 128],
+                            max_seqlens=[128, 128], vocab_size=258, block=BaseTransformerArgs(multiple_of=64, norm_eps=1e-5))
+    torch.manual_seed(0)
+    model = HierarchicalTransformer(args)
+    model.init_weights()
+    model = model.cuda().bfloat16().eval()
+    for mod in model.modules():
+        if hasattr(mod, "reset_parameters") and type(mod).__name__ == "RotaryEmbedding":
+            mod.reset_parameters()
+    n, L, P = 3, 80, [30, 41, 36]
+    tok = torch.randint(0, 256, (n, L), device="cuda")
+    lv = (torch.rand(n, L, device="cuda") < 0.35).long()
+    lv[:, 0] = 1
+    gen = Generator(GenArgs(max_gen_len=40, max_tokens=600), model, build_tokenizer("bytes"),
+                    RegexPool(RegexArgs({"word1": "1@1"})))
+    ptok, plv = torch.zeros(n, max(P), dtype=torch.long, device="cuda"), torch.zeros(n, max(P), dtype=torch.long, device="cuda")
+    for i in range(n):
+        ptok[i, :P[i]], plv[i, :P[i]] = tok[i, :P[i]], lv[i, :P[i]]
+    with torch.no_grad():
+        full = model(tok, lv).float()
+        pre = gen.prefill(ptok, plv, torch.tensor(P, device="cuda")).float()
+        for i in range(n):
+            assert (pre[i, :P[i]] - full[i, :P[i]]).abs().max() < 0.08
+        for s in range(30):
+            cur = torch.stack([tok[i, P[i] + s] for i in range(n)])
+            cur_lv = torch.stack([lv[i, P[i] + s] for i in range(n)])
+            logits = gen.generate_next_token(cur, cur_lv).float()
+            for i in range(n):
+                assert (logits[i] - full[i, P[i] + s]).abs().max() < 0.08, (s, i)
+    gen.release_cache()
+
+
 def test_engine_training_step_matches_fp32():
     import copy
 
