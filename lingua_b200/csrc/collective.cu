@@ -221,7 +221,13 @@ extern "C" int lb_reduce_slots(const float* own, const float* slots, int n_slots
       reinterpret_cast<uintptr_t>(slots) % 16 || slot_stride % 4)
     return 2;
   long long blocks = (n / 4 + 255) / 256;
-  const long long cap = (long long)lb::num_sms() * 8;
+  // The kernel runs beside the backward GEMMs: LB_REDUCE_BLOCKS caps its grid (a smaller grid takes longer but
+  // draws less memory bandwidth at a time). Default: 8 blocks per SM.
+  static const long long env_cap = [] {
+    const char* s = getenv("LB_REDUCE_BLOCKS");
+    return s ? atoll(s) : 0LL;
+  }();
+  const long long cap = env_cap > 0 ? env_cap : (long long)lb::num_sms() * 8;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   lb::reduce_slots_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
