@@ -73,6 +73,10 @@ def gemm(
         out = torch.empty(*batch, M, N8, dtype=out_dtype, device=a.device)[..., :N]
     else:
         assert out.shape[-2:] == (M, N) and out.stride(-1) == 1
+    if M == 0 or N == 0 or (K == 0 and accumulate):
+        return out  # nothing to compute (an empty group of a grouped product, a step without active rows)
+    if K == 0:
+        return out.zero_()
     a, b = _aligned(a), _aligned(b)
     a_major, lda = _major_and_ld(a)
     b_major, ldb = _major_and_ld(b)
