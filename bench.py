@@ -268,8 +268,10 @@ def main() -> None:
             if tr is None:
                 raise torch.OutOfMemoryError("the training step does not fit with or without activation recomputation")
             extra["selective_activation_checkpointing"] = sac
-            extra["collectives"] = ("nvlink copy engines + reduce kernel" if (world > 1 and tr.engine.groups[0].peer_full
-                                                                              is not None) else "nccl" if world > 1 else "none")
+            g0 = tr.engine.groups[0]
+            extra["collectives"] = ("none" if world == 1 else "nccl" if g0.peer_full is None else
+                                    "all-gather: nvlink copy engines; reduce-scatter: one kernel pulling peer gradients"
+                                    if g0.peer_grad_ptrs is not None else "nvlink copy engines + reduce kernel")
             host_batches = [views(h).contiguous().pin_memory() for h in host]
 
             def dev_step(i):

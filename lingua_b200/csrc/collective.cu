@@ -212,7 +212,76 @@ reduce_slots_kernel(const float* __restrict__ own, const float* __restrict__ slo
     atomicAdd(sumsq, t);
   }
 }
+// Reduce-scatter by pulling: out[i] = scale * sum_r src[r][i], where src[r] points at this rank's slice inside
+// rank r's gradient buffer (peer-visible memory, plain loads over NVLink; src[0] is the local one), fused with
+// the squared-norm pass. No staging copy: each gradient byte is read once where it lives and crosses NVLink
+// once. All loads of an element are issued before the first add, so a thread keeps n_src requests in flight.
+struct PeerSrcs {
+  const float* p[LB_MAX_PEERS];
+};
+template <int NS>
+__global__ void __launch_bounds__(256)
+reduce_peers_kernel(PeerSrcs srcs, float* __restrict__ out, long long n, float scale, float* __restrict__ sumsq) {
+  float acc = 0.f;
+  const long long n4 = n / 4;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    float4 v[NS];
+#pragma unroll
+    for (int s = 0; s < NS; ++s) v[s] = __ldcs(reinterpret_cast<const float4*>(srcs.p[s]) + i);
+#pragma unroll
+    for (int s = 1; s < NS; ++s) {
+      v[0].x += v[s].x; v[0].y += v[s].y; v[0].z += v[s].z; v[0].w += v[s].w;
+    }
+    v[0].x *= scale; v[0].y *= scale; v[0].z *= scale; v[0].w *= scale;
+    __stcs(reinterpret_cast<float4*>(out) + i, v[0]);
+    acc += v[0].x * v[0].x + v[0].y * v[0].y + v[0].z * v[0].z + v[0].w * v[0].w;
+  }
+  if (blockIdx.x == 0) {
+    for (long long i = n4 * 4 + threadIdx.x; i < n; i += blockDim.x) {
+      float v = 0.f;
+      for (int s = 0; s < NS; ++s) v += srcs.p[s][i];
+      v *= scale;
+      out[i] = v;
+      acc += v * v;
+    }
+  }
+  __shared__ float red[8];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0 && sumsq) {
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t += red[i];
+    atomicAdd(sumsq, t);
+  }
+}
 }  // namespace lb
+
+extern "C" int lb_reduce_peers(const void* const* srcs, int n_src, float* out, long long n, float scale, float* sumsq,
+                               void* stream) {
+  if (!srcs || !out || n <= 0 || n_src < 1 || n_src > LB_MAX_PEERS) return 1;
+  lb::PeerSrcs ps{};
+  for (int s = 0; s < n_src; ++s) {
+    if (!srcs[s] || reinterpret_cast<uintptr_t>(srcs[s]) % 16) return 2;
+    ps.p[s] = static_cast<const float*>(srcs[s]);
+  }
+  if (reinterpret_cast<uintptr_t>(out) % 16) return 2;
+  long long blocks = (n / 4 + 255) / 256;
+  const long long cap = (long long)lb::num_sms() * 8;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  switch (n_src) {
+#define LB_RP(NS) case NS: lb::reduce_peers_kernel<NS><<<(unsigned)blocks, 256, 0, st>>>(ps, out, n, scale, sumsq); break;
+    LB_RP(1) LB_RP(2) LB_RP(3) LB_RP(4) LB_RP(5) LB_RP(6) LB_RP(7) LB_RP(8)
+#undef LB_RP
+  }
+  lb::g_launches.fetch_add(1, std::memory_order_relaxed);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}
 
 extern "C" int lb_reduce_slots(const float* own, const float* slots, int n_slots, long long slot_stride, float* out,
                                long long n, float scale, float* sumsq, void* stream) {

@@ -140,6 +140,12 @@ int lb_peer_barrier_limit(void* const* pads, int world, int rank, uint32_t epoch
 int lb_reduce_slots(const float* own, const float* slots, int n_slots, long long slot_stride, float* out,
                     long long n, float scale, float* sumsq, void* stream);
 
+// out[i] = scale * sum_r srcs[r][i], *sumsq += sum out[i]^2 (fp32, n elements, n_src <= LB_MAX_PEERS): a
+// reduce-scatter without staging. srcs[r] is this rank's slice inside rank r's buffer (peer-visible addresses,
+// read with plain loads); order the ranks with lb_peer_barrier before (sources final) and after (readers done).
+int lb_reduce_peers(const void* const* srcs, int n_src, float* out, long long n, float scale, float* sumsq,
+                    void* stream);
+
 // h = resid + sum_s slots[s] (bf16 [rows, D] each, slot_stride elements apart), y = RMSNorm(h) * w.
 // resid, h_out, y_out (with w) and rstd_out are optional. D % 8 == 0, D <= 8192.
 int lb_reduce_norm(const void* slots, int n_slots, long long slot_stride, const void* resid, const void* w,

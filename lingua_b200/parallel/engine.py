@@ -44,8 +44,12 @@ class ParamGroup:
     """One flat buffer worth of parameters."""
 
     def __init__(self, name: str, params: List[Tuple[str, nn.Parameter]], world: int, rank: int,
-                 compute_dtype: torch.dtype, device: torch.device, alloc_full: Optional[Callable] = None):
+                 compute_dtype: torch.dtype, device: torch.device, alloc_full: Optional[Callable] = None,
+                 alloc_grad: Optional[Callable] = None):
         self.name, self.params = name, params
+        # peer-visible addresses of this rank's slice inside every rank's gradient buffer (own first), when the
+        # gradient buffers live in symmetric memory: the reduce-scatter then pulls instead of staging
+        self.peer_grad_ptrs: Optional[List[int]] = None
         self.peer_full: Optional[List[torch.Tensor]] = None  # every rank's ``full`` buffer, when peer-visible
         self.peer_stage: Optional[List[torch.Tensor]] = None  # every rank's reduce-scatter staging [world-1, shard]
         self.rs_stage: Optional[torch.Tensor] = None
@@ -62,7 +66,8 @@ class ParamGroup:
         self.shard_numel = self.padded // world
         self.full = (alloc_full(self.padded) if alloc_full is not None
                      else torch.zeros(self.padded, dtype=compute_dtype, device=device))
-        self.grad = torch.zeros(self.padded, dtype=torch.float32, device=device)
+        self.grad = (alloc_grad(self.padded) if alloc_grad is not None
+                     else torch.zeros(self.padded, dtype=torch.float32, device=device))
         s0 = rank * self.shard_numel
         self.shard_slice = slice(s0, s0 + self.shard_numel)
         self.master = torch.zeros(self.shard_numel, dtype=torch.float32, device=device)
@@ -92,8 +97,14 @@ class ParamGroup:
 class ShardedEngine:
     def __init__(self, model: nn.Module, plan: Sequence[Tuple[str, bool]], process_group=None,
                  compute_dtype: torch.dtype = torch.bfloat16, optim: Optional[EngineOptim] = None,
-                 device: Optional[torch.device] = None, p2p_gather: bool = True):
+                 device: Optional[torch.device] = None, p2p_gather: bool = True, p2p_reduce: Optional[str] = None):
         self.model = model
+        # gradient reduce-scatter over peer memory: "pull" (one kernel reads the peers' gradient buffers) or
+        # "push" (copy engines fill staging slots, a kernel sums them); LB_P2P_REDUCE overrides the default
+        import os
+
+        self.p2p_reduce = p2p_reduce or os.environ.get("LB_P2P_REDUCE", "push")
+        assert self.p2p_reduce in ("pull", "push")
         self.pg = process_group
         self.world = dist.get_world_size(process_group) if (dist.is_initialized() and process_group is not False) else 1
         self.rank = dist.get_rank(process_group) if self.world > 1 else 0
@@ -123,6 +134,10 @@ class ShardedEngine:
                 pad.zero_()
                 hdl = sm.rendezvous(pad, group=self.pg if self.pg is not None else dist.group.WORLD)
                 self._symm, self._pad = sm, pad
+                from ..ops import _lib
+
+                if self.p2p_reduce == "pull" and not hasattr(_lib.load(), "lb_reduce_peers"):
+                    self.p2p_reduce = "push"  # a library built before the pull kernel existed
                 self._pad_ptrs = [int(p) for p in hdl.buffer_ptrs]
                 torch.cuda.synchronize(self.device)
                 dist.barrier(group=self.pg)  # every pad is zero before the first barrier kernel runs
@@ -156,11 +171,25 @@ class ShardedEngine:
                 t = self._symm.empty(n, dtype=self.compute_dtype, device=self.device)
                 t.zero_()
                 return t
-        g = ParamGroup(path, ps, self.world, self.rank, self.compute_dtype, self.device, alloc_full=alloc)
+        alloc_grad = None
+        if self._symm is not None and self.p2p_reduce == "pull":
+            def alloc_grad(n):
+                t = self._symm.empty(n, dtype=torch.float32, device=self.device)
+                t.zero_()
+                return t
+        g = ParamGroup(path, ps, self.world, self.rank, self.compute_dtype, self.device, alloc_full=alloc,
+                       alloc_grad=alloc_grad)
         if self._symm is not None:
             try:
                 hdl = self._symm.rendezvous(g.full, group=self.pg if self.pg is not None else dist.group.WORLD)
                 g.peer_full = [hdl.get_buffer(r, (g.padded,), self.compute_dtype) for r in range(self.world)]
+                if alloc_grad is not None:
+                    hg = self._symm.rendezvous(g.grad, group=self.pg if self.pg is not None else dist.group.WORLD)
+                    mine = self.rank * g.shard_numel * 4
+                    ring = [(self.rank + k) % self.world for k in range(self.world)]  # own first, then the ring
+                    g.peer_grad_ptrs = [int(hg.buffer_ptrs[r]) + mine for r in ring]
+                    self.groups.append(g)
+                    return
                 # staging of the gradient reduce-scatter: slot k-1 of rank r receives the slice from rank r - k
                 g.rs_stage = self._symm.empty((self.world - 1) * g.shard_numel, dtype=torch.float32, device=self.device)
                 h2 = self._symm.rendezvous(g.rs_stage, group=self.pg if self.pg is not None else dist.group.WORLD)
@@ -242,7 +271,14 @@ class ShardedEngine:
             self.comm_stream.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(self.comm_stream):
                 part.zero_()
-                if self.world > 1 and g.peer_stage is not None:
+                if self.world > 1 and g.peer_grad_ptrs is not None:
+                    # reduce-scatter by pulling: once every rank's gradients of this group are final (barrier),
+                    # one kernel reads this rank's slice out of every rank's buffer over NVLink, sums, scales and
+                    # accumulates the squared norm. Nobody writes these buffers again before the parameter
+                    # all-gather barriers of this step, which every rank reaches only after its own pull.
+                    self._peer_barrier()
+                    self._reduce_peers(g, part)
+                elif self.world > 1 and g.peer_stage is not None:
                     # reduce-scatter by the copy engines: every rank pushes the slice owned by rank r into the
                     # slot it has in r's staging buffer; after the barrier one kernel sums the slots with the
                     # local slice, scales by 1 / world and accumulates the squared norm
@@ -332,6 +368,22 @@ class ShardedEngine:
                                  g.grad_shard.data_ptr(), g.shard_numel, 1.0 / self.world, part.data_ptr(),
                                  _lib.stream_ptr())
         _lib.check(rc, "lb_reduce_slots")
+
+    def _reduce_peers(self, g: ParamGroup, part: torch.Tensor) -> None:
+        import ctypes as C
+
+        from ..ops import _lib
+
+        lib = _lib.load()
+        if not getattr(lib, "_reduce_peers_declared", False):
+            lib.lb_reduce_peers.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_longlong, C.c_float, C.c_void_p,
+                                            C.c_void_p]
+            lib.lb_reduce_peers.restype = C.c_int
+            lib._reduce_peers_declared = True
+        srcs = (C.c_void_p * self.world)(*g.peer_grad_ptrs)
+        rc = lib.lb_reduce_peers(srcs, self.world, g.grad_shard.data_ptr(), g.shard_numel, 1.0 / self.world,
+                                 part.data_ptr(), _lib.stream_ptr())
+        _lib.check(rc, "lb_reduce_peers")
 
     def _peer_barrier(self) -> None:
         from .tp_fused import peer_barrier
