@@ -22,6 +22,8 @@ def run(p2p: bool, rank: int, world: int, dev):
     tr = Trainer(args, DistributedArgs(dp_shard=world, fsdp_type="full_shard", p2p_param_gather=p2p),
                  OptimArgs(lr=3e-3, warmup=1, clip=1.0), total_steps=100, device=dev)
     assert (tr.engine.groups[0].peer_full is not None) == p2p
+    pulls = p2p and os.environ.get("LB_P2P_REDUCE", "push") == "pull"
+    assert (tr.engine.groups[0].peer_grad_ptrs is not None) == pulls, "reduce mode did not take effect"
     g = torch.Generator().manual_seed(100 + rank)
     losses = []
     tok = torch.randint(0, 1024, (2, 257), generator=g)  # one batch per rank, repeated: the loss must go down

@@ -22,9 +22,13 @@ def test_fused_tp_two_ranks():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_engine_p2p_parameter_gather_two_ranks():
+@pytest.mark.parametrize("reduce_mode", ["push", "pull"])
+def test_engine_p2p_parameter_gather_two_ranks(reduce_mode):
+    """Peer-memory collectives of the sharded engine against its NCCL path (same losses, same parameters);
+    the gradient reduce-scatter once through staging slots and once by pulling the peers' buffers."""
     worker = Path(__file__).with_name("engine_p2p_worker.py")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
            "--master-addr", "127.0.0.1", "--master-port", "29654", str(worker)]
-    r = subprocess.run(cmd, env=dict(os.environ), capture_output=True, text=True, timeout=600)
+    r = subprocess.run(cmd, env=dict(os.environ, LB_P2P_REDUCE=reduce_mode), capture_output=True, text=True,
+                       timeout=600)
     assert r.returncode == 0 and "ENGINE_P2P_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
