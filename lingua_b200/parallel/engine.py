@@ -188,18 +188,18 @@ class ShardedEngine:
                     mine = self.rank * g.shard_numel * 4
                     ring = [(self.rank + k) % self.world for k in range(self.world)]  # own first, then the ring
                     g.peer_grad_ptrs = [int(hg.buffer_ptrs[r]) + mine for r in ring]
-                    self.groups.append(g)
-                    return
-                # staging of the gradient reduce-scatter: slot k-1 of rank r receives the slice from rank r - k
-                g.rs_stage = self._symm.empty((self.world - 1) * g.shard_numel, dtype=torch.float32, device=self.device)
-                h2 = self._symm.rendezvous(g.rs_stage, group=self.pg if self.pg is not None else dist.group.WORLD)
-                g.peer_stage = [h2.get_buffer(r, (self.world - 1, g.shard_numel), torch.float32)
-                                for r in range(self.world)]
+                if g.peer_grad_ptrs is None:
+                    # staging of the gradient reduce-scatter: slot k-1 of rank r receives the slice from rank r - k
+                    g.rs_stage = self._symm.empty((self.world - 1) * g.shard_numel, dtype=torch.float32,
+                                                  device=self.device)
+                    h2 = self._symm.rendezvous(g.rs_stage, group=self.pg if self.pg is not None else dist.group.WORLD)
+                    g.peer_stage = [h2.get_buffer(r, (self.world - 1, g.shard_numel), torch.float32)
+                                    for r in range(self.world)]
             except Exception as e:  # this group then uses the NCCL collectives
                 import logging
 
                 logging.getLogger(__name__).warning("no peer view of group %s: %s", path, e)
-                g.peer_full = g.peer_stage = None
+                g.peer_full = g.peer_stage = g.peer_grad_ptrs = None
         self.groups.append(g)
         for fqn, new_p in g.params:
             owner_path, _, attr = fqn.rpartition(".")
