@@ -135,6 +135,45 @@ def main(argv=None):
         x, w = torch.randn(B, S, C, device=dev, dtype=bf), torch.randn(C, 4, device=dev, dtype=bf)
         fn = lambda: Q.causal_conv1d(x, w)
         bytes_ = 2.0 * B * S * C * 2
+    elif a.op in ("indexed_matmul", "indexed_matmul_loop"):
+        # the distance-indexed up-projection of the hierarchical byte model, forward + backward:
+        # --m rows, --k inputs, --n outputs, 16 weights; "_loop" = one masked product per weight with a
+        # torch.where per weight in forward and again in backward (the formulation this library replaces)
+        from .indexed_matmul import indexed_matmul
+
+        T, Din, Dout, nW = a.m, a.k, a.n, 16
+        x = (torch.randn(T, Din, device=dev) * 0.5).to(bf).requires_grad_()
+        w = (torch.randn(nW, Dout, Din, device=dev) * Din ** -0.5).to(bf).requires_grad_()
+        idx = (torch.arange(T, device=dev) % 23 % nW).view(1, T)  # short distances are the common ones
+        g = torch.randn(1, T, Dout, device=dev, dtype=bf)
+
+        class Loop(torch.autograd.Function):
+            @staticmethod
+            def forward(ctx, X, W, I):
+                ctx.save_for_backward(X, W, I)
+                Y = X.new_empty(X.shape[0], X.shape[1], W.shape[1])
+                for n_ in range(W.shape[0]):
+                    bi, si = torch.where(I == n_)
+                    if si.numel():
+                        Y[bi, si] = torch.nn.functional.linear(X[bi, si], W[n_])
+                return Y
+
+            @staticmethod
+            def backward(ctx, dY):
+                X, W, I = ctx.saved_tensors
+                dX, dW = torch.zeros_like(X), torch.zeros_like(W)
+                for n_ in range(W.shape[0]):
+                    bi, si = torch.where(I == n_)
+                    if si.numel():
+                        dX[bi, si] = dY[bi, si] @ W[n_]
+                        dW[n_] = dY[bi, si].t() @ X[bi, si]
+                return dX, dW, None
+
+        def fn():
+            x.grad = w.grad = None
+            y = indexed_matmul(x.view(1, T, Din), w, idx) if a.op == "indexed_matmul" else Loop.apply(x.view(1, T, Din), w, idx)
+            y.backward(g)
+        flops = 3 * 2.0 * T * Din * Dout
     elif a.op == "decode":
         import math
 
