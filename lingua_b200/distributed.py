@@ -57,7 +57,10 @@ class EnvironmentArgs:
     MKL_SERVICE_FORCE_INTEL: str = "GNU"
     OMP_NUM_THREADS: str = "1"
     MKL_NUM_THREADS: str = "1"
-    ENABLE_INTRA_NODE_COMM: str = "1"
+    # The reference sets this to "1" (PyTorch's own intra-node all-reduce). Off here: the engine has its own
+    # peer-memory collectives, and with PyTorch 2.11 the option makes the NCCL process group fail to initialise
+    # ("Could not resolve the process group registered under the name IntraNodeComm0").
+    ENABLE_INTRA_NODE_COMM: str = "0"
     TORCH_NCCL_AVOID_RECORD_STREAMS: str = "1"
     NCCL_IB_TIMEOUT: str = "22"
     NCCL_DEBUG: str = "INFO"
