@@ -84,4 +84,9 @@ class Trainer:
         return loss.detach()
 
     def train_step(self, batch, doc_start=None, doc_end=None) -> float:
-        return float(self.train_step_async(batch, doc_start, doc_end).item())
+        loss = float(self.train_step_async(batch, doc_start, doc_end).item())
+        if self.device.type == "cuda":
+            from .ops import _lib
+
+            _lib.check_status()  # raises if a bounded wait of any kernel (peer barrier, copy) ran out during the step
+        return loss

@@ -972,12 +972,7 @@ extern "C" int lb_attn_fwd(const LbAttnArgs* a, void* stream) {
   p.causal = a->causal; p.window = a->window; p.scale = a->scale;
   p.doc_start = a->doc_start; p.doc_end = a->doc_end;
   p.O = (__nv_bfloat16*)a->o; p.lse = a->lse; p.status = a->status;
-  static bool attr = false;
-  if (!attr) {
-    if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM) != cudaSuccess)
-      return 20;
-    attr = true;
-  }
+  if (ensure_dyn_smem<attn_fwd_kernel>(FWD_SMEM)) return 20;
   dim3 grid(((a->S + 127) / 128 + 1) / 2, a->H, a->B);
   attn_fwd_kernel<<<grid, FWD_THREADS, FWD_SMEM, (cudaStream_t)stream>>>(tq, tk, tv, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -1015,12 +1010,7 @@ extern "C" int lb_attn_bwd(const LbAttnArgs* a, void* stream) {
   p.k_sb = a->k_sb; p.k_ss = a->k_ss; p.k_sh = a->k_sh;
   p.v_sb = a->v_sb; p.v_ss = a->v_ss; p.v_sh = a->v_sh;
   p.status = a->status;
-  static bool attr = false;
-  if (!attr) {
-    if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM) != cudaSuccess)
-      return 20;
-    attr = true;
-  }
+  if (ensure_dyn_smem<attn_bwd_kernel>(BWD_SMEM)) return 20;
   dim3 grid((a->S + 127) / 128, a->Hkv, a->B);
   attn_bwd_kernel<<<grid, BWD_THREADS, BWD_SMEM, st>>>(tq, tk, tv, tdo, tdq, p);
   long long total = rows * 16;

@@ -334,12 +334,7 @@ static int launch_gemm(const LbGemmArgs& a, cudaStream_t stream) {
   const long long tiles = (long long)p.tiles_m * p.tiles_n * a.nb0 * a.nb1;
   const int grid = (int)(tiles < num_sms() ? tiles : num_sms());
   auto kern = gemm_kernel<BN, ESZ, AMAJ, BMAJ, OutT>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
-    if (e != cudaSuccess) return 300 + (int)e;
-    attr_set = true;
-  }
+  if (ensure_dyn_smem<gemm_kernel<BN, ESZ, AMAJ, BMAJ, OutT>>(Cfg::SMEM)) return 300;
   kern<<<grid, GEMM_THREADS, Cfg::SMEM, stream>>>(ta, tb, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   cudaError_t e = cudaGetLastError();

@@ -201,12 +201,7 @@ static int launch(const LbGemmFp8Args& a, cudaStream_t stream) {
   const long long tiles = (long long)p.tiles_m * p.tiles_n;
   const int grid = (int)(tiles < num_sms() ? tiles : num_sms());
   auto kern = gemm_fp8_kernel<OutT>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-    if (e != cudaSuccess) return 300 + (int)e;
-    attr_set = true;
-  }
+  if (ensure_dyn_smem<gemm_fp8_kernel<OutT>>(SMEM)) return 300;
   kern<<<grid, THREADS, SMEM, stream>>>(ta, tb, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   cudaError_t e = cudaGetLastError();

@@ -420,12 +420,7 @@ static int launch(const LbTpGemmArgs& a, cudaStream_t stream) {
   const long long tiles = (long long)W * p.tiles_per_slab * p.tiles_n;
   const int grid = (int)(tiles < num_sms() ? tiles : num_sms());
   auto kern = gemm_tp_kernel<MODE>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-    if (e != cudaSuccess) return 300 + (int)e;
-    attr_set = true;
-  }
+  if (ensure_dyn_smem<gemm_tp_kernel<MODE>>(SMEM)) return 300;
   kern<<<grid, THREADS, SMEM, stream>>>(ta, tg, tb, owners, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   cudaError_t e = cudaGetLastError();

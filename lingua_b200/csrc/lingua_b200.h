@@ -69,6 +69,8 @@ int lb_attn_bwd(const LbAttnArgs* a, void* stream);
 //     rejected with return code 30 and nothing is launched.
 //   * The first call on each device looks up the array's device address (with that device
 //     current). Make that first call outside any stream capture.
+//   * `stream` must belong to the device that is current when the call is made: the scratch
+//     address is chosen by the current device, not by the stream.
 //   * All calls on one GPU share the array. Each call clears the part that must start at zero
 //     on its own stream, but two calls that overlap in time on the same GPU (different streams,
 //     threads or processes sharing the context) race on it: serialise them.
@@ -167,6 +169,19 @@ struct LbGemmArgsFwd;
 int make_tmap_4d(CUtensorMap* out, const void* base, int esz, long long inner, long long outer,
                  long long ld, int nb0, long long bs0, int nb1, long long bs1, int box_inner,
                  int box_outer);
+// Opt a kernel in to `bytes` of dynamic shared memory. The attribute belongs to the (function, device) pair,
+// so it is set once per device that launches the kernel, with that device current. Returns 0 on success.
+template <auto Kern>
+int ensure_dyn_smem(int bytes) {
+  static bool done[64] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 1;
+  if (!done[dev]) {
+    if (cudaFuncSetAttribute(Kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return 2;
+    done[dev] = true;
+  }
+  return 0;
+}
 // two-SM (cta_group::2) 256 x 256-tile variant, gemm2.cu
 int gemm2_dispatch(const LbGemmArgs& a, cudaStream_t s);
 }

@@ -33,6 +33,7 @@ from .distributed import (DistributedArgs, EnvironmentArgs, check_model_value_ra
                           requeue_slurm_job, setup_env, setup_torch_distributed)
 from .logger import init_logger
 from .metrics import GPUMemoryMonitor, LoggingArgs, MetricLogger, get_num_params, peak_flops
+from .ops import _lib as kernel_lib
 from .optim import LRScheduler, OptimArgs, build_engine_optim, build_lr_fn
 from .profiling import ProfilerArgs, maybe_run_profiler
 from .tokenizer import build_tokenizer
@@ -278,6 +279,9 @@ def run_training(args: TrainArgs, spec: ModelSpec) -> Dict[str, Any]:
             if on_gpu:
                 end_timer.record()
                 torch.cuda.synchronize()
+                # a kernel whose bounded wait ran out (a peer that never arrived at a barrier, a copy that never
+                # landed) has left a code in the status word: stop here instead of training on partial data
+                kernel_lib.check_status()
                 curr_iter_time = round(start_timer.elapsed_time(end_timer) * 1e-3, 4)
             else:
                 curr_iter_time = round(timer() - t_start, 4)
