@@ -6,6 +6,21 @@
 // SM shrinks a stage to 32 KB, which buys a 6-deep TMA ring instead of 4.
 //
 // Same contract as gemm_kernel in gemm.cu (operand majors, alpha, fp32 accumulate, batching).
+//
+// Epilogue: the four epilogue warps of a CTA move the accumulator TMEM -> registers -> a
+// 128-byte-swizzled shared-memory piece of 128 rows x 128 bytes, and one thread hands the piece
+// to the TMA unit (cp.async.bulk.tensor store, or cp.reduce...add when accumulating into an fp32
+// output, which needs no read of C by the SM). Every row of a piece is one full 128-byte line.
+//
+// Scatter mode (fp32 output, lb_gemm_scatter): the rows of the output are owned by the ranks of a
+// data-parallel group in blocks of 128 rows. A table gives (owner, destination row) per block;
+// the TMA store of a piece goes straight into the owner's buffer -- over NVLink when the owner is
+// a peer -- so the reduce-scatter of a weight gradient (lingua/distributed.py:434-463 leaves it to
+// FSDP2's post-backward NCCL reduce-scatter) travels tile by tile underneath the main loop of the
+// following tiles. The kernel waits on no other GPU; cross-rank ordering is the caller's job.
+//
+// Tiles are walked in groups of `group_m` row tiles (all column tiles of a group before the next
+// group), so the tiles in flight at any time share few distinct A and B panels in L2.
 #include "common.cuh"
 #include "lingua_b200.h"
 
@@ -18,7 +33,12 @@ constexpr int G2_BK = 64;                 // bf16 elements per stage (128 bytes)
 constexpr int G2_A_BYTES = G2_ROWS * 128;
 constexpr int G2_STAGE_BYTES = 2 * G2_A_BYTES;
 constexpr int G2_STAGES = 6;
-constexpr int G2_SMEM = G2_STAGES * G2_STAGE_BYTES + 1024 + 256;
+constexpr int G2_PIECE = G2_ROWS * 128;   // one epilogue piece: 128 rows x 128 bytes
+constexpr int G2_SMEM = G2_STAGES * G2_STAGE_BYTES + 2 * G2_PIECE + 1024 + 256;
+
+struct OwnerMaps {
+  CUtensorMap m[LB_MAX_PEERS];
+};
 
 struct Gemm2Params {
   int M, N, K;
@@ -26,9 +46,27 @@ struct Gemm2Params {
   long long ldc, c_bs0, c_bs1;
   float alpha;
   int accumulate;
+  int epi_tma;        // epilogue through shared memory + TMA (C meets the TMA alignment rules)
+  int scatter;        // rows go to their owners' buffers (fp32 only)
+  int group_m;        // row tiles per rasterisation group
+  int m_rot;          // the walk over row tiles starts at this tile (scatter: rows that have to travel first)
+  const int2* blocks; // scatter: (owner, destination row) per 128-row block of M
   void* C;
   uint32_t* status;
 };
+
+// tile index inside one batch -> (row tile, column tile)
+__device__ __forceinline__ void g2_tile_coords(int t, const Gemm2Params& p, int& mt, int& nt) {
+  const int per_group = p.group_m * p.tiles_n;
+  const int grp = t / per_group;
+  const int first = grp * p.group_m;
+  const int gsz = min(p.group_m, p.tiles_m - first);
+  const int r = t - grp * per_group;
+  nt = r / gsz;
+  mt = first + (r - nt * gsz) + p.m_rot;
+  if (mt >= p.tiles_m) mt -= p.tiles_m;
+}
+__device__ __forceinline__ void g2_epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -88,13 +126,15 @@ __device__ __forceinline__ void umma2_commit(uint32_t bar_cluster) {
 template <int AMAJ, int BMAJ, typename OutT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
 gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+             const __grid_constant__ CUtensorMap tma_c, const __grid_constant__ OwnerMaps owners,
              const Gemm2Params p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ int abort_flag;
   __shared__ uint32_t tmem_base_slot;
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t bar_base = smem_base + G2_STAGES * G2_STAGE_BYTES;
+  const uint32_t aux_base = smem_base + G2_STAGES * G2_STAGE_BYTES;
+  const uint32_t bar_base = aux_base + 2 * G2_PIECE;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (G2_STAGES + s); };
   auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * G2_STAGES + a); };
@@ -141,8 +181,10 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
       for (int tile = pair; ok && tile < num_tiles; tile += n_pairs) {
         const int batch = tile / tiles_per_batch;
         const int t = tile - batch * tiles_per_batch;
-        const int m0 = (t % p.tiles_m) * G2_BM + rank * G2_ROWS;
-        const int n0 = (t / p.tiles_m) * G2_BN + rank * G2_ROWS;
+        int mt, nt;
+        g2_tile_coords(t, p, mt, nt);
+        const int m0 = mt * G2_BM + rank * G2_ROWS;
+        const int n0 = nt * G2_BN + rank * G2_ROWS;
         const int b0 = batch % p.nb0, b1 = batch / p.nb0;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % G2_STAGES;
@@ -212,55 +254,124 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
   } else {
     // -------------------------------------------------- epilogue (warps 2..5, both CTAs)
     const int quarter = warp & 3;
-    uint32_t tile_iter = 0;
+    const int trow = quarter * 32 + lane;
+    const bool issuer = (warp == 2 && lane == 0);
+    constexpr int PC = 128 / (int)sizeof(OutT);  // columns per piece: 32 fp32 or 64 bf16
+    uint32_t tile_iter = 0, piece_iter = 0;
     for (int tile = pair; tile < num_tiles; tile += n_pairs, ++tile_iter) {
       const int acc = tile_iter & 1;
       const uint32_t acc_ph = (tile_iter >> 1) & 1u;
       const int batch = tile / tiles_per_batch;
       const int t = tile - batch * tiles_per_batch;
-      const int m0 = (t % p.tiles_m) * G2_BM + rank * G2_ROWS;
-      const int n0 = (t / p.tiles_m) * G2_BN;
+      int mt, nt;
+      g2_tile_coords(t, p, mt, nt);
+      const int m0 = mt * G2_BM + rank * G2_ROWS;
+      const int n0 = nt * G2_BN;
       const int b0 = batch % p.nb0, b1 = batch / p.nb0;
       if (!mbar_wait(tfull_bar(acc), acc_ph, &abort_flag, p.status, 0x34)) break;
       tc_fence_after();
-      const int row = m0 + quarter * 32 + lane;
-      OutT* crow = reinterpret_cast<OutT*>(p.C) + b0 * p.c_bs0 + b1 * p.c_bs1 + static_cast<long long>(row) * p.ldc;
       const uint32_t taddr = tmem_base + acc * G2_BN + (static_cast<uint32_t>(quarter * 32) << 16);
+      if (p.epi_tma) {
+        if (m0 < p.M) {
+          const CUtensorMap* cmap = &tma_c;
+          int drow = m0;
+          if (p.scatter) {
+            const int2 e = p.blocks[m0 / G2_ROWS];
+            cmap = &owners.m[e.x];
+            drow = e.y;
+          }
 #pragma unroll 1
-      for (int c = 0; c < G2_BN / 32; ++c) {
-        const int col0 = n0 + c * 32;
-        if (col0 >= p.N) break;
-        uint32_t r[32];
-        tmem_ld32(taddr + c * 32, r);
-        tmem_wait_ld();
-        if (row < p.M) {
-          if (sizeof(OutT) == 2) {
+          for (int c = 0; c < G2_BN / PC; ++c) {
+            const int col0 = n0 + c * PC;
+            if (col0 >= p.N) break;  // uniform over the four warps
+            const uint32_t buf = aux_base + (piece_iter & 1u) * G2_PIECE;
+            if (issuer) tma_store_wait_read<1>();  // the store that last used this buffer has read it
+            g2_epi_bar_sync();
+            const uint32_t rowbase = buf + trow * 128;
+            const uint32_t sw = static_cast<uint32_t>(trow & 7);
+            if (sizeof(OutT) == 4) {
+              uint32_t r[32];
+              tmem_ld32(taddr + c * 32, r);
+              tmem_wait_ld();
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              if (col0 + g * 8 < p.N) {
-                uint4 v;
-                v.x = pack_bf16(__uint_as_float(r[g * 8 + 0]) * p.alpha, __uint_as_float(r[g * 8 + 1]) * p.alpha);
-                v.y = pack_bf16(__uint_as_float(r[g * 8 + 2]) * p.alpha, __uint_as_float(r[g * 8 + 3]) * p.alpha);
-                v.z = pack_bf16(__uint_as_float(r[g * 8 + 4]) * p.alpha, __uint_as_float(r[g * 8 + 5]) * p.alpha);
-                v.w = pack_bf16(__uint_as_float(r[g * 8 + 6]) * p.alpha, __uint_as_float(r[g * 8 + 7]) * p.alpha);
-                *reinterpret_cast<uint4*>(crow + col0 + g * 8) = v;
+              for (int g = 0; g < 8; ++g) {
+                const uint32_t dst = rowbase + ((static_cast<uint32_t>(g) ^ sw) << 4);
+                const uint32_t v0 = __float_as_uint(__uint_as_float(r[g * 4 + 0]) * p.alpha);
+                const uint32_t v1 = __float_as_uint(__uint_as_float(r[g * 4 + 1]) * p.alpha);
+                const uint32_t v2 = __float_as_uint(__uint_as_float(r[g * 4 + 2]) * p.alpha);
+                const uint32_t v3 = __float_as_uint(__uint_as_float(r[g * 4 + 3]) * p.alpha);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v0), "r"(v1), "r"(v2), "r"(v3)
+                             : "memory");
+              }
+            } else {
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                uint32_t r[32];
+                tmem_ld32(taddr + c * 64 + h * 32, r);
+                tmem_wait_ld();
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                  const uint32_t dst = rowbase + ((static_cast<uint32_t>(h * 4 + g) ^ sw) << 4);
+                  const uint32_t v0 = pack_bf16(__uint_as_float(r[g * 8 + 0]) * p.alpha, __uint_as_float(r[g * 8 + 1]) * p.alpha);
+                  const uint32_t v1 = pack_bf16(__uint_as_float(r[g * 8 + 2]) * p.alpha, __uint_as_float(r[g * 8 + 3]) * p.alpha);
+                  const uint32_t v2 = pack_bf16(__uint_as_float(r[g * 8 + 4]) * p.alpha, __uint_as_float(r[g * 8 + 5]) * p.alpha);
+                  const uint32_t v3 = pack_bf16(__uint_as_float(r[g * 8 + 6]) * p.alpha, __uint_as_float(r[g * 8 + 7]) * p.alpha);
+                  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v0), "r"(v1), "r"(v2), "r"(v3)
+                               : "memory");
+                }
               }
             }
-          } else {
+            fence_proxy_async_smem();
+            g2_epi_bar_sync();
+            if (issuer) {
+              if (sizeof(OutT) == 4 && p.accumulate)
+                tma_reduce_add_4d(cmap, buf, col0, drow, b0, b1);
+              else
+                tma_store_4d(cmap, buf, col0, drow, b0, b1);
+              tma_store_commit();
+            }
+            ++piece_iter;
+          }
+        }
+      } else {
+        const int row = m0 + trow;
+        OutT* crow = reinterpret_cast<OutT*>(p.C) + b0 * p.c_bs0 + b1 * p.c_bs1 + static_cast<long long>(row) * p.ldc;
+#pragma unroll 1
+        for (int c = 0; c < G2_BN / 32; ++c) {
+          const int col0 = n0 + c * 32;
+          if (col0 >= p.N) break;
+          uint32_t r[32];
+          tmem_ld32(taddr + c * 32, r);
+          tmem_wait_ld();
+          if (row < p.M) {
+            if (sizeof(OutT) == 2) {
 #pragma unroll
-            for (int g = 0; g < 8; ++g) {
-              if (col0 + g * 4 < p.N) {
-                float4* dst = reinterpret_cast<float4*>(crow + col0 + g * 4);
-                float4 v;
-                v.x = __uint_as_float(r[g * 4 + 0]) * p.alpha;
-                v.y = __uint_as_float(r[g * 4 + 1]) * p.alpha;
-                v.z = __uint_as_float(r[g * 4 + 2]) * p.alpha;
-                v.w = __uint_as_float(r[g * 4 + 3]) * p.alpha;
-                if (p.accumulate) {
-                  const float4 o = *dst;
-                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+              for (int g = 0; g < 4; ++g) {
+                if (col0 + g * 8 < p.N) {
+                  uint4 v;
+                  v.x = pack_bf16(__uint_as_float(r[g * 8 + 0]) * p.alpha, __uint_as_float(r[g * 8 + 1]) * p.alpha);
+                  v.y = pack_bf16(__uint_as_float(r[g * 8 + 2]) * p.alpha, __uint_as_float(r[g * 8 + 3]) * p.alpha);
+                  v.z = pack_bf16(__uint_as_float(r[g * 8 + 4]) * p.alpha, __uint_as_float(r[g * 8 + 5]) * p.alpha);
+                  v.w = pack_bf16(__uint_as_float(r[g * 8 + 6]) * p.alpha, __uint_as_float(r[g * 8 + 7]) * p.alpha);
+                  *reinterpret_cast<uint4*>(crow + col0 + g * 8) = v;
                 }
-                *dst = v;
+              }
+            } else {
+#pragma unroll
+              for (int g = 0; g < 8; ++g) {
+                if (col0 + g * 4 < p.N) {
+                  float4* dst = reinterpret_cast<float4*>(crow + col0 + g * 4);
+                  float4 v;
+                  v.x = __uint_as_float(r[g * 4 + 0]) * p.alpha;
+                  v.y = __uint_as_float(r[g * 4 + 1]) * p.alpha;
+                  v.z = __uint_as_float(r[g * 4 + 2]) * p.alpha;
+                  v.w = __uint_as_float(r[g * 4 + 3]) * p.alpha;
+                  if (p.accumulate) {
+                    const float4 o = *dst;
+                    v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                  }
+                  *dst = v;
+                }
               }
             }
           }
@@ -270,6 +381,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa(tempty_bar(acc), 0));
     }
+    if (issuer) tma_store_wait<0>();  // every piece has left shared memory and landed
   }
 
   __syncwarp();
@@ -289,8 +401,9 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
 }
 
 template <int AMAJ, int BMAJ, typename OutT>
-static int launch_gemm2(const LbGemmArgs& a, cudaStream_t stream) {
-  CUtensorMap ta, tb;
+static int launch_gemm2(const LbGemmArgs& a, const LbScatterArgs* sc, cudaStream_t stream) {
+  CUtensorMap ta, tb, tc;
+  OwnerMaps owners;
   int rc;
   if (AMAJ == 0)
     rc = make_tmap_4d(&ta, a.A, 2, a.K, a.M, a.lda, a.nb0, a.a_bs0, a.nb1, a.a_bs1, G2_BK, G2_ROWS);
@@ -310,34 +423,75 @@ static int launch_gemm2(const LbGemmArgs& a, cudaStream_t stream) {
   p.ldc = a.ldc; p.c_bs0 = a.c_bs0; p.c_bs1 = a.c_bs1;
   p.alpha = a.alpha; p.accumulate = a.accumulate;
   p.C = a.C; p.status = a.status;
+  p.group_m = p.tiles_m < 8 ? p.tiles_m : 8;
+  p.m_rot = 0;
+  p.scatter = 0;
+  p.blocks = nullptr;
+  constexpr int ESZ = (int)sizeof(OutT);
+  constexpr int PC = 128 / ESZ;
+  // TMA stores need a 16-byte aligned base and pitches that are multiples of 16 bytes
+  auto tma_ok = [&](const void* base) {
+    return (reinterpret_cast<uintptr_t>(base) % 16 == 0) && (a.ldc * ESZ) % 16 == 0 &&
+           (a.nb0 <= 1 || (a.c_bs0 * ESZ) % 16 == 0) && (a.nb1 <= 1 || (a.c_bs1 * ESZ) % 16 == 0);
+  };
+  if (sc) {
+    if (ESZ != 4 || a.nb0 != 1 || a.nb1 != 1) return 6;
+    for (int o = 0; o < LB_MAX_PEERS; ++o) {
+      const int src = o < sc->world ? o : 0;
+      if (!tma_ok(sc->dst[src]) || sc->dst_rows[src] < 0) return 7;
+      // an owner without rows in this product still needs a valid map (it is never used)
+      const long long rows = sc->dst_rows[src] > 0 ? sc->dst_rows[src] : 1;
+      rc = make_tmap_4d(&owners.m[o], sc->dst[src], ESZ, a.N, rows, a.ldc, 1, 0, 1, 0, PC, G2_ROWS);
+      if (rc) return 120 + rc;
+    }
+    tc = owners.m[0];
+    p.scatter = 1;
+    p.epi_tma = 1;
+    p.blocks = reinterpret_cast<const int2*>(sc->blocks);
+    p.m_rot = sc->m_rot >= 0 && sc->m_rot < p.tiles_m ? sc->m_rot : 0;
+  } else {
+    p.epi_tma = tma_ok(a.C) ? 1 : 0;
+    if (p.epi_tma) {
+      rc = make_tmap_4d(&tc, a.C, ESZ, a.N, a.M, a.ldc, a.nb0, a.c_bs0, a.nb1, a.c_bs1, PC, G2_ROWS);
+      if (rc) return 110 + rc;
+    } else {
+      tc = ta;
+    }
+    for (int o = 0; o < LB_MAX_PEERS; ++o) owners.m[o] = tc;
+  }
   const long long tiles = (long long)p.tiles_m * p.tiles_n * a.nb0 * a.nb1;
   const int max_pairs = num_sms() / 2;
   const int pairs = (int)(tiles < max_pairs ? tiles : max_pairs);
-  auto kern = gemm2_kernel<AMAJ, BMAJ, OutT>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM);
-    if (e != cudaSuccess) return 300 + (int)e;
-    attr_set = true;
-  }
-  kern<<<2 * pairs, G2_THREADS, G2_SMEM, stream>>>(ta, tb, p);
+  if (ensure_dyn_smem<gemm2_kernel<AMAJ, BMAJ, OutT>>(G2_SMEM)) return 300;
+  gemm2_kernel<AMAJ, BMAJ, OutT><<<2 * pairs, G2_THREADS, G2_SMEM, stream>>>(ta, tb, tc, owners, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;
 }
 
 template <typename OutT>
-static int dispatch2(const LbGemmArgs& a, cudaStream_t s) {
-  if (a.a_major == 0 && a.b_major == 0) return launch_gemm2<0, 0, OutT>(a, s);
-  if (a.a_major == 0 && a.b_major == 1) return launch_gemm2<0, 1, OutT>(a, s);
-  if (a.a_major == 1 && a.b_major == 0) return launch_gemm2<1, 0, OutT>(a, s);
-  return launch_gemm2<1, 1, OutT>(a, s);
+static int dispatch2(const LbGemmArgs& a, const LbScatterArgs* sc, cudaStream_t s) {
+  if (a.a_major == 0 && a.b_major == 0) return launch_gemm2<0, 0, OutT>(a, sc, s);
+  if (a.a_major == 0 && a.b_major == 1) return launch_gemm2<0, 1, OutT>(a, sc, s);
+  if (a.a_major == 1 && a.b_major == 0) return launch_gemm2<1, 0, OutT>(a, sc, s);
+  return launch_gemm2<1, 1, OutT>(a, sc, s);
 }
 
 int gemm2_dispatch(const LbGemmArgs& a, cudaStream_t s) {
-  if (a.out_dtype == LB_BF16) return dispatch2<__nv_bfloat16>(a, s);
-  if (a.out_dtype == LB_F32) return dispatch2<float>(a, s);
+  if (a.out_dtype == LB_BF16) return dispatch2<__nv_bfloat16>(a, nullptr, s);
+  if (a.out_dtype == LB_F32) return dispatch2<float>(a, nullptr, s);
   return 5;
 }
 
 }  // namespace lb
+
+extern "C" int lb_gemm_scatter(const LbGemmArgs* args, const LbScatterArgs* sc, void* stream) {
+  using namespace lb;
+  if (!args || !sc) return 1;
+  const LbGemmArgs& a = *args;
+  if (a.M <= 0 || a.N <= 0 || a.K <= 0 || a.nb0 != 1 || a.nb1 != 1) return 1;
+  if (a.in_dtype != LB_BF16 || a.out_dtype != LB_F32) return 2;
+  if ((a.ldc % 4) || (a.lda % 8) || (a.ldb % 8) || a.ldc < a.N || (a.N % 4)) return 3;
+  if (sc->world < 1 || sc->world > LB_MAX_PEERS || !sc->blocks) return 4;
+  return dispatch2<float>(a, sc, reinterpret_cast<cudaStream_t>(stream));
+}

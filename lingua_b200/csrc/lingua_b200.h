@@ -130,6 +130,24 @@ typedef struct LbTpGemmArgs {
 } LbTpGemmArgs;
 int lb_gemm_tp(const LbTpGemmArgs* a, void* stream);
 
+// Weight-gradient GEMM with the reduce-scatter's transfer fused into its epilogue (gemm2.cu): the product
+// args->A * args->B^T (bf16 operands, fp32 result, no batching; args->C is ignored) is not written to one
+// local matrix; its rows belong to the ranks of a data-parallel group in blocks of 128 rows. `blocks` holds
+// one (owner, destination row) pair of ints per 128-row block of M; rows of owner o go to the matrix at dst[o]
+// (dst_rows[o] rows of N floats, row pitch args->ldc), a peer-visible address when o is another rank -- usually
+// this rank's slot in o's staging area, and this rank's own gradient shard for o == rank. args->accumulate adds
+// to the destination (TMA reduction) instead of overwriting it. m_rot: index of the 256-row tile the walk over
+// M starts at (the first rows that have to travel). The kernel waits on no other GPU: order the ranks with
+// lb_peer_barrier before the destinations are read and before they are written again.
+typedef struct LbScatterArgs {
+  int world;
+  int m_rot;
+  const int* blocks;
+  void* dst[LB_MAX_PEERS];
+  long long dst_rows[LB_MAX_PEERS];
+} LbScatterArgs;
+int lb_gemm_scatter(const LbGemmArgs* args, const LbScatterArgs* sc, void* stream);
+
 // Barrier over the ranks of a group. pads[r] is the peer-visible address of rank r's pad
 // (uint32[world], zero before first use); epoch is the number of this barrier on these pads,
 // counted from 1 by every rank alike. Bounded wait: on timeout the status word is set.

@@ -36,6 +36,13 @@ class GemmArgs(C.Structure):
     ]
 
 
+class ScatterArgs(C.Structure):
+    _fields_ = [
+        ("world", C.c_int), ("m_rot", C.c_int), ("blocks", C.c_void_p),
+        ("dst", C.c_void_p * 8), ("dst_rows", C.c_longlong * 8),
+    ]
+
+
 class AttnArgs(C.Structure):
     _fields_ = [
         ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("o", C.c_void_p), ("lse", C.c_void_p),
@@ -75,6 +82,9 @@ def load():
     lib = C.CDLL(str(_LIB_PATH))
     lib.lb_gemm.argtypes = [C.POINTER(GemmArgs), C.c_void_p]
     lib.lb_gemm.restype = C.c_int
+    if hasattr(lib, "lb_gemm_scatter"):
+        lib.lb_gemm_scatter.argtypes = [C.POINTER(GemmArgs), C.POINTER(ScatterArgs), C.c_void_p]
+        lib.lb_gemm_scatter.restype = C.c_int
     lib.lb_launch_count.restype = C.c_longlong
     lib.lb_launch_count_add.argtypes = [C.c_longlong]
     _declare(lib)

@@ -8,7 +8,7 @@ and M/N-contiguous operands directly, so the dgrad and wgrad GEMMs of a linear l
 from __future__ import annotations
 
 import ctypes as C
-from typing import Optional
+from typing import Optional, Sequence
 
 import torch
 
@@ -109,6 +109,46 @@ def gemm(
     rc = _lib.load().lb_gemm(C.byref(args), _lib.stream_ptr())
     _lib.check(rc, f"lb_gemm(M={M},N={N},K={K},majors={a_major}{b_major})")
     return out
+
+
+def gemm_scatter(a: torch.Tensor, b: torch.Tensor, blocks: torch.Tensor, dst_ptrs: Sequence[int],
+                 dst_rows: Sequence[int], ldc: int, accumulate: bool = False, alpha: float = 1.0,
+                 m_rot: int = 0) -> None:
+    """``a @ b^T`` ([M, K] x [N, K]^T, bf16) in fp32, written by owner instead of into one matrix.
+
+    ``blocks`` is an int32 device tensor [ceil(M / 128), 2] holding (owner, destination row) for every block of
+    128 result rows; the rows of owner ``o`` land in the [dst_rows[o], N] fp32 matrix at address ``dst_ptrs[o]``
+    (row pitch ``ldc`` elements), which may be peer memory. ``accumulate`` adds to the destination. The epilogue
+    of the SM-pair GEMM kernel performs the stores, so the transfer overlaps the remaining tiles' main loops.
+    """
+    assert a.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.dim() == 2 and b.dim() == 2
+    M, K = a.shape
+    N = b.shape[0]
+    assert b.shape[1] == K and blocks.dtype == torch.int32 and blocks.is_contiguous()
+    assert blocks.numel() >= 2 * ((M + 127) // 128)
+    a, b = _aligned(a), _aligned(b)
+    a_major, lda = _major_and_ld(a)
+    b_major, ldb = _major_and_ld(b)
+    args = _lib.GemmArgs()
+    args.A, args.B, args.C = a.data_ptr(), b.data_ptr(), 0
+    args.status = _lib.status_word(a.device).data_ptr()
+    args.M, args.N, args.K = M, N, K
+    args.a_major, args.b_major = a_major, b_major
+    args.in_dtype, args.out_dtype = _lib.LB_BF16, _lib.LB_F32
+    args.accumulate = int(accumulate)
+    args.alpha = float(alpha)
+    args.force_bn = 0
+    args.lda, args.ldb, args.ldc = lda, ldb, ldc
+    args.nb0 = args.nb1 = 1
+    sc = _lib.ScatterArgs()
+    sc.world = len(dst_ptrs)
+    sc.m_rot = int(m_rot)
+    sc.blocks = blocks.data_ptr()
+    for o, (ptr, rows) in enumerate(zip(dst_ptrs, dst_rows)):
+        sc.dst[o] = ptr
+        sc.dst_rows[o] = rows
+    rc = _lib.load().lb_gemm_scatter(C.byref(args), C.byref(sc), _lib.stream_ptr())
+    _lib.check(rc, f"lb_gemm_scatter(M={M},N={N},K={K})")
 
 
 def mm_nt(x: torch.Tensor, w: torch.Tensor, **kw) -> torch.Tensor:

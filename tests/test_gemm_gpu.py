@@ -96,3 +96,37 @@ def test_gemm_two_sm_batched_accumulate():
     c = c0.clone()
     G.gemm(a, b, out=c, accumulate=True, alpha=2.0, force_bn=512)
     _check(c, c0 + _ref(a, b, 2.0), 320)
+
+
+@pytest.mark.parametrize("W", [1, 2, 4, 8])
+@pytest.mark.parametrize("M,N,K", [(1024, 512, 512), (1400, 264, 320), (4096, 1024, 256)])
+def test_gemm_scatter_rows_to_owners(W, M, N, K):
+    """The scatter epilogue delivers every 128-row block to its owner's matrix (all "owners" are buffers of this
+    GPU here: the kernel never waits on a peer, so one device can stand in for the group). Uneven splits, a
+    rotated tile walk, overwrite and accumulate."""
+    torch.manual_seed(W)
+    dy = torch.randn(K, M, device="cuda", dtype=torch.bfloat16)  # [tokens, out]: the wgrad's MN-major A operand
+    x = torch.randn(K, N, device="cuda", dtype=torch.bfloat16)   # [tokens, in]
+    ref = dy.float().t() @ x.float()
+    nblk = (M + 127) // 128
+    bounds = [round(r * nblk / W) * 128 for r in range(W + 1)]
+    bounds[-1] = M
+    dst = [torch.full((max(bounds[o + 1] - bounds[o], 1) + 3, N), 7.0, device="cuda") for o in range(W)]
+    table = []
+    for blk in range(nblk):
+        o = max(i for i in range(W) if bounds[i] <= blk * 128)
+        table.append((o, blk * 128 - bounds[o]))
+    blocks = torch.tensor(table, dtype=torch.int32, device="cuda")
+    rows = [bounds[o + 1] - bounds[o] for o in range(W)]
+    ptrs = [d.data_ptr() for d in dst]
+    G.gemm_scatter(dy.t(), x.t(), blocks, ptrs, rows, ldc=N, m_rot=(bounds[1 % W] // 256) % max(1, (M + 255) // 256))
+    torch.cuda.synchronize()
+    for o in range(W):
+        if rows[o]:
+            _check(dst[o][:rows[o]], ref[bounds[o]:bounds[o + 1]], K)
+        assert (dst[o][rows[o]:] == 7.0).all(), "rows beyond an owner's share were touched"
+    G.gemm_scatter(dy.t(), x.t(), blocks, ptrs, rows, ldc=N, accumulate=True, alpha=0.5)
+    torch.cuda.synchronize()
+    for o in range(W):
+        if rows[o]:
+            _check(dst[o][:rows[o]], 1.5 * ref[bounds[o]:bounds[o + 1]], K)
