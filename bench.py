@@ -268,10 +268,9 @@ def main() -> None:
             if tr is None:
                 raise torch.OutOfMemoryError("the training step does not fit with or without activation recomputation")
             extra["selective_activation_checkpointing"] = sac
-            g0 = tr.engine.groups[0]
-            extra["collectives"] = ("none" if world == 1 else "nccl" if g0.peer_full is None else
-                                    "all-gather: nvlink copy engines; reduce-scatter: one kernel pulling peer gradients"
-                                    if g0.peer_grad_ptrs is not None else "nvlink copy engines + reduce kernel")
+            extra["collectives"] = ("none" if world == 1 else "nccl" if not tr.engine.p2p else
+                                    "reduce-scatter: weight-gradient GEMM epilogue stores row blocks into the owners' "
+                                    "slots over NVLink + one slot-sum kernel per group; all-gather: copy engines")
             host_batches = [views(h).contiguous().pin_memory() for h in host]
 
             def dev_step(i):

@@ -40,7 +40,8 @@ class Trainer:
         from .parallel.tensor_parallel import tp_parallelize as tp_plan
         self.model, self.engine = parallelize_model(model, self.mesh, model_args, self.dist_args,
                                                     fsdp_grouping_plan=plan, tp_parallelize=tp_plan,
-                                                    optim=build_engine_optim(self.optim_args), device=device)
+                                                    optim=build_engine_optim(self.optim_args), device=device,
+                                                    grad_acc_steps=grad_acc_steps)
         with torch.random.fork_rng(devices=[device] if device.type == "cuda" else []):
             torch.manual_seed(model_args.seed)
             self.engine.init_weights_fp32(self.model.init_weights)

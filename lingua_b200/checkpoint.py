@@ -94,6 +94,49 @@ def _device_mesh(engine):
     return engine._dcp_mesh
 
 
+def _tp_info(engine, fqn: str):
+    """(dim, degree, rank) of the tensor-parallel split of parameter ``fqn``, or None."""
+    owner, _, attr = fqn.rpartition(".")
+    try:
+        mod = engine.model.get_submodule(owner)
+    except AttributeError:
+        return None
+    info = getattr(mod, "tp_shard", None)
+    return info if (info is not None and attr == "weight") else None
+
+
+def _as_checkpoint_tensor(engine, fqn: str, p, full: torch.Tensor):
+    """``full`` holds this process's whole fp32 tensor of one parameter (its tensor-parallel slice when TP is on).
+    Returns what goes into the state dict under ``fqn``: always a description of the *unsplit* parameter, so that
+    every TP rank writes the same values under the same key and a checkpoint loads on any layout. Tensor-parallel
+    slices are first all-gathered over the TP group along their split dim; with more than one data-parallel rank
+    the result is a DTensor sharded on dim 0 over the shard group (torch.chunk sizes, the form FSDP2 checkpoints of
+    the reference have), else the plain tensor."""
+    from torch.distributed.tensor import DTensor, Shard
+
+    tp = _tp_info(engine, fqn) if engine.tp_pg is not None else None
+    if tp is not None:
+        dim, degree, _ = tp
+        parts = [torch.empty_like(full) for _ in range(degree)]
+        dist.all_gather(parts, full.contiguous(), group=engine.tp_pg)
+        full = torch.cat(parts, dim=dim)
+    W, R = engine.world, engine.rank
+    if W == 1:
+        return full
+    r0, r1 = _row_range(full.shape[0], W, R)
+    local = full[r0:r1].clone()
+    return DTensor.from_local(local, _device_mesh(engine), [Shard(0)], run_check=False, shape=full.shape,
+                              stride=_contig_stride(list(full.shape)))
+
+
+def _contig_stride(shape):
+    st, acc = [], 1
+    for d in reversed(shape):
+        st.append(acc)
+        acc *= d
+    return tuple(reversed(st))
+
+
 def engine_state_dict(engine, lr: float = 0.0) -> Dict[str, Any]:
     """``{"model": ..., "optim": ...}`` with the reference's keys; tensors are plain (one rank) or
     dim-0 sharded DTensors holding this rank's rows."""
@@ -105,27 +148,17 @@ def engine_state_dict(engine, lr: float = 0.0) -> Dict[str, Any]:
     names: List[str] = []
     step_t = torch.tensor(float(engine.step_count))
     for gi, g in enumerate(engine.groups):
-        if W == 1:
-            bufs = {"p": g.master, "m": g.exp_avg, "v": g.exp_avg_sq}
-        else:
-            bufs = {}
-            for key, shard in (("p", g.master), ("m", g.exp_avg), ("v", g.exp_avg_sq)):
-                full = torch.empty(g.padded, dtype=torch.float32, device=engine.device)
-                dist.all_gather_into_tensor(full, shard, group=engine.pg)
-                bufs[key] = full
+        # every rank assembles the group's fp32 tensors in parameter order and keeps its dim-0 chunk of each
+        # parameter: the engine's own shards are row slabs of uneven size, a DTensor wants torch.chunk sizes
+        bufs = {key: engine.export_group_fp32(gi, which)
+                for key, which in (("p", "master"), ("m", "exp_avg"), ("v", "exp_avg_sq"))}
         for fqn, p in g.params:
             o, n = g.offsets[fqn]
             names.append(fqn)
             out = {}
             for key in ("p", "m", "v"):
                 full = bufs[key][o:o + n].view(p.shape)
-                if W == 1:
-                    out[key] = full
-                else:
-                    r0, r1 = _row_range(p.shape[0], W, R)
-                    local = full[r0:r1].clone()
-                    out[key] = DTensor.from_local(local, _device_mesh(engine), [Shard(0)], run_check=False,
-                                                  shape=p.shape, stride=full.stride())
+                out[key] = _as_checkpoint_tensor(engine, fqn, p, full)
             model_sd[fqn] = out["p"]
             opt_state[fqn] = {"step": step_t.clone(), "exp_avg": out["m"], "exp_avg_sq": out["v"]}
         del bufs
@@ -137,26 +170,28 @@ def engine_state_dict(engine, lr: float = 0.0) -> Dict[str, Any]:
 
 
 def load_engine_state_dict(engine, sd: Dict[str, Any], load_optim: bool = True) -> None:
-    """Scatter a (loaded) state dict of the above form back into the engine's flat slices."""
+    """Scatter a (loaded) state dict of the above form back into the engine's shards."""
     from torch.distributed.tensor import DTensor
 
-    def full_of(t):
-        return (t.full_tensor() if isinstance(t, DTensor) else t).to(device=engine.device, dtype=torch.float32)
+    def local_of(fqn, t):
+        t = (t.full_tensor() if isinstance(t, DTensor) else t).to(device=engine.device, dtype=torch.float32)
+        tp = _tp_info(engine, fqn) if engine.tp_pg is not None else None
+        if tp is not None:
+            t = t.chunk(tp[1], dim=tp[0])[tp[2]]
+        return t
 
-    for g in engine.groups:
+    keys = [("master", lambda f: sd["model"][f])]
+    if load_optim and "optim" in sd:
+        keys += [("exp_avg", lambda f: sd["optim"]["state"][f]["exp_avg"]),
+                 ("exp_avg_sq", lambda f: sd["optim"]["state"][f]["exp_avg_sq"])]
+    for gi, g in enumerate(engine.groups):
         buf = torch.zeros(g.padded, dtype=torch.float32, device=engine.device)
-        for fqn, p in g.params:
-            o, n = g.offsets[fqn]
-            buf[o:o + n].copy_(full_of(sd["model"][fqn]).reshape(-1))
-        g.master.copy_(buf[g.shard_slice])
-        g.full.copy_(buf)
-        if load_optim and "optim" in sd:
-            for key, dst in (("exp_avg", g.exp_avg), ("exp_avg_sq", g.exp_avg_sq)):
-                buf.zero_()
-                for fqn, p in g.params:
-                    o, n = g.offsets[fqn]
-                    buf[o:o + n].copy_(full_of(sd["optim"]["state"][fqn][key]).reshape(-1))
-                dst.copy_(buf[g.shard_slice])
+        for which, get in keys:
+            buf.zero_()
+            for fqn, p in g.params:
+                o, n = g.offsets[fqn]
+                buf[o:o + n].copy_(local_of(fqn, get(fqn)).reshape(-1))
+            engine.load_group_fp32(gi, buf, which)
         del buf
     if load_optim and "optim" in sd:
         steps = [float(v["step"]) for v in sd["optim"]["state"].values()]

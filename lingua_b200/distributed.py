@@ -320,7 +320,7 @@ DTYPES = {"fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16}
 
 
 def parallelize_model(model, mesh: Mesh, model_args, distributed_args: DistributedArgs, fsdp_grouping_plan=None,
-                      tp_parallelize=None, no_recompute_ops=None, optim=None, device=None):
+                      tp_parallelize=None, no_recompute_ops=None, optim=None, device=None, grad_acc_steps: int = 1):
     """Shard ``model`` over the mesh's data-parallel axis and return (model, engine).
 
     ``fsdp_type``: ``full_shard`` shards parameters, gradients and optimiser state over dp_shard;
@@ -343,9 +343,18 @@ def parallelize_model(model, mesh: Mesh, model_args, distributed_args: Distribut
         device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
     dtype = DTYPES[distributed_args.model_dtype] if device.type == "cuda" else torch.float32
     assert distributed_args.fsdp_type in ("full_shard", "no_shard")
-    pg = mesh.group("dp") if mesh.size("dp") > 1 else False
-    engine = ShardedEngine(model, fsdp_grouping_plan, process_group=pg, compute_dtype=dtype, optim=optim, device=device,
-                           p2p_gather=distributed_args.p2p_param_gather)
+    # parameters, gradients and optimiser state are sharded over the dp_shard axis; the dp_replicate axis holds
+    # copies whose reduced gradients are averaged (hybrid sharding, lingua/distributed.py:106-113,441-446). With
+    # ``no_shard`` every data-parallel rank is a replica.
+    if distributed_args.fsdp_type == "no_shard":
+        shard_pg, rep_pg = False, (mesh.group("dp") if mesh.size("dp") > 1 else None)
+    else:
+        shard_pg = mesh.group("dp_shard") if mesh.size("dp_shard") > 1 else False
+        rep_pg = mesh.group("dp_replicate") if mesh.size("dp_replicate") > 1 else None
+    engine = ShardedEngine(model, fsdp_grouping_plan, process_group=shard_pg, replicate_group=rep_pg,
+                           tp_group=mesh.group("tp") if mesh.size("tp") > 1 else None, compute_dtype=dtype,
+                           optim=optim, device=device, p2p_gather=distributed_args.p2p_param_gather,
+                           accumulate=grad_acc_steps > 1)
     for buf_owner in model.modules():
         for name, buf in list(buf_owner._buffers.items()):
             if buf is not None and buf.device.type == "meta":

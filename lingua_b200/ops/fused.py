@@ -18,7 +18,7 @@ import torch
 
 from . import functional as F
 from .attention import flash_bwd, flash_fwd
-from .gemm import gemm, mm_nn, mm_nt, mm_tn
+from .gemm import gemm, gemm_scatter, mm_nn, mm_nt, mm_tn
 
 
 # Statistics probe (lingua_b200.probe.AutoProbeD): when set, the functions below report their
@@ -91,8 +91,38 @@ def _main_grads(ws: Sequence[torch.Tensor]) -> Optional[torch.Tensor]:
     return fused_view([w.main_grad for w in ws])
 
 
+def _emit_scatter(ws: Sequence[torch.Tensor], dy2d: torch.Tensor, x2d: torch.Tensor) -> bool:
+    """Weight gradient of row-sharded parameters (``w.lb_scatter``, set by the sharded engine): no local matrix is
+    written; the GEMM epilogue stores every 128-row block into its owner's buffer. One GEMM for the whole fused
+    weight when the engine can describe it with one block table, else one per parameter."""
+    targets = [w.lb_scatter for w in ws]
+    engine = targets[0].engine
+    written = [getattr(w, "grad_written", False) for w in ws]
+    if not dy2d.is_cuda:
+        return False
+    plan = engine.scatter_plan(targets) if (all(written) or not any(written)) else None
+    if plan is not None:
+        blocks, ptrs, rows, K, m_rot = plan
+        gemm_scatter(dy2d.transpose(0, 1), x2d.transpose(0, 1), blocks, ptrs, rows, ldc=K, accumulate=written[0],
+                     m_rot=m_rot)
+        for w in ws:
+            w.grad_written = True
+        return True
+    r0 = 0
+    for w, t, wr in zip(ws, targets, written):
+        n = w.shape[0]
+        blocks, ptrs, rows, K, m_rot = engine.scatter_plan([t])
+        gemm_scatter(dy2d[:, r0:r0 + n].transpose(0, 1), x2d.transpose(0, 1), blocks, ptrs, rows, ldc=K, accumulate=wr,
+                     m_rot=m_rot)
+        w.grad_written = True
+        r0 += n
+    return True
+
+
 def _emit_wgrad(ws: Sequence[torch.Tensor], dy2d: torch.Tensor, x2d: torch.Tensor) -> List[Optional[torch.Tensor]]:
     """dW_i = dy[:, rows_i]^T x for the row-blocks ``ws`` of one fused weight."""
+    if all(hasattr(w, "lb_scatter") for w in ws) and _emit_scatter(ws, dy2d, x2d):
+        return [None] * len(ws)
     mg = _main_grads(ws)
     if mg is not None:
         written = [getattr(w, "grad_written", False) for w in ws]
@@ -382,7 +412,9 @@ class LinearCrossEntropyFn(torch.autograd.Function):
                 del logits
             mm_nn(dl_all, wd, out=dy)
             if w.requires_grad:
-                if has_mg:
+                if hasattr(w, "lb_scatter") and _emit_scatter([w], dl_all, y):
+                    pass
+                elif has_mg:
                     mm_tn(dl_all, y, out=w.main_grad, accumulate=getattr(w, "grad_written", False))
                     w.grad_written = True
                 else:
@@ -399,7 +431,9 @@ class LinearCrossEntropyFn(torch.autograd.Function):
             del logits
             mm_nn(dl, wd, out=dy[r0:r1])
             if w.requires_grad:
-                if has_mg:
+                if hasattr(w, "lb_scatter") and _emit_scatter([w], dl, y[r0:r1]):
+                    pass
+                elif has_mg:
                     mm_tn(dl, y[r0:r1], out=w.main_grad, accumulate=getattr(w, "grad_written", False))
                     w.grad_written = True
                 else:
@@ -430,7 +464,9 @@ class LinearCrossEntropyFn(torch.autograd.Function):
             del logits
             mm_nn(dl, wd, out=dy[r0:r1])
             if w.requires_grad:
-                if has_mg:
+                if hasattr(w, "lb_scatter") and _emit_scatter([w], dl, y[r0:r1]):
+                    pass
+                elif has_mg:
                     mm_tn(dl, y[r0:r1], out=w.main_grad, accumulate=getattr(w, "grad_written", False))
                     w.grad_written = True
                 else:

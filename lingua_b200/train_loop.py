@@ -181,7 +181,8 @@ def run_training(args: TrainArgs, spec: ModelSpec) -> Dict[str, Any]:
         plan = spec.build_plan(args.model) if spec.build_plan else None
         model, engine = parallelize_model(model, mesh, args.model, args.distributed, fsdp_grouping_plan=plan,
                                           tp_parallelize=spec.tp_parallelize, optim=build_engine_optim(args.optim),
-                                          device=device)
+                                          device=device, grad_acc_steps=args.grad_acc_steps)
+        logger.info(f"Gradient / parameter collectives of the sharded engine: {engine.collective_path}")
         with torch.random.fork_rng(devices=[device] if on_gpu else []):
             torch.manual_seed(args.model.seed)
             engine.init_weights_fp32(model.init_weights)

@@ -21,14 +21,21 @@ def test_fused_tp_two_ranks():
     assert r.returncode == 0 and "TP_FUSED_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
 
 
+def _rank_counts():
+    n = min(torch.cuda.device_count(), 8)
+    return [w for w in (2, 4, 8) if w <= n] or [2]
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("reduce_mode", ["push", "pull"])
-def test_engine_p2p_parameter_gather_two_ranks(reduce_mode):
-    """Peer-memory collectives of the sharded engine against its NCCL path (same losses, same parameters);
-    the gradient reduce-scatter once through staging slots and once by pulling the peers' buffers."""
+@pytest.mark.parametrize("world", _rank_counts())
+@pytest.mark.parametrize("grad_acc", [1, 2])
+def test_engine_fused_gradient_scatter(world, grad_acc):
+    """Peer-memory collectives of the sharded engine (weight gradients scattered to their owners by the GEMM
+    epilogue, slot sums, copy-engine parameter gather) against its NCCL path: same losses, same parameters, and
+    bit-identical results when the peer-memory run is repeated."""
     worker = Path(__file__).with_name("engine_p2p_worker.py")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", "29654", str(worker)]
-    r = subprocess.run(cmd, env=dict(os.environ, LB_P2P_REDUCE=reduce_mode), capture_output=True, text=True,
+    r = subprocess.run(cmd, env=dict(os.environ, LB_TEST_GRAD_ACC=str(grad_acc)), capture_output=True, text=True,
                        timeout=600)
     assert r.returncode == 0 and "ENGINE_P2P_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
