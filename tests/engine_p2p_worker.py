@@ -46,6 +46,51 @@ def run(p2p: bool, rank: int, world: int, dev):
     return losses, sums
 
 
+class _Mlp(torch.nn.Module):
+    """Linear layers only, no clipping (the squared norm is summed with atomics): every kernel that touches the
+    weights is deterministic, so two runs of the peer-memory engine must leave bit-identical master weights, and
+    with two ranks (a + b == b + a) so must the NCCL path."""
+
+    def __init__(self, dim=512, hidden=1408, n=5):
+        super().__init__()
+        self.layers = torch.nn.ModuleList()
+        for _ in range(n):
+            blk = torch.nn.Module()
+            blk.up = torch.nn.Linear(dim, hidden, bias=False)
+            blk.down = torch.nn.Linear(hidden, dim, bias=False)
+            self.layers.append(blk)
+
+    def forward(self, x):
+        from lingua_b200.ops.fused import LinearFn
+
+        eng = self._engine
+        for i, blk in enumerate(self.layers):
+            (x,) = eng.boundary(f"layers.{i}", x)
+            x = x + LinearFn.apply(torch.relu(LinearFn.apply(x, blk.up.weight)), blk.down.weight)
+        return x.float().pow(2).mean()
+
+
+def run_mlp(p2p: bool, rank: int, world: int, dev):
+    from lingua_b200.parallel.engine import EngineOptim, ShardedEngine
+
+    torch.manual_seed(0)
+    model = _Mlp().to(dev)
+    plan = [(f"layers.{i}", False) for i in range(len(model.layers))]
+    eng = ShardedEngine(model, plan, process_group=None, optim=EngineOptim(clip=0.0), device=dev, p2p_gather=p2p)
+    model._engine = eng
+    eng.sync_master()
+    x = torch.randn(512, 512, generator=torch.Generator().manual_seed(7 + rank)).to(dev, torch.bfloat16).requires_grad_()
+    norms = []
+    for _ in range(4):
+        eng.zero_grad()
+        model(x).backward()
+        norms.append(eng.step(1e-2))
+    eng.wait_all_params()
+    torch.cuda.synchronize()
+    _lib.check_status()
+    return torch.stack(norms).cpu(), [g.master.clone().cpu() for g in eng.groups]
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
@@ -53,9 +98,10 @@ def main():
     dist.init_process_group("nccl", device_id=dev)
     l_p2p, s_p2p = run(True, rank, world, dev)
     l_again, s_again = run(True, rank, world, dev)
-    # the slots are summed in a fixed order: the peer-memory path repeats bit for bit as far as the reductions go
-    # (attention's dQ accumulation uses atomics, hence a tolerance far below the one against NCCL, not equality)
-    assert all(abs(a - b) <= 1e-3 * abs(b) for a, b in zip(l_again, l_p2p)), (l_again, l_p2p)
+    # attention's dQ accumulation and the embedding gradient use atomics, so whole-model runs agree closely but not
+    # bit for bit; the bitwise check of the reductions themselves is the linear-layers-only model below
+    assert all(abs(a - b) <= (2e-3 if i < 3 else 5e-2) * abs(b) for i, (a, b) in enumerate(zip(l_again, l_p2p))), \
+        (l_again, l_p2p)
     l_nccl, s_nccl = run(False, rank, world, dev)
     # the kernels accumulate some gradients with atomics, so two runs agree closely but not bit for bit
     # (differences grow with every optimiser step: tight at the start, loose at the end)
@@ -63,6 +109,18 @@ def main():
         (l_p2p, l_nccl)
     assert all(abs(a - b) <= 1e-2 * (abs(b) + 1.0) for a, b in zip(s_p2p, s_nccl)), (s_p2p, s_nccl)
     assert l_p2p[-1] < l_p2p[0]
+    n1, m1 = run_mlp(True, rank, world, dev)
+    n2, m2 = run_mlp(True, rank, world, dev)
+    assert torch.allclose(n1, n2, rtol=1e-5), (n1, n2)
+    bad = [i for i, (a, b) in enumerate(zip(m1, m2)) if not torch.equal(a, b)]
+    assert not bad, f"peer-memory run does not repeat: groups {bad}, max diff {max(float((m1[i] - m2[i]).abs().max()) for i in bad)}"
+    n3, m3 = run_mlp(False, rank, world, dev)
+    assert torch.allclose(n1, n3, rtol=1e-5), (n1, n3)
+    if world == 2:
+        bad = [i for i, (a, b) in enumerate(zip(m1, m3)) if not torch.equal(a, b)]
+        assert not bad, f"differs from the NCCL path: groups {bad}"
+    else:
+        assert all(torch.allclose(a, b, rtol=1e-3, atol=1e-5) for a, b in zip(m1, m3))
     dist.barrier()
     if rank == 0:
         print("ENGINE_P2P_OK", l_p2p)
