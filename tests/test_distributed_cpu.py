@@ -11,14 +11,14 @@ import pytest
 WORKER = str(Path(__file__).resolve().parent / "dist_worker.py")
 
 
-def _run(nproc, dp_shard, tp, steps=4, fail_rank=-1, timeout=300, port=29631):
+def _run(nproc, dp_shard, tp, steps=4, fail_rank=-1, timeout=300, port=29631, dp_replicate=1, clip=1.0, ckpt=""):
     env = dict(os.environ, OMP_NUM_THREADS="1", MASTER_ADDR="127.0.0.1")
+    tail = [str(dp_shard), str(tp), str(steps), str(fail_rank), str(dp_replicate), str(clip)] + ([ckpt] if ckpt else [])
     if nproc == 1:
-        cmd = [sys.executable, WORKER, str(dp_shard), str(tp), str(steps), str(fail_rank)]
+        cmd = [sys.executable, WORKER] + tail
     else:
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
-               "--master-addr", "127.0.0.1", "--master-port", str(port), WORKER, str(dp_shard), str(tp), str(steps),
-               str(fail_rank)]
+               "--master-addr", "127.0.0.1", "--master-port", str(port), WORKER] + tail
     return subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
 
 
@@ -51,3 +51,26 @@ def test_rank_failure_is_detected_not_hung():
     proc = _run(2, 2, 1, fail_rank=1, timeout=240, port=29634)
     assert proc.returncode != 0
     assert "injected failure" in (proc.stderr + proc.stdout)
+
+
+def test_hybrid_sharding_two_by_two_matches_single_process(single):
+    """dp_replicate 2 x dp_shard 2: shards inside a pair, averaged across the pairs (lingua/distributed.py:106-113)."""
+    four = _losses(_run(4, 2, 1, port=29635, dp_replicate=2))
+    for a, b in zip(single, four):
+        assert abs(a - b) < 2e-4 * max(1.0, abs(a)), (single, four)
+
+
+def test_tensor_parallel_gradient_norm_clips_like_single_process():
+    """A clip threshold far below the gradient norm: every step's update depends on the global norm, which under
+    tensor parallelism is the sum over the TP ranks' slices plus the replicated parameters counted once."""
+    one = _losses(_run(1, 1, 1, clip=0.05))
+    two = _losses(_run(2, 1, 2, port=29636, clip=0.05))
+    for a, b in zip(one, two):
+        assert abs(a - b) < 2e-4 * max(1.0, abs(a)), (one, two)
+
+
+@pytest.mark.parametrize("nproc,dp_shard,tp", [(2, 1, 2), (2, 2, 1), (4, 2, 2)])
+def test_checkpoint_round_trip_keeps_every_ranks_shard(tmp_path, nproc, dp_shard, tp):
+    proc = _run(nproc, dp_shard, tp, steps=2, port=29637, ckpt=str(tmp_path / "ckpt"))
+    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-3000:]
+    assert proc.stdout.count("CKPT_OK") == nproc
