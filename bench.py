@@ -145,6 +145,9 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="7b", choices=list(MODELS) + list(OTHER_MODELS))
     ap.add_argument("--ref-eager", action="store_true", help="reference arm without torch.compile")
+    ap.add_argument("--layers", type=int, default=0,
+                    help="override the model's depth (kernel profiling on a small case; the line is then marked "
+                         "'reduced_depth' and is not a benchmark value)")
     ap.add_argument("--float8", action="store_true",
                     help="ours only: row-wise e4m3 forward / input-gradient products in the blocks (reported as dtype fp8)")
     ap.add_argument("--sac", default="auto", choices=["auto", "on", "off"],
@@ -192,6 +195,8 @@ def main() -> None:
 
     other = OTHER_MODELS.get(a.model)
     mcfg = other[3] if other else MODELS[a.model]
+    if a.layers > 0:
+        mcfg = dict(mcfg, n_layers=a.layers)
     B = BATCH[a.model]
     fpt = flops_per_token(mcfg) if not other else 0.0  # filled in from the parameter count below
     if other and a.impl != "ours":
@@ -268,6 +273,8 @@ def main() -> None:
             if tr is None:
                 raise torch.OutOfMemoryError("the training step does not fit with or without activation recomputation")
             extra["selective_activation_checkpointing"] = sac
+            if a.layers > 0:
+                extra["reduced_depth"] = a.layers
             extra["collectives"] = ("none" if world == 1 else "nccl" if not tr.engine.p2p else
                                     "reduce-scatter: weight-gradient GEMM epilogue stores row blocks into the owners' "
                                     "slots over NVLink + one slot-sum kernel per group; all-gather: copy engines")
@@ -359,14 +366,21 @@ def main() -> None:
         "config": {"model": a.model if other else f"llama_{a.model}", "global_batch": B * world, "seq_len": SEQ,
                    "parallelism": f"fsdp{world}", "tokens_per_gpu_per_step": B * SEQ,
                    "l2": "working set (>= 15 GB of weights re-read every step) exceeds the 126 MB L2; no explicit flush",
-                   "optimizer": "AdamW fp32 states, clip 1.0, inside the timed region", **extra},
+                   "optimizer": "AdamW fp32 states, clip 1.0, inside the timed region",
+                   # everything that only one of the two arms has to say sits under "arm", so that both arms
+                   # print the same key set for the same benchmark
+                   "arm": extra},
         "wps_per_gpu": round(value / world, 1),
         "mfu_of_measured_sustained_peak": round(value / world * fpt / (peak_tf * 1e12), 4),
         "tflops_per_gpu": round(value / world * fpt / 1e12, 1),
         "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
         "clocks": clocks,
+        # step time x median SM clock: compares arms that settle at different clocks under the power cap
+        "ms_x_sm_mhz": round(ms * clocks["sm_mhz"], 0) if clocks.get("sm_mhz") else None,
         "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "ms_per_step": round(ms_e2e, 3),
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4},
+                "h2d_bytes_per_step": h2d,
+                # the loss (4 bytes) and, in this library's arm, the kernels' status word (4 bytes)
+                "d2h_bytes_per_step": 8 if a.impl == "ours" else 4},
         "gpu_launches": launches,
     }
     if rank == 0:
