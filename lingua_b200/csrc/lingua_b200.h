@@ -171,6 +171,30 @@ int lb_reduce_peers(const void* const* srcs, int n_src, float* out, long long n,
 int lb_reduce_norm(const void* slots, int n_slots, long long slot_stride, const void* resid, const void* w,
                    float eps, void* h_out, void* y_out, float* rstd_out, long long rows, int D, void* stream);
 
+// Decoding-step and gate kernels of the recurrent models (recurrent_step.cu). bf16 tensors unless noted.
+// conv1d_update: x [N, C] (row pitch ldx), state [N, C, W] updated in place (window shifted, x appended),
+//   w [C, W], out [N, C] (row pitch ldo) = (SiLU of) the weighted window. W in {2, 3, 4}.
+int lb_conv1d_update(const void* x, long long ldx, void* state, const void* w, void* out, long long ldo, int N, int C,
+                     int W, int act, void* stream);
+// conv_states: x [T, C] packed documents (row pitch ldx), document d covers rows [starts[d], ends[d]) (int64 on the
+//   device); out [n_docs, C, W] = the last W inputs of every document, zero where the document is shorter.
+int lb_conv_states(const void* x, long long ldx, const long long* starts, const long long* ends, void* out, int n_docs,
+                   int C, int W, void* stream);
+// ssm_state_update: state fp32 [n, H, P, N] in place: state = exp(dt A) state + dt x B^T; y [n, H, P] = state . C
+//   (+ D x). x [n, H*P] (pitch ldx), dt fp32 [n, H], A fp32 [H], B / C [n, G, N] (pitches ldb / ldc), D fp32 [H] or
+//   [H, P] (d_has_p) or NULL. N % 4 == 0.
+int lb_ssm_state_update(float* state, const void* x, long long ldx, const float* dt, const float* A, const void* B,
+                        long long ldb, const void* Cm, long long ldc, const float* D, int d_has_p, void* y, int nseq,
+                        int H, int P, int N, int G, void* stream);
+// rnn_step: state fp32 [n] = a * state + b; out = bf16(state).
+int lb_rnn_step(const void* a, const void* b, float* state, void* out, long long n, void* stream);
+// RG-LRU gates on contiguous [rows, C] tensors (C % 8 == 0), sp = softplus(lambda) per channel (fp32 [C]):
+//   a = exp(-8 sigmoid(ga) sp), b = sqrt(1 - a^2) sigmoid(gx) x. The backward also accumulates d sp into dsp (fp32 [C]).
+int lb_rglru_gates_fwd(const void* gx, const void* ga, const void* x, const float* sp, void* a_out, void* b_out,
+                       long long rows, int C, void* stream);
+int lb_rglru_gates_bwd(const void* gx, const void* ga, const void* x, const float* sp, const void* da, const void* db,
+                       void* dgx, void* dga, void* dx, float* dsp, long long rows, int C, void* stream);
+
 // Number of kernels launched by this library in this process so far.
 long long lb_launch_count(void);
 void lb_launch_count_add(long long n);

@@ -22,6 +22,7 @@ import torch.nn.functional as TF
 
 from ..ops import fused
 from ..ops.sequence import (causal_conv1d, conv1d_update, conv_states_from_packed, last_states_from_packed,
+                            rglru_gates, rnn_step,
                             linear_scan)
 from .transformer import (FeedForward, InitStdFactor, Linear, RMSNorm, TiedLinear, _is_native, _trunc,
                           cross_entropy)
@@ -81,9 +82,7 @@ class _Recurrent(nn.Module):
     def _scan(self, a, b, doc_start, impl):
         cache = self.cache
         if impl == "sequential":
-            h = a[0].float() * cache.state_cache + b[0].float()
-            cache.state_cache.copy_(h)
-            return h.to(a.dtype).unsqueeze(0)
+            return rnn_step(a[0], b[0], cache.state_cache).unsqueeze(0)
         h = linear_scan(a, b, doc_start)
         if cache is not None:
             cache.state_cache.copy_(last_states_from_packed(h[0], cache.lengths).float())
@@ -234,23 +233,6 @@ class BaseHawkArgs:
     gate_structure: str = "dense"
 
 
-_MAX_SQRT_GRADIENT = 1000.0
-
-
-class SqrtBoundDerivative(torch.autograd.Function):
-    """sqrt whose gradient is clipped at ``_MAX_SQRT_GRADIENT`` (1 - a^2 can reach 0)."""
-
-    @staticmethod
-    def forward(ctx, x):
-        ctx.save_for_backward(x)
-        return torch.sqrt(x)
-
-    @staticmethod
-    def backward(ctx, g):
-        (x,) = ctx.saved_tensors
-        return g / torch.sqrt(torch.clip(4.0 * x, min=1 / (_MAX_SQRT_GRADIENT ** 2)))
-
-
 class BlockDiagonalLinear(nn.Module):
     """``n_blocks`` independent [w, w] maps applied to consecutive channel groups."""
 
@@ -287,13 +269,10 @@ class RGLRU(_Recurrent):
     def forward(self, x, doc_start=None, impl="parallel"):
         B, S, _ = x.shape
         x = self._conv(x, doc_start, impl)
-        gate_x = torch.sigmoid(self.input_gate(x).float())
-        gate_a = torch.sigmoid(self.a_gate(x).float())
-        a_param = TF.softplus(self.a.float()).repeat(self.n_heads).view(1, 1, self.dim)
-        log_a = -self.c * gate_a * a_param
-        a = log_a.exp()
-        mult = SqrtBoundDerivative.apply(1.0 - (2.0 * log_a).exp())
-        return self._scan(a.to(x.dtype), (mult * gate_x * x.float()).to(x.dtype), doc_start, impl)
+        # both gates, the decay and the input scaling in one kernel each way (ops.sequence.rglru_gates)
+        sp = TF.softplus(self.a.float()).repeat(self.n_heads)
+        a, b = rglru_gates(self.input_gate(x), self.a_gate(x), x, sp)
+        return self._scan(a, b, doc_start, impl)
 
     def reset_parameters(self, init_std, factor):
         in_std = (init_std or (self.dim ** (-0.5))) / factor

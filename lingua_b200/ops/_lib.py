@@ -119,6 +119,12 @@ def _declare(lib) -> None:
         "lb_scan_fwd": [vp, vp, ip, fp, vp, fp, fp, i, i, i, vp],
         "lb_scan_bwd": [vp, vp, vp, ip, fp, vp, vp, fp, i, i, i, vp],
         "lb_decode_attn": [vp, vp, vp, vp, vp, ip, ip, vp, i, i, i, i, ll, ll, f, vp],
+        "lb_conv1d_update": [vp, ll, vp, vp, vp, ll, i, i, i, i, vp],
+        "lb_conv_states": [vp, ll, llp, llp, vp, i, i, i, vp],
+        "lb_ssm_state_update": [fp, vp, ll, fp, fp, vp, ll, vp, ll, fp, i, vp, i, i, i, i, i, vp],
+        "lb_rnn_step": [vp, vp, fp, vp, ll, vp],
+        "lb_rglru_gates_fwd": [vp, vp, vp, fp, vp, vp, ll, i, vp],
+        "lb_rglru_gates_bwd": [vp, vp, vp, fp, vp, vp, vp, vp, vp, fp, ll, i, vp],
     }
     for name, args in sigs.items():
         if hasattr(lib, name):

@@ -85,17 +85,30 @@ def causal_conv1d(x: torch.Tensor, w: torch.Tensor, doc_start: Optional[torch.Te
     return conv1d_ref(x, w, doc_start, act)
 
 
-def conv1d_update(x_t: torch.Tensor, conv_state: torch.Tensor, w: torch.Tensor, act: bool = True) -> torch.Tensor:
-    """One decoding step. x_t: [N, C]; conv_state: [N, C, W] holds the last W inputs (updated in place)."""
+def conv1d_update_ref(x_t, conv_state, w, act=True):
     conv_state.copy_(torch.roll(conv_state, shifts=-1, dims=-1))
     conv_state[:, :, -1] = x_t
     out = (conv_state.float() * w.float().unsqueeze(0)).sum(-1)
     return (TF.silu(out) if act else out).to(x_t.dtype)
 
 
-def conv_states_from_packed(x: torch.Tensor, lengths: torch.Tensor, width: int) -> torch.Tensor:
-    """Last ``width`` inputs of every document of a packed sequence x [T, C] -> [n_docs, C, width]
-    (zero-padded on the left for documents shorter than the window)."""
+def conv1d_update(x_t: torch.Tensor, conv_state: torch.Tensor, w: torch.Tensor, act: bool = True) -> torch.Tensor:
+    """One decoding step. x_t: [N, C] (rows may be strided); conv_state: [N, C, W] holds the last W inputs
+    (updated in place); returns [N, C]."""
+    N, C = x_t.shape
+    W = w.shape[1]
+    if (x_t.is_cuda and x_t.dtype == torch.bfloat16 and conv_state.dtype == torch.bfloat16 and x_t.stride(1) == 1
+            and conv_state.is_contiguous() and W in (2, 3, 4)):
+        out = torch.empty(N, C, dtype=x_t.dtype, device=x_t.device)
+        wd = w.detach().to(torch.bfloat16).contiguous()
+        rc = _lib.load().lb_conv1d_update(x_t.data_ptr(), x_t.stride(0), conv_state.data_ptr(), wd.data_ptr(),
+                                          out.data_ptr(), C, N, C, W, int(act), _lib.stream_ptr())
+        _lib.check(rc, "lb_conv1d_update")
+        return out
+    return conv1d_update_ref(x_t, conv_state, w, act)
+
+
+def conv_states_ref(x, lengths, width):
     ends = torch.cumsum(lengths, 0)
     starts = ends - lengths
     idx = ends.view(-1, 1) - width + torch.arange(width, device=x.device).view(1, -1)  # [n, width]
@@ -103,6 +116,98 @@ def conv_states_from_packed(x: torch.Tensor, lengths: torch.Tensor, width: int) 
     g = x[idx.clamp(min=0)]  # [n, width, C]
     g = torch.where(valid.unsqueeze(-1), g, torch.zeros_like(g))
     return g.permute(0, 2, 1).contiguous()
+
+
+def conv_states_from_packed(x: torch.Tensor, lengths: torch.Tensor, width: int) -> torch.Tensor:
+    """Last ``width`` inputs of every document of a packed sequence x [T, C] -> [n_docs, C, width]
+    (zero-padded on the left for documents shorter than the window)."""
+    if x.is_cuda and x.dtype == torch.bfloat16 and x.stride(1) == 1:
+        ends = torch.cumsum(lengths.to(torch.int64), 0).contiguous()
+        starts = (ends - lengths.to(torch.int64)).contiguous()
+        n, C = lengths.numel(), x.shape[1]
+        out = torch.empty(n, C, width, dtype=x.dtype, device=x.device)
+        rc = _lib.load().lb_conv_states(x.data_ptr(), x.stride(0), starts.data_ptr(), ends.data_ptr(), out.data_ptr(),
+                                        n, C, width, _lib.stream_ptr())
+        _lib.check(rc, "lb_conv_states")
+        return out
+    return conv_states_ref(x, lengths, width)
+
+
+def rnn_step(a: torch.Tensor, b: torch.Tensor, state: torch.Tensor) -> torch.Tensor:
+    """One step of h = a * h + b on the cached fp32 ``state`` [N, C] (updated in place); a, b: [N, C]."""
+    if a.is_cuda and a.dtype == torch.bfloat16 and state.dtype == torch.float32 and state.is_contiguous():
+        a, b = a.contiguous(), b.contiguous()
+        out = torch.empty_like(a)
+        rc = _lib.load().lb_rnn_step(a.data_ptr(), b.data_ptr(), state.data_ptr(), out.data_ptr(), a.numel(),
+                                     _lib.stream_ptr())
+        _lib.check(rc, "lb_rnn_step")
+        return out
+    h = a.float() * state + b.float()
+    state.copy_(h)
+    return h.to(a.dtype)
+
+
+# ----------------------------------------------------------------------------- RG-LRU gates
+_MAX_SQRT_GRADIENT = 1000.0
+
+
+def rglru_gates_ref(gx, ga, x, sp, c: float = 8.0):
+    """(a, b) of the RG-LRU recurrence from the gate pre-activations; differentiable PyTorch version."""
+    gate_x = torch.sigmoid(gx.float())
+    gate_a = torch.sigmoid(ga.float())
+    log_a = -c * gate_a * sp.float().view(*([1] * (gx.dim() - 1)), -1)
+    a = log_a.exp()
+    mult = _SqrtBound.apply(1.0 - (2.0 * log_a).exp())
+    return a.to(x.dtype), (mult * gate_x * x.float()).to(x.dtype)
+
+
+class _SqrtBound(torch.autograd.Function):
+    """sqrt whose gradient is clipped at 1000 (1 - a^2 can reach 0)."""
+
+    @staticmethod
+    def forward(ctx, x):
+        ctx.save_for_backward(x)
+        return torch.sqrt(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        (x,) = ctx.saved_tensors
+        return g / torch.sqrt(torch.clip(4.0 * x, min=1 / (_MAX_SQRT_GRADIENT ** 2)))
+
+
+class _RglruGates(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gx, ga, x, sp):
+        gx, ga, x = gx.contiguous(), ga.contiguous(), x.contiguous()
+        sp = sp.float().contiguous()
+        C = x.shape[-1]
+        a, b = torch.empty_like(x), torch.empty_like(x)
+        rc = _lib.load().lb_rglru_gates_fwd(gx.data_ptr(), ga.data_ptr(), x.data_ptr(), sp.data_ptr(), a.data_ptr(),
+                                            b.data_ptr(), x.numel() // C, C, _lib.stream_ptr())
+        _lib.check(rc, "lb_rglru_gates_fwd")
+        ctx.save_for_backward(gx, ga, x, sp)
+        return a, b
+
+    @staticmethod
+    def backward(ctx, da, db):
+        gx, ga, x, sp = ctx.saved_tensors
+        C = x.shape[-1]
+        da, db = da.contiguous(), db.contiguous()
+        dgx, dga, dx = torch.empty_like(x), torch.empty_like(x), torch.empty_like(x)
+        dsp = torch.zeros(C, dtype=torch.float32, device=x.device)
+        rc = _lib.load().lb_rglru_gates_bwd(gx.data_ptr(), ga.data_ptr(), x.data_ptr(), sp.data_ptr(), da.data_ptr(),
+                                            db.data_ptr(), dgx.data_ptr(), dga.data_ptr(), dx.data_ptr(),
+                                            dsp.data_ptr(), x.numel() // C, C, _lib.stream_ptr())
+        _lib.check(rc, "lb_rglru_gates_bwd")
+        return dgx, dga, dx, dsp
+
+
+def rglru_gates(gx: torch.Tensor, ga: torch.Tensor, x: torch.Tensor, sp: torch.Tensor):
+    """a = exp(-8 sigmoid(ga) sp), b = sqrt(1 - a^2) sigmoid(gx) x for [..., C] gate pre-activations ``gx``, ``ga``,
+    the input ``x`` and ``sp`` = softplus(lambda) per channel ([C], fp32). One kernel each way on the GPU."""
+    if x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0:
+        return _RglruGates.apply(gx, ga, x, sp)
+    return rglru_gates_ref(gx, ga, x, sp)
 
 
 # ----------------------------------------------------------------------------- linear recurrence

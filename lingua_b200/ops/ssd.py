@@ -250,6 +250,27 @@ def ssd_chunked(x, dt, A, B, C, D=None, chunk: int = 256, doc_start: Optional[to
 def selective_state_update(state, x, dt, A, B, C, D=None):
     """One decode step. state [n, h, p, N] (updated in place, fp32); x [n,h,p]; dt [n,h]; B/C [n,g,N]."""
     nseq, h, p = x.shape
+    N = state.shape[-1]
+    if (x.is_cuda and x.dtype == torch.bfloat16 and state.dtype == torch.float32 and state.is_contiguous()
+            and N % 4 == 0 and x.stride(2) == 1 and x.stride(1) == p and B.stride(2) == 1 and B.stride(1) == N
+            and C.stride(2) == 1 and C.stride(1) == N and B.dtype == torch.bfloat16 and C.dtype == torch.bfloat16
+            and B.stride(0) % 4 == 0 and C.stride(0) % 4 == 0 and B.data_ptr() % 8 == 0 and C.data_ptr() % 8 == 0):
+        from . import _lib
+
+        y = torch.empty(nseq, h, p, dtype=x.dtype, device=x.device)
+        dtf, Af = dt.float().contiguous(), A.float().contiguous()
+        Df = D.float().contiguous() if D is not None else None
+        rc = _lib.load().lb_ssm_state_update(state.data_ptr(), x.data_ptr(), x.stride(0), dtf.data_ptr(), Af.data_ptr(),
+                                             B.data_ptr(), B.stride(0), C.data_ptr(), C.stride(0),
+                                             None if Df is None else Df.data_ptr(), int(Df is not None and Df.dim() == 2),
+                                             y.data_ptr(), nseq, h, p, N, B.shape[1], _lib.stream_ptr())
+        _lib.check(rc, "lb_ssm_state_update")
+        return y
+    return selective_state_update_ref(state, x, dt, A, B, C, D)
+
+
+def selective_state_update_ref(state, x, dt, A, B, C, D=None):
+    nseq, h, p = x.shape
     rep = h // B.shape[1]
     Bh = B.float().repeat_interleave(rep, dim=1)
     Ch = C.float().repeat_interleave(rep, dim=1)
