@@ -26,6 +26,7 @@ from typing import Any, Dict, List, Optional, Tuple
 import torch
 import torch.distributed as dist
 import torch.distributed.checkpoint as dcp
+from torch.distributed.checkpoint.api import CheckpointException  # derives from BaseException
 from torch.distributed.checkpoint.format_utils import dcp_to_torch_save
 
 from .config import dataclass_to_dict
@@ -313,17 +314,31 @@ class CheckpointManager:
 
     @torch.no_grad()
     def load(self, engine, train_state, mesh=None, path: Optional[Path] = None) -> None:
+        """Resume from ``path`` or, by default, from the newest step folder that loads. A folder whose shards are
+        damaged (a job killed in the middle of a save, a truncated ``.distcp`` file) is reported and skipped, and the
+        next older one is tried, so a bad last save costs the steps since the previous one instead of the run."""
         dp_rank, _ = self._get_dp_tp_mesh(mesh)
-        path = path or self.get_last_step_path(dp_rank=dp_rank)
-        if path is None:
+        if path is not None:
+            candidates = [Path(path)]
+        else:
+            candidates = [p for p in reversed(self.existing_saves) if (p / TRAIN_STATE_NAME.format(dp_rank)).is_file()]
+        for i, cand in enumerate(candidates):
+            try:
+                with open(cand / TRAIN_STATE_NAME.format(dp_rank), "r") as f:
+                    state = json.load(f)
+                sd = engine_state_dict(engine)
+                dcp.load(sd, checkpoint_id=cand)
+            except (Exception, CheckpointException) as e:  # any reader error means the folder cannot be trusted
+                if path is not None or i == len(candidates) - 1:
+                    raise
+                logger.error(f"Checkpoint {cand} cannot be loaded ({type(e).__name__}: {str(e)[:200]}); "
+                             f"falling back to {candidates[i + 1]}")
+                continue
+            train_state.load_state_dict(state)
+            logger.info(f"Train state reloaded; loading from: {cand}")
+            load_engine_state_dict(engine, sd, load_optim=True)
+            logger.info("Model and optim reloaded")
             return
-        with open(Path(path) / TRAIN_STATE_NAME.format(dp_rank), "r") as f:
-            train_state.load_state_dict(json.load(f))
-        logger.info(f"Train state reloaded; loading from: {path}")
-        sd = engine_state_dict(engine)
-        dcp.load(sd, checkpoint_id=path)
-        load_engine_state_dict(engine, sd, load_optim=True)
-        logger.info("Model and optim reloaded")
 
     @classmethod
     def instantiate_and_make_dir(cls, args: CheckpointArgs):

@@ -115,3 +115,74 @@ def test_grad_accumulation_and_probe(tmp_path):
     assert "layers.0.attention.wq::in" in keys and "layers.0.attention.wq::out.g" in keys
     assert "layers.0.attention_norm::resid" in keys
     assert any(k.endswith("::w.g") for k in keys)
+
+
+def test_preemption_signal_saves_and_resume_continues_bitwise(tmp_path, monkeypatch):
+    """SIGUSR2 (what the scheduler sends before it preempts a job, lingua/stool.py:57) in the middle of a run: the
+    loop finishes the step, writes a checkpoint and exits; the same command then resumes, and the losses of the two
+    halves are exactly those of an uninterrupted run (apps/main/train.py:203-209,582-592)."""
+    import os
+    import signal
+
+    from lingua_b200 import train_loop
+
+    train(dataclass_from_dict(TrainArgs, _cfg(tmp_path / "whole", steps=8)))
+    whole = _losses(tmp_path / "whole")
+
+    real_log = train_loop.MetricLogger.log
+    seen = {"n": 0}
+
+    def log_and_signal(self, metrics):
+        real_log(self, metrics)
+        seen["n"] += 1
+        if seen["n"] == 3:
+            os.kill(os.getpid(), signal.SIGUSR2)
+
+    monkeypatch.setattr(train_loop.MetricLogger, "log", log_and_signal)
+    monkeypatch.delenv("SLURM_JOB_ID", raising=False)
+    train_loop.preemption_flag["flag"] = False
+    d = tmp_path / "cut"
+    with pytest.raises(SystemExit) as ex:
+        train(dataclass_from_dict(TrainArgs, _cfg(d, steps=8)))
+    assert ex.value.code == 0
+    first = _losses(d)
+    assert first == whole[:3]
+    assert (d / "checkpoints" / "0000000003" / "train_state_00000.json").is_file()  # not a regular dump step
+    monkeypatch.setattr(train_loop.MetricLogger, "log", real_log)
+    train_loop.preemption_flag["flag"] = False
+    (d / "metrics.jsonl").unlink()
+    train(dataclass_from_dict(TrainArgs, _cfg(d, steps=8)))
+    assert _losses(d) == whole[3:]
+
+
+def test_damaged_last_checkpoint_falls_back_to_the_previous_one(tmp_path):
+    d = tmp_path / "run"
+    train(dataclass_from_dict(TrainArgs, _cfg(d, steps=10)))
+    full = _losses(d)
+    shard = next((d / "checkpoints" / "0000000010").glob("*.distcp"))
+    data = shard.read_bytes()
+    shard.write_bytes(data[: len(data) // 3])  # a save that was cut short
+    (d / "metrics.jsonl").unlink()
+    train(dataclass_from_dict(TrainArgs, _cfg(d, steps=10)))
+    assert _losses(d) == full[5:]  # resumed from step 5, not from the damaged step 10
+    # an explicitly requested folder that is damaged is an error, not a silent fallback
+    from lingua_b200.checkpoint import CheckpointArgs, CheckpointManager
+
+    mgr = CheckpointManager(CheckpointArgs(path=str(d / "checkpoints")))
+    shard2 = next((d / "checkpoints" / "0000000005").glob("*.distcp"))
+    shard2.write_bytes(shard2.read_bytes()[:100])
+    with pytest.raises(BaseException):
+        mgr.load(_FakeEngineNeverUsed(), None, path=d / "checkpoints" / "0000000005")
+
+
+class _FakeEngineNeverUsed:
+    """Loading must fail while reading the folder, before anything is written into an engine."""
+
+    world = 1
+    rank = 0
+    groups = []
+    step_count = 0
+    tp_pg = None
+
+    class optim:  # noqa: N801
+        beta1 = beta2 = eps = weight_decay = 0.0
