@@ -150,6 +150,9 @@ def main() -> None:
                          "'reduced_depth' and is not a benchmark value)")
     ap.add_argument("--float8", action="store_true",
                     help="ours only: row-wise e4m3 forward / input-gradient products in the blocks (reported as dtype fp8)")
+    ap.add_argument("--fp8-steps", type=int, default=-1,
+                    help="timed steps of the additional float8 measurement reported under 'fp8' (Llama arms of this "
+                         "library only; -1 = min(steps, 10), 0 = skip)")
     ap.add_argument("--sac", default="auto", choices=["auto", "on", "off"],
                     help="recompute cheap activations in backward (auto: only where memory needs it)")
     a = ap.parse_args()
@@ -341,6 +344,43 @@ def main() -> None:
         clocks = sampler.stop() if rank == 0 else {}
         if counter:
             launches = c1 - c0
+        # second half of the headline metric: the same step with float8 (e4m3, row-wise scales) forward and
+        # input-gradient products, measured in the same process right after the bf16 run
+        fp8_info, peak_bytes = None, None
+        n8 = min(a.steps, 10) if a.fp8_steps < 0 else a.fp8_steps
+        if a.impl == "ours" and not other and not a.float8 and n8 > 0 and a.layers == 0:
+            import gc
+
+            peak_bytes = torch.cuda.max_memory_allocated()
+            sac_used, p2p_used = extra.get("selective_activation_checkpointing", False), tr.engine.p2p
+            tr = None
+            gc.collect()
+            torch.cuda.empty_cache()
+            why = ""
+            try:
+                tr = Trainer(LMTransformerArgs(**mcfg),
+                             DistributedArgs(dp_shard=world, fsdp_type="full_shard",
+                                             selective_activation_checkpointing=sac_used, p2p_param_gather=p2p_used,
+                                             float8_recipe="rowwise"),
+                             OptimArgs(lr=1e-3, warmup=2000, clip=1.0), total_steps=100000, device=dev)
+                dev_step(0)
+                torch.cuda.synchronize()
+            except Exception as e:  # the bf16 line above must not depend on this extra measurement
+                why = f"{type(e).__name__}: {str(e)[:160]}"
+            ok8 = torch.tensor([0 if why else 1], device=dev)
+            if world > 1:  # every rank measures, or none does
+                dist.all_reduce(ok8, op=dist.ReduceOp.MIN)
+            if int(ok8.item()):
+                for i in range(max(3, min(a.warmup, 5))):
+                    dev_step(i)
+                ms8 = timed(torch, dist, dev_step, n8, world)
+                ms8_e2e = timed(torch, dist, e2e_step, n8, world)
+                fp8_info = {"value": round(B * SEQ * world / ms8 * 1e3, 1), "unit": "tokens/s", "steps": n8,
+                            "ms_per_step": round(ms8, 3), "e2e_value": round(B * SEQ * world / ms8_e2e * 1e3, 1),
+                            "dtype": "fp8 (e4m3 row-wise fwd / dgrad in the blocks, bf16 wgrad and head)",
+                            "speedup_over_bf16": round(ms / ms8, 4)}
+            else:
+                fp8_info = {"unavailable": why or "another rank could not build the float8 model"}
     except torch.OutOfMemoryError as e:
         if rank == 0:
             print(json.dumps({**base, "unavailable": f"out of memory: {str(e)[:200]}"}))
@@ -373,7 +413,7 @@ def main() -> None:
         "wps_per_gpu": round(value / world, 1),
         "mfu_of_measured_sustained_peak": round(value / world * fpt / (peak_tf * 1e12), 4),
         "tflops_per_gpu": round(value / world * fpt / 1e12, 1),
-        "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
+        "peak_mem_gb": round((peak_bytes or torch.cuda.max_memory_allocated()) / 2 ** 30, 1),
         "clocks": clocks,
         # step time x median SM clock: compares arms that settle at different clocks under the power cap
         "ms_x_sm_mhz": round(ms * clocks["sm_mhz"], 0) if clocks.get("sm_mhz") else None,
@@ -383,6 +423,8 @@ def main() -> None:
                 "d2h_bytes_per_step": 8 if a.impl == "ours" else 4},
         "gpu_launches": launches,
     }
+    if fp8_info is not None:
+        out["fp8"] = fp8_info
     if rank == 0:
         print(json.dumps(out))
     if dist.is_initialized():

@@ -27,14 +27,18 @@
 namespace lb {
 
 constexpr int G2_THREADS = 192;
+constexpr int G2_THREADS_GATHER = 224;    // + the warp that pulls remote weight rows (gather mode)
 constexpr int G2_BM = 256, G2_BN = 256;   // per cluster
 constexpr int G2_ROWS = 128;              // A rows and B rows loaded by one CTA
 constexpr int G2_BK = 64;                 // bf16 elements per stage (128 bytes)
 constexpr int G2_A_BYTES = G2_ROWS * 128;
 constexpr int G2_STAGE_BYTES = 2 * G2_A_BYTES;
 constexpr int G2_STAGES = 6;
+constexpr int G2_STAGES_GATHER = 5;       // gather mode trades one stage for the two copy buffers
 constexpr int G2_PIECE = G2_ROWS * 128;   // one epilogue piece: 128 rows x 128 bytes
+constexpr int G2_COPY = 16384;            // bytes per pulled piece of a remote weight block
 constexpr int G2_SMEM = G2_STAGES * G2_STAGE_BYTES + 2 * G2_PIECE + 1024 + 256;
+static_assert(G2_STAGES_GATHER * G2_STAGE_BYTES + 2 * G2_COPY <= G2_STAGES * G2_STAGE_BYTES, "gather buffers fit");
 
 struct OwnerMaps {
   CUtensorMap m[LB_MAX_PEERS];
@@ -53,10 +57,38 @@ struct Gemm2Params {
   const int2* blocks; // scatter: (owner, destination row) per 128-row block of M
   void* C;
   uint32_t* status;
+  // gather mode (lb_gemm_gather): B is a weight matrix whose 128-row blocks are owned by the ranks of a group; the
+  // blocks of other ranks are pulled from their copy of the matrix into this one while the product runs
+  // float8 operands (lb_gemm_fp8 on SM pairs): result scaled by row_scale[m] * col_scale[n] instead of alpha
+  const float* row_scale;
+  const float* col_scale;
+  uint32_t idesc_f8;                   // instruction descriptor with the two operand formats (e4m3 / e5m2)
+  int raster_n;                        // walk column tiles in groups instead of row tiles
+  const int* n_order;                  // column tile visited at each position of the walk (own rows first)
+  const int2* g_blocks;                // remote blocks in the order they are pulled: (block, owner)
+  int g_n_remote;
+  uint32_t g_ppb;                      // pieces per block
+  const uint8_t* peer_b[LB_MAX_PEERS]; // every rank's copy of B
+  uint8_t* local_b;
+  uint32_t* flags;                     // [blocks of N] pieces landed, then the piece counter
+  int n_blocks;
 };
 
 // tile index inside one batch -> (row tile, column tile)
 __device__ __forceinline__ void g2_tile_coords(int t, const Gemm2Params& p, int& mt, int& nt) {
+  if (p.raster_n) {
+    // groups of group_m column tiles, all row tiles of a group before the next group: the weight rows are needed
+    // in the order of p.n_order, which leaves the remote ones time to arrive
+    const int per_group = p.group_m * p.tiles_m;
+    const int grp = t / per_group;
+    const int first = grp * p.group_m;
+    const int gsz = min(p.group_m, p.tiles_n - first);
+    const int r = t - grp * per_group;
+    mt = r / gsz;
+    nt = first + (r - mt * gsz);
+    if (p.n_order) nt = p.n_order[nt];
+    return;
+  }
   const int per_group = p.group_m * p.tiles_n;
   const int grp = t / per_group;
   const int first = grp * p.group_m;
@@ -117,14 +149,25 @@ __device__ __forceinline__ void umma2_f16(uint32_t tmem_d, uint64_t adesc, uint6
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+__device__ __forceinline__ void umma2_f8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
+      "}\n"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // arrive on one mbarrier (cluster address, either CTA) when all MMAs issued so far have completed
 __device__ __forceinline__ void umma2_commit(uint32_t bar_cluster) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster)
                : "memory");
 }
 
-template <int AMAJ, int BMAJ, typename OutT>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
+template <int AMAJ, int BMAJ, typename OutT, bool GATHER = false, bool F8 = false>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GATHER ? G2_THREADS_GATHER : G2_THREADS, 1)
 gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
              const __grid_constant__ CUtensorMap tma_c, const __grid_constant__ OwnerMaps owners,
              const Gemm2Params p) {
@@ -132,13 +175,16 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
   __shared__ int abort_flag;
   __shared__ uint32_t tmem_base_slot;
 
+  constexpr int STAGES = GATHER ? G2_STAGES_GATHER : G2_STAGES;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t copy_base = smem_base + STAGES * G2_STAGE_BYTES;  // gather mode only: two copy buffers
   const uint32_t aux_base = smem_base + G2_STAGES * G2_STAGE_BYTES;
   const uint32_t bar_base = aux_base + 2 * G2_PIECE;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (G2_STAGES + s); };
   auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * G2_STAGES + a); };
   auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * G2_STAGES + 2 + a); };
+  auto copy_bar = [&](int b) { return bar_base + 8u * (2 * G2_STAGES + 4 + b); };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -154,6 +200,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar(a), 1);
       mbar_init(tempty_bar(a), 8);  // 4 epilogue warps x 2 CTAs (used in the leader only)
+      mbar_init(copy_bar(a), 1);
     }
     fence_mbar_init();
     tma_prefetch_desc(&tma_a);
@@ -169,7 +216,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
 
-  const int num_kb = (p.K + G2_BK - 1) / G2_BK;
+  constexpr int BK_ELEMS = F8 ? 128 : G2_BK;  // one 128-byte swizzle row along K per stage
+  const int num_kb = (p.K + BK_ELEMS - 1) / BK_ELEMS;
   const int tiles_per_batch = p.tiles_m * p.tiles_n;
   const int num_tiles = tiles_per_batch * p.nb0 * p.nb1;
 
@@ -186,16 +234,26 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
         const int m0 = mt * G2_BM + rank * G2_ROWS;
         const int n0 = nt * G2_BN + rank * G2_ROWS;
         const int b0 = batch % p.nb0, b1 = batch / p.nb0;
+        if (GATHER && p.g_n_remote > 0) {
+          // this CTA's half of the B tile is one 128-row block of the weight: if another rank owns it, its pieces
+          // must have landed in the local copy (written by bulk copies of any CTA's gather warp)
+          const int blk = n0 / G2_ROWS;
+          if (blk < p.n_blocks) {
+            ok = flag_wait_ge(p.flags + blk, p.g_ppb, &abort_flag, p.status, 0x35);
+            if (!ok) break;
+            fence_proxy_async_all();
+          }
+        }
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % G2_STAGES;
-          const uint32_t ph = (it / G2_STAGES) & 1u;
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
           ok = mbar_wait(empty_bar(s), ph ^ 1u, &abort_flag, p.status, 0x31);
           if (!ok) break;
           if (leader) mbar_arrive_expect_tx(full_bar(s), 2 * G2_STAGE_BYTES);
           const uint32_t lead_full = mapa(full_bar(s), 0);
           const uint32_t sa = smem_base + s * G2_STAGE_BYTES;
           const uint32_t sb = sa + G2_A_BYTES;
-          const int k0 = kb * G2_BK;
+          const int k0 = kb * BK_ELEMS;
           if (AMAJ == 0) {
             tma_load_4d_pair(sa, &tma_a, lead_full, k0, m0, b0, b1);
           } else {
@@ -230,8 +288,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * G2_BN;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % G2_STAGES;
-          const uint32_t ph = (it / G2_STAGES) & 1u;
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
           ok = mbar_wait(full_bar(s), ph, &abort_flag, p.status, 0x33);
           if (!ok) break;
           tc_fence_after();
@@ -241,7 +299,10 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
           for (int k = 0; k < G2_BK / 16; ++k) {
             const uint64_t ad = make_smem_desc(sa + k * A_KSTEP, AMAJ ? LBO_MN : 16u, SBO);
             const uint64_t bd = make_smem_desc(sb + k * B_KSTEP, BMAJ ? LBO_MN : 16u, SBO);
-            umma2_f16(tmem_d, ad, bd, idesc, (kb | k) != 0);
+            if (F8)
+              umma2_f8(tmem_d, ad, bd, p.idesc_f8, (kb | k) != 0);
+            else
+              umma2_f16(tmem_d, ad, bd, idesc, (kb | k) != 0);
           }
           umma2_commit(mapa(empty_bar(s), 0));
           umma2_commit(mapa(empty_bar(s), 1));
@@ -251,7 +312,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
         umma2_commit(mapa(tfull_bar(acc), 1));
       }
     }
-  } else {
+  } else if (warp < 6) {
     // -------------------------------------------------- epilogue (warps 2..5, both CTAs)
     const int quarter = warp & 3;
     const int trow = quarter * 32 + lane;
@@ -271,6 +332,12 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
       if (!mbar_wait(tfull_bar(acc), acc_ph, &abort_flag, p.status, 0x34)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * G2_BN + (static_cast<uint32_t>(quarter * 32) << 16);
+      // scale of this thread's row: alpha, or the row's quantisation scale for float8 operands
+      float rs = p.alpha;
+      if (F8) rs = (m0 + trow < p.M && p.row_scale) ? __ldg(p.row_scale + m0 + trow) : 1.f;
+      auto cscale = [&](int col) -> float {
+        return (F8 && p.col_scale && col < p.N) ? __ldg(p.col_scale + col) : 1.f;
+      };
       if (p.epi_tma) {
         if (m0 < p.M) {
           const CUtensorMap* cmap = &tma_c;
@@ -296,10 +363,11 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
 #pragma unroll
               for (int g = 0; g < 8; ++g) {
                 const uint32_t dst = rowbase + ((static_cast<uint32_t>(g) ^ sw) << 4);
-                const uint32_t v0 = __float_as_uint(__uint_as_float(r[g * 4 + 0]) * p.alpha);
-                const uint32_t v1 = __float_as_uint(__uint_as_float(r[g * 4 + 1]) * p.alpha);
-                const uint32_t v2 = __float_as_uint(__uint_as_float(r[g * 4 + 2]) * p.alpha);
-                const uint32_t v3 = __float_as_uint(__uint_as_float(r[g * 4 + 3]) * p.alpha);
+                const int cc = col0 + g * 4;
+                const uint32_t v0 = __float_as_uint(__uint_as_float(r[g * 4 + 0]) * rs * cscale(cc + 0));
+                const uint32_t v1 = __float_as_uint(__uint_as_float(r[g * 4 + 1]) * rs * cscale(cc + 1));
+                const uint32_t v2 = __float_as_uint(__uint_as_float(r[g * 4 + 2]) * rs * cscale(cc + 2));
+                const uint32_t v3 = __float_as_uint(__uint_as_float(r[g * 4 + 3]) * rs * cscale(cc + 3));
                 asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v0), "r"(v1), "r"(v2), "r"(v3)
                              : "memory");
               }
@@ -312,10 +380,11 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
                   const uint32_t dst = rowbase + ((static_cast<uint32_t>(h * 4 + g) ^ sw) << 4);
-                  const uint32_t v0 = pack_bf16(__uint_as_float(r[g * 8 + 0]) * p.alpha, __uint_as_float(r[g * 8 + 1]) * p.alpha);
-                  const uint32_t v1 = pack_bf16(__uint_as_float(r[g * 8 + 2]) * p.alpha, __uint_as_float(r[g * 8 + 3]) * p.alpha);
-                  const uint32_t v2 = pack_bf16(__uint_as_float(r[g * 8 + 4]) * p.alpha, __uint_as_float(r[g * 8 + 5]) * p.alpha);
-                  const uint32_t v3 = pack_bf16(__uint_as_float(r[g * 8 + 6]) * p.alpha, __uint_as_float(r[g * 8 + 7]) * p.alpha);
+                  const int cc = col0 + h * 32 + g * 8;
+                  const uint32_t v0 = pack_bf16(__uint_as_float(r[g * 8 + 0]) * rs * cscale(cc + 0), __uint_as_float(r[g * 8 + 1]) * rs * cscale(cc + 1));
+                  const uint32_t v1 = pack_bf16(__uint_as_float(r[g * 8 + 2]) * rs * cscale(cc + 2), __uint_as_float(r[g * 8 + 3]) * rs * cscale(cc + 3));
+                  const uint32_t v2 = pack_bf16(__uint_as_float(r[g * 8 + 4]) * rs * cscale(cc + 4), __uint_as_float(r[g * 8 + 5]) * rs * cscale(cc + 5));
+                  const uint32_t v3 = pack_bf16(__uint_as_float(r[g * 8 + 6]) * rs * cscale(cc + 6), __uint_as_float(r[g * 8 + 7]) * rs * cscale(cc + 7));
                   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v0), "r"(v1), "r"(v2), "r"(v3)
                                : "memory");
                 }
@@ -382,6 +451,62 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
       if (lane == 0) mbar_arrive_cluster(mapa(tempty_bar(acc), 0));
     }
     if (issuer) tma_store_wait<0>();  // every piece has left shared memory and landed
+  } else if (GATHER && lane == 0 && p.g_n_remote > 0) {
+    // -------------------------------------------------- weight gather (warp 6, both CTAs)
+    // Pieces of the remote blocks are claimed from one counter by all CTAs, pulled peer -> shared -> local with
+    // bulk copies (two in flight), and counted per block once they have landed; every remote byte crosses NVLink
+    // once. Blocks are pulled in the order the tile walk needs them.
+    const uint32_t total = static_cast<uint32_t>(p.g_n_remote) * p.g_ppb;
+    const long long block_bytes = (long long)p.g_ppb * G2_COPY;
+    uint32_t* counter = p.flags + p.n_blocks;
+    auto claim = [&]() -> long long {
+      const uint32_t i = atomicAdd(counter, 1u);
+      return i < total ? (long long)i : -1ll;
+    };
+    auto locate = [&](long long piece, int& blk, int& owner, long long& off) {
+      const int2 e = p.g_blocks[piece / p.g_ppb];
+      blk = e.x;
+      owner = e.y;
+      off = (long long)blk * block_bytes + (piece % p.g_ppb) * G2_COPY;
+    };
+    uint32_t i = 0;
+    long long cur = claim();
+    if (cur >= 0) {
+      int blk, owner; long long off;
+      locate(cur, blk, owner, off);
+      mbar_arrive_expect_tx(copy_bar(0), G2_COPY);
+      bulk_load(copy_base, p.peer_b[owner] + off, G2_COPY, copy_bar(0));
+    }
+    uint32_t* pending = nullptr;  // flag of the piece whose store is in flight
+    while (cur >= 0) {
+      if (pending) {
+        tma_store_wait<0>();  // landed in local memory (and its buffer is free again)
+        fence_proxy_async_all();
+        red_release_gpu_add(pending, 1u);
+        pending = nullptr;
+      }
+      const long long nxt = claim();
+      if (nxt >= 0) {
+        int blk, owner; long long off;
+        locate(nxt, blk, owner, off);
+        const uint32_t b = (i + 1) & 1u;
+        mbar_arrive_expect_tx(copy_bar(b), G2_COPY);
+        bulk_load(copy_base + b * G2_COPY, p.peer_b[owner] + off, G2_COPY, copy_bar(b));
+      }
+      if (!mbar_wait(copy_bar(i & 1u), (i >> 1) & 1u, &abort_flag, p.status, 0x36)) break;
+      int blk, owner; long long off;
+      locate(cur, blk, owner, off);
+      bulk_store(p.local_b + off, copy_base + (i & 1u) * G2_COPY, G2_COPY);
+      tma_store_commit();
+      pending = p.flags + blk;
+      cur = nxt;
+      ++i;
+    }
+    tma_store_wait<0>();
+    if (pending) {
+      fence_proxy_async_all();
+      red_release_gpu_add(pending, 1u);
+    }
   }
 
   __syncwarp();
@@ -400,22 +525,34 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
   }
 }
 
-template <int AMAJ, int BMAJ, typename OutT>
-static int launch_gemm2(const LbGemmArgs& a, const LbScatterArgs* sc, cudaStream_t stream) {
+struct F8Extra {
+  const float* row_scale;
+  const float* col_scale;
+  int a_fmt, b_fmt;  // 0 = e4m3, 1 = e5m2
+};
+
+template <int AMAJ, int BMAJ, typename OutT, bool GATHER = false, bool F8 = false>
+static int launch_gemm2(const LbGemmArgs& a, const LbScatterArgs* sc, cudaStream_t stream,
+                        const LbGatherArgs* ga = nullptr, const F8Extra* f8 = nullptr) {
   CUtensorMap ta, tb, tc;
   OwnerMaps owners;
   int rc;
+  constexpr int IN_ESZ = F8 ? 1 : 2;
+  constexpr int BK_IN = 128 / IN_ESZ;
   if (AMAJ == 0)
-    rc = make_tmap_4d(&ta, a.A, 2, a.K, a.M, a.lda, a.nb0, a.a_bs0, a.nb1, a.a_bs1, G2_BK, G2_ROWS);
+    rc = make_tmap_4d(&ta, a.A, IN_ESZ, a.K, a.M, a.lda, a.nb0, a.a_bs0, a.nb1, a.a_bs1, BK_IN, G2_ROWS);
   else
     rc = make_tmap_4d(&ta, a.A, 2, a.M, a.K, a.lda, a.nb0, a.a_bs0, a.nb1, a.a_bs1, 64, G2_BK);
   if (rc) return 100 + rc;
   if (BMAJ == 0)
-    rc = make_tmap_4d(&tb, a.B, 2, a.K, a.N, a.ldb, a.nb0, a.b_bs0, a.nb1, a.b_bs1, G2_BK, G2_ROWS);
+    rc = make_tmap_4d(&tb, a.B, IN_ESZ, a.K, a.N, a.ldb, a.nb0, a.b_bs0, a.nb1, a.b_bs1, BK_IN, G2_ROWS);
   else
     rc = make_tmap_4d(&tb, a.B, 2, a.N, a.K, a.ldb, a.nb0, a.b_bs0, a.nb1, a.b_bs1, 64, G2_BK);
   if (rc) return 200 + rc;
   Gemm2Params p;
+  p.row_scale = f8 ? f8->row_scale : nullptr;
+  p.col_scale = f8 ? f8->col_scale : nullptr;
+  p.idesc_f8 = f8 ? make_idesc(G2_BM, G2_BN, (uint32_t)f8->a_fmt, (uint32_t)f8->b_fmt, 0, 0) : 0u;
   p.M = a.M; p.N = a.N; p.K = a.K;
   p.tiles_m = (a.M + G2_BM - 1) / G2_BM;
   p.tiles_n = (a.N + G2_BN - 1) / G2_BN;
@@ -427,6 +564,35 @@ static int launch_gemm2(const LbGemmArgs& a, const LbScatterArgs* sc, cudaStream
   p.m_rot = 0;
   p.scatter = 0;
   p.blocks = nullptr;
+  p.raster_n = 0;
+  p.n_order = nullptr;
+  p.g_blocks = nullptr;
+  p.g_n_remote = 0;
+  p.g_ppb = 0;
+  p.local_b = nullptr;
+  p.flags = nullptr;
+  p.n_blocks = 0;
+  for (int r = 0; r < LB_MAX_PEERS; ++r) p.peer_b[r] = nullptr;
+  if (GATHER) {
+    if (!ga) return 8;
+    p.raster_n = 1;
+    p.group_m = p.tiles_n < 8 ? p.tiles_n : 8;
+    p.n_order = ga->n_order;
+    p.g_blocks = reinterpret_cast<const int2*>(ga->remote_blocks);
+    p.g_n_remote = ga->n_remote;
+    p.g_ppb = static_cast<uint32_t>((long long)G2_ROWS * a.K * 2 / G2_COPY);
+    p.local_b = reinterpret_cast<uint8_t*>(const_cast<void*>(a.B));
+    p.flags = ga->flags;
+    p.n_blocks = a.N / G2_ROWS;
+    for (int r = 0; r < LB_MAX_PEERS; ++r)
+      p.peer_b[r] = reinterpret_cast<const uint8_t*>(ga->b_peers[r < ga->world ? r : 0]);
+    if (ga->n_remote > 0) {
+      // own blocks start complete, remote ones at zero; the piece counter follows the block flags
+      cudaError_t e = cudaMemcpyAsync(ga->flags, ga->flags_init, sizeof(uint32_t) * (p.n_blocks + 1),
+                                      cudaMemcpyDeviceToDevice, stream);
+      if (e != cudaSuccess) return 500 + (int)e;
+    }
+  }
   constexpr int ESZ = (int)sizeof(OutT);
   constexpr int PC = 128 / ESZ;
   // TMA stores need a 16-byte aligned base and pitches that are multiples of 16 bytes
@@ -462,8 +628,9 @@ static int launch_gemm2(const LbGemmArgs& a, const LbScatterArgs* sc, cudaStream
   const long long tiles = (long long)p.tiles_m * p.tiles_n * a.nb0 * a.nb1;
   const int max_pairs = num_sms() / 2;
   const int pairs = (int)(tiles < max_pairs ? tiles : max_pairs);
-  if (ensure_dyn_smem<gemm2_kernel<AMAJ, BMAJ, OutT>>(G2_SMEM)) return 300;
-  gemm2_kernel<AMAJ, BMAJ, OutT><<<2 * pairs, G2_THREADS, G2_SMEM, stream>>>(ta, tb, tc, owners, p);
+  if (ensure_dyn_smem<gemm2_kernel<AMAJ, BMAJ, OutT, GATHER, F8>>(G2_SMEM)) return 300;
+  gemm2_kernel<AMAJ, BMAJ, OutT, GATHER, F8>
+      <<<2 * pairs, GATHER ? G2_THREADS_GATHER : G2_THREADS, G2_SMEM, stream>>>(ta, tb, tc, owners, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;
@@ -483,6 +650,20 @@ int gemm2_dispatch(const LbGemmArgs& a, cudaStream_t s) {
   return 5;
 }
 
+// float8 operands on SM pairs: same contract as lb_gemm_fp8 (gemm_fp8.cu), which forwards large problems here
+int gemm2_fp8_dispatch(const LbGemmFp8Args& f, cudaStream_t s) {
+  LbGemmArgs a = {};
+  a.A = f.A; a.B = f.B; a.C = f.C; a.status = f.status;
+  a.M = f.M; a.N = f.N; a.K = f.K;
+  a.nb0 = a.nb1 = 1;
+  a.alpha = 1.f;
+  a.lda = f.lda; a.ldb = f.ldb; a.ldc = f.ldc;
+  F8Extra x = {f.row_scale, f.col_scale, f.a_fmt, f.b_fmt};
+  if (f.out_dtype == LB_BF16) return launch_gemm2<0, 0, __nv_bfloat16, false, true>(a, nullptr, s, nullptr, &x);
+  if (f.out_dtype == LB_F32) return launch_gemm2<0, 0, float, false, true>(a, nullptr, s, nullptr, &x);
+  return 5;
+}
+
 }  // namespace lb
 
 extern "C" int lb_gemm_scatter(const LbGemmArgs* args, const LbScatterArgs* sc, void* stream) {
@@ -494,4 +675,16 @@ extern "C" int lb_gemm_scatter(const LbGemmArgs* args, const LbScatterArgs* sc, 
   if ((a.ldc % 4) || (a.lda % 8) || (a.ldb % 8) || a.ldc < a.N || (a.N % 4)) return 3;
   if (sc->world < 1 || sc->world > LB_MAX_PEERS || !sc->blocks) return 4;
   return dispatch2<float>(a, sc, reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int lb_gemm_gather(const LbGemmArgs* args, const LbGatherArgs* ga, void* stream) {
+  using namespace lb;
+  if (!args || !ga) return 1;
+  const LbGemmArgs& a = *args;
+  if (a.M <= 0 || a.N <= 0 || a.K <= 0 || a.nb0 != 1 || a.nb1 != 1) return 1;
+  if (a.in_dtype != LB_BF16 || a.out_dtype != LB_BF16 || a.a_major != 0 || a.b_major != 0 || a.accumulate) return 2;
+  if ((a.ldc % 8) || (a.lda % 8) || a.ldb != a.K || a.K % 64 || a.N % G2_ROWS) return 3;  // whole contiguous blocks
+  if (ga->world < 1 || ga->world > LB_MAX_PEERS || ga->n_remote < 0) return 4;
+  if (ga->n_remote > 0 && (!ga->remote_blocks || !ga->flags || !ga->flags_init || !ga->n_order)) return 5;
+  return launch_gemm2<0, 0, __nv_bfloat16, true>(a, nullptr, reinterpret_cast<cudaStream_t>(stream), ga);
 }

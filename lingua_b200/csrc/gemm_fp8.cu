@@ -36,6 +36,7 @@ struct Params {
   const float* col_scale;
   void* C;
   uint32_t* status;
+  uint32_t idesc;  // carries the operand formats (e4m3 / e5m2)
 };
 
 template <typename OutT>
@@ -98,7 +99,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(BM, BN, 0u, 0u, 0, 0);  // e4m3 x e4m3 -> f32
+      const uint32_t idesc = p.idesc;
       uint32_t it = 0, tile_iter = 0;
       for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tile_iter) {
         const int acc = tile_iter & 1;
@@ -198,6 +199,7 @@ static int launch(const LbGemmFp8Args& a, cudaStream_t stream) {
   p.ldc = a.ldc;
   p.row_scale = a.row_scale; p.col_scale = a.col_scale;
   p.C = a.C; p.status = a.status;
+  p.idesc = make_idesc(BM, BN, (uint32_t)a.a_fmt, (uint32_t)a.b_fmt, 0, 0);
   const long long tiles = (long long)p.tiles_m * p.tiles_n;
   const int grid = (int)(tiles < num_sms() ? tiles : num_sms());
   auto kern = gemm_fp8_kernel<OutT>;
@@ -212,12 +214,15 @@ static int launch(const LbGemmFp8Args& a, cudaStream_t stream) {
 constexpr int Q_THREADS = 256;
 constexpr int Q_MAXV = 8;  // 8-element vectors per thread held in registers: K <= 16384
 
+template <int FMT = 0>
 __device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float d) {
-  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
-  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, FMT ? __NV_E5M2 : __NV_E4M3);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, FMT ? __NV_E5M2 : __NV_E4M3);
   return lo | (hi << 16);
 }
+constexpr float E5M2_MAX = 57344.f;
 
+template <int FMT>
 __global__ void __launch_bounds__(Q_THREADS)
 quant_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int K, uint8_t* __restrict__ out,
                   long long ldo, float* __restrict__ scale) {
@@ -246,7 +251,7 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int K, uin
   amax = 0.f;
 #pragma unroll
   for (int i = 0; i < Q_THREADS / 32; ++i) amax = fmaxf(amax, red[i]);
-  const float sc = fmaxf(amax, AMAX_EPS) / E4M3_MAX;
+  const float sc = fmaxf(amax, AMAX_EPS) / (FMT ? E5M2_MAX : E4M3_MAX);
   const float inv = 1.f / sc;
   if (threadIdx.x == 0) scale[row] = sc;
 #pragma unroll
@@ -257,8 +262,8 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int K, uin
       const float2 f0 = __bfloat1622float2(b[0]), f1 = __bfloat1622float2(b[1]);
       const float2 f2 = __bfloat1622float2(b[2]), f3 = __bfloat1622float2(b[3]);
       uint2 o;
-      o.x = cvt_e4m3x4(f0.x * inv, f0.y * inv, f1.x * inv, f1.y * inv);
-      o.y = cvt_e4m3x4(f2.x * inv, f2.y * inv, f3.x * inv, f3.y * inv);
+      o.x = cvt_e4m3x4<FMT>(f0.x * inv, f0.y * inv, f1.x * inv, f1.y * inv);
+      o.y = cvt_e4m3x4<FMT>(f2.x * inv, f2.y * inv, f3.x * inv, f3.y * inv);
       *reinterpret_cast<uint2*>(out + row * ldo + v * 8) = o;
     }
   }
@@ -266,6 +271,7 @@ quant_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int K, uin
 
 // Rows longer than the register budget of quant_rows_kernel: two passes over the row (the second one
 // hits L2).
+template <int FMT>
 __global__ void __launch_bounds__(Q_THREADS)
 quant_rows_long_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int K, uint8_t* __restrict__ out,
                        long long ldo, float* __restrict__ scale) {
@@ -289,7 +295,7 @@ quant_rows_long_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int K
   amax = 0.f;
 #pragma unroll
   for (int i = 0; i < Q_THREADS / 32; ++i) amax = fmaxf(amax, red[i]);
-  const float sc = fmaxf(amax, AMAX_EPS) / E4M3_MAX;
+  const float sc = fmaxf(amax, AMAX_EPS) / (FMT ? E5M2_MAX : E4M3_MAX);
   const float inv = 1.f / sc;
   if (threadIdx.x == 0) scale[row] = sc;
   for (int v = threadIdx.x; v < nvec; v += Q_THREADS) {
@@ -298,8 +304,8 @@ quant_rows_long_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int K
     const float2 f0 = __bfloat1622float2(b[0]), f1 = __bfloat1622float2(b[1]);
     const float2 f2 = __bfloat1622float2(b[2]), f3 = __bfloat1622float2(b[3]);
     uint2 o;
-    o.x = cvt_e4m3x4(f0.x * inv, f0.y * inv, f1.x * inv, f1.y * inv);
-    o.y = cvt_e4m3x4(f2.x * inv, f2.y * inv, f3.x * inv, f3.y * inv);
+    o.x = cvt_e4m3x4<FMT>(f0.x * inv, f0.y * inv, f1.x * inv, f1.y * inv);
+    o.y = cvt_e4m3x4<FMT>(f2.x * inv, f2.y * inv, f3.x * inv, f3.y * inv);
     *reinterpret_cast<uint2*>(out + row * ldo + v * 8) = o;
   }
 }
@@ -330,26 +336,42 @@ quant_transpose_kernel(const __nv_bfloat16* __restrict__ w, int N, int K, const 
 }  // namespace f8
 }  // namespace lb
 
+extern "C" int lb_quant_rows(const void* x, long long ldx, long long rows, int K, void* out, long long ldo,
+                             float* scale, void* stream) {
+  return lb_quant_rows_fmt(x, ldx, rows, K, out, ldo, scale, 0, stream);
+}
+
 extern "C" int lb_gemm_fp8(const LbGemmFp8Args* a, void* stream) {
   if (!a || a->M <= 0 || a->N <= 0 || a->K <= 0) return 1;
   if ((a->lda % 16) || (a->ldb % 16) || (a->K % 16)) return 2;  // TMA strides in bytes
   if ((a->ldc % 8) || (a->N % 8)) return 3;
+  if (a->a_fmt < 0 || a->a_fmt > 1 || a->b_fmt < 0 || a->b_fmt > 1) return 4;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  // large problems run on SM pairs (256 x 256 tiles, epilogue through TMA stores), like the bf16 products
+  const long long tiles2 = (long long)((a->M + 255) / 256) * ((a->N + 255) / 256);
+  if (a->M >= 256 && a->N >= 256 && tiles2 >= lb::num_sms() / 2 && !getenv("LB_FP8_ONE_SM"))
+    return lb::gemm2_fp8_dispatch(*a, s);
   if (a->out_dtype == LB_BF16) return lb::f8::launch<__nv_bfloat16>(*a, s);
   if (a->out_dtype == LB_F32) return lb::f8::launch<float>(*a, s);
   return 5;
 }
 
-extern "C" int lb_quant_rows(const void* x, long long ldx, long long rows, int K, void* out, long long ldo,
-                             float* scale, void* stream) {
-  if (!x || !out || !scale || rows <= 0) return 1;
+extern "C" int lb_quant_rows_fmt(const void* x, long long ldx, long long rows, int K, void* out, long long ldo,
+                                 float* scale, int fmt, void* stream) {
+  if (!x || !out || !scale || rows <= 0 || fmt < 0 || fmt > 1) return 1;
   if (K % 8 != 0 || ldx % 8 != 0 || ldo % 8 != 0) return 2;
-  if (K > 8 * lb::f8::Q_THREADS * lb::f8::Q_MAXV)
-    lb::f8::quant_rows_long_kernel<<<(unsigned)rows, lb::f8::Q_THREADS, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-        reinterpret_cast<const __nv_bfloat16*>(x), ldx, K, reinterpret_cast<uint8_t*>(out), ldo, scale);
-  else
-    lb::f8::quant_rows_kernel<<<(unsigned)rows, lb::f8::Q_THREADS, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-        reinterpret_cast<const __nv_bfloat16*>(x), ldx, K, reinterpret_cast<uint8_t*>(out), ldo, scale);
+  using namespace lb::f8;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const __nv_bfloat16* xp = reinterpret_cast<const __nv_bfloat16*>(x);
+  uint8_t* op = reinterpret_cast<uint8_t*>(out);
+  const bool lng = K > 8 * Q_THREADS * Q_MAXV;
+  if (fmt == 0) {
+    if (lng) quant_rows_long_kernel<0><<<(unsigned)rows, Q_THREADS, 0, st>>>(xp, ldx, K, op, ldo, scale);
+    else quant_rows_kernel<0><<<(unsigned)rows, Q_THREADS, 0, st>>>(xp, ldx, K, op, ldo, scale);
+  } else {
+    if (lng) quant_rows_long_kernel<1><<<(unsigned)rows, Q_THREADS, 0, st>>>(xp, ldx, K, op, ldo, scale);
+    else quant_rows_kernel<1><<<(unsigned)rows, Q_THREADS, 0, st>>>(xp, ldx, K, op, ldo, scale);
+  }
   lb::g_launches.fetch_add(1, std::memory_order_relaxed);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;

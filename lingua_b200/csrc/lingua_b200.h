@@ -89,11 +89,15 @@ typedef struct LbGemmFp8Args {
   int M, N, K;
   int out_dtype;  // LB_BF16 or LB_F32
   long long lda, ldb, ldc;
+  int a_fmt, b_fmt;  // 0 = e4m3, 1 = e5m2 (the reference's choice for gradients is configurable the same way)
 } LbGemmFp8Args;
 int lb_gemm_fp8(const LbGemmFp8Args* a, void* stream);
 // x bf16 [rows, K] (row pitch ldx) -> out e4m3 [rows, K] (pitch ldo bytes), scale[r] = max(amax_r, 1e-12) / 448.
 int lb_quant_rows(const void* x, long long ldx, long long rows, int K, void* out, long long ldo, float* scale,
                   void* stream);
+// Same with the target format chosen: fmt 0 = e4m3 (largest value 448), 1 = e5m2 (57344).
+int lb_quant_rows_fmt(const void* x, long long ldx, long long rows, int K, void* out, long long ldo, float* scale,
+                      int fmt, void* stream);
 // w bf16 [N, K] contiguous -> out e4m3 [K, N] (pitch ldo bytes), every element divided by *scale (device fp32).
 int lb_quant_transpose(const void* w, int N, int K, const float* scale, void* out, long long ldo, void* stream);
 
@@ -147,6 +151,28 @@ typedef struct LbScatterArgs {
   long long dst_rows[LB_MAX_PEERS];
 } LbScatterArgs;
 int lb_gemm_scatter(const LbGemmArgs* args, const LbScatterArgs* sc, void* stream);
+
+// Forward GEMM with the parameter all-gather fused in (gemm2.cu): C[M, N] = A[M, K] * B[N, K]^T (bf16, both
+// K-contiguous) where B is this rank's copy of a weight matrix whose 128-row blocks are owned by the ranks of a
+// data-parallel group. Only the own blocks of the local copy are current when the call is made; the kernel pulls
+// every other block out of its owner's copy (b_peers[owner], the same matrix in that rank's peer-visible buffer) into
+// the local one while it multiplies, own blocks first, and leaves the local copy complete for later kernels.
+//   n_order        [ceil(N / 256)] column tiles in the order they are computed (device)
+//   remote_blocks  n_remote (block, owner) int pairs in the order they are pulled (device)
+//   flags_init     [N / 128 + 1] uint32: K / 64 for own blocks, 0 for remote ones, 0 for the trailing counter (device)
+//   flags          workspace of the same size, overwritten by every call (device)
+// N % 128 == 0, K % 64 == 0, ldb == K. The owners' copies must be final before the call (lb_peer_barrier) and
+// must not change before every reader has finished.
+typedef struct LbGatherArgs {
+  int world, rank;
+  int n_remote;
+  const int* n_order;
+  const int* remote_blocks;
+  const uint32_t* flags_init;
+  uint32_t* flags;
+  const void* b_peers[LB_MAX_PEERS];
+} LbGatherArgs;
+int lb_gemm_gather(const LbGemmArgs* args, const LbGatherArgs* ga, void* stream);
 
 // Barrier over the ranks of a group. pads[r] is the peer-visible address of rank r's pad
 // (uint32[world], zero before first use); epoch is the number of this barrier on these pads,
@@ -226,5 +252,6 @@ int ensure_dyn_smem(int bytes) {
 }
 // two-SM (cta_group::2) 256 x 256-tile variant, gemm2.cu
 int gemm2_dispatch(const LbGemmArgs& a, cudaStream_t s);
+int gemm2_fp8_dispatch(const LbGemmFp8Args& a, cudaStream_t s);
 }
 #endif

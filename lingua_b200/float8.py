@@ -19,6 +19,7 @@ switched to ``Fp8Linear``.
 from __future__ import annotations
 
 import ctypes as C
+import os
 import re
 from typing import Optional, Tuple
 
@@ -26,7 +27,18 @@ import torch
 import torch.nn as nn
 
 E4M3_MAX = 448.0
+E5M2_MAX = 57344.0
 EPS = 1e-12
+_FMT = {"e4m3": (0, torch.float8_e4m3fn, E4M3_MAX), "e5m2": (1, torch.float8_e5m2, E5M2_MAX)}
+# Format of the output gradient in the input-gradient product: e4m3 as lingua/float8.py:43-47 uses for every
+# operand, or e5m2 (wider range, the usual choice for gradients). LB_FP8_GRAD_FORMAT / set_grad_format select it.
+_GRAD_FORMAT = os.environ.get("LB_FP8_GRAD_FORMAT", "e4m3")
+
+
+def set_grad_format(fmt: str) -> None:
+    global _GRAD_FORMAT
+    assert fmt in _FMT
+    _GRAD_FORMAT = fmt
 
 
 class GemmFp8Args(C.Structure):
@@ -35,6 +47,7 @@ class GemmFp8Args(C.Structure):
         ("row_scale", C.c_void_p), ("col_scale", C.c_void_p), ("status", C.c_void_p),
         ("M", C.c_int), ("N", C.c_int), ("K", C.c_int), ("out_dtype", C.c_int),
         ("lda", C.c_longlong), ("ldb", C.c_longlong), ("ldc", C.c_longlong),
+        ("a_fmt", C.c_int), ("b_fmt", C.c_int),
     ]
 
 
@@ -48,6 +61,9 @@ def _L():
         lib.lb_quant_rows.argtypes = [C.c_void_p, C.c_longlong, C.c_longlong, C.c_int, C.c_void_p, C.c_longlong,
                                       C.c_void_p, C.c_void_p]
         lib.lb_quant_rows.restype = C.c_int
+        lib.lb_quant_rows_fmt.argtypes = [C.c_void_p, C.c_longlong, C.c_longlong, C.c_int, C.c_void_p, C.c_longlong,
+                                          C.c_void_p, C.c_int, C.c_void_p]
+        lib.lb_quant_rows_fmt.restype = C.c_int
         lib.lb_quant_transpose.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_longlong,
                                            C.c_void_p]
         lib.lb_quant_transpose.restype = C.c_int
@@ -65,25 +81,27 @@ def supported(K: int, N: int) -> bool:
 
 
 # ------------------------------------------------------------------ quantisation
-def quant_rows_ref(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
-    """(e4m3 values, scale [rows]) - PyTorch statement of the row-wise quantisation."""
+def quant_rows_ref(x: torch.Tensor, fmt: str = "e4m3") -> Tuple[torch.Tensor, torch.Tensor]:
+    """(float8 values, scale [rows]) - PyTorch statement of the row-wise quantisation."""
+    _, dt, fmax = _FMT[fmt]
     amax = x.abs().amax(dim=-1).float()
-    scale = amax.clamp(min=EPS) / E4M3_MAX
-    q = (x.float() * scale.reciprocal()[:, None]).clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn)
+    scale = amax.clamp(min=EPS) / fmax
+    q = (x.float() * scale.reciprocal()[:, None]).clamp(-fmax, fmax).to(dt)
     return q, scale
 
 
-def quant_rows(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+def quant_rows(x: torch.Tensor, fmt: str = "e4m3") -> Tuple[torch.Tensor, torch.Tensor]:
     if not _native(x):
-        return quant_rows_ref(x)
+        return quant_rows_ref(x, fmt)
     from .ops import _lib
 
+    code, dt, _ = _FMT[fmt]
     rows, K = x.shape
     assert x.stride(1) == 1
-    q = torch.empty(rows, K, dtype=torch.float8_e4m3fn, device=x.device)
+    q = torch.empty(rows, K, dtype=dt, device=x.device)
     scale = torch.empty(rows, dtype=torch.float32, device=x.device)
-    _lib.check(_L().lb_quant_rows(x.data_ptr(), x.stride(0), rows, K, q.data_ptr(), K, scale.data_ptr(),
-                                  _lib.stream_ptr()), "lb_quant_rows")
+    _lib.check(_L().lb_quant_rows_fmt(x.data_ptr(), x.stride(0), rows, K, q.data_ptr(), K, scale.data_ptr(), code,
+                                      _lib.stream_ptr()), "lb_quant_rows")
     return q, scale
 
 
@@ -132,6 +150,8 @@ def scaled_mm(a8: torch.Tensor, sa: torch.Tensor, b8: torch.Tensor, sb: torch.Te
     a.M, a.N, a.K = M, N, K
     a.out_dtype = 0 if out_dtype == torch.bfloat16 else 1
     a.lda, a.ldb, a.ldc = a8.stride(0), b8.stride(0), out.stride(0)
+    a.a_fmt = 1 if a8.dtype == torch.float8_e5m2 else 0
+    a.b_fmt = 1 if b8.dtype == torch.float8_e5m2 else 0
     _lib.check(_L().lb_gemm_fp8(C.byref(a), _lib.stream_ptr()), "lb_gemm_fp8")
     return out
 
@@ -146,7 +166,7 @@ def fp8_forward_mm(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
 
 def fp8_dgrad_mm(dy: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """dy [M, N] @ w [N, K]: row-wise scales for dy, one scale for the weight."""
-    dy8, sdy = quant_rows(dy)
+    dy8, sdy = quant_rows(dy, _GRAD_FORMAT)
     sw = (w.detach().abs().amax().float().clamp(min=EPS) / E4M3_MAX).reshape(1)
     wt8 = quant_transpose(w, sw)
     return scaled_mm(dy8, sdy, wt8, sw, dy.dtype if dy.dtype != torch.float32 else torch.float32)

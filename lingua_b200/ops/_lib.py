@@ -43,6 +43,14 @@ class ScatterArgs(C.Structure):
     ]
 
 
+class GatherArgs(C.Structure):
+    _fields_ = [
+        ("world", C.c_int), ("rank", C.c_int), ("n_remote", C.c_int),
+        ("n_order", C.c_void_p), ("remote_blocks", C.c_void_p), ("flags_init", C.c_void_p), ("flags", C.c_void_p),
+        ("b_peers", C.c_void_p * 8),
+    ]
+
+
 class AttnArgs(C.Structure):
     _fields_ = [
         ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("o", C.c_void_p), ("lse", C.c_void_p),
@@ -85,6 +93,9 @@ def load():
     if hasattr(lib, "lb_gemm_scatter"):
         lib.lb_gemm_scatter.argtypes = [C.POINTER(GemmArgs), C.POINTER(ScatterArgs), C.c_void_p]
         lib.lb_gemm_scatter.restype = C.c_int
+    if hasattr(lib, "lb_gemm_gather"):
+        lib.lb_gemm_gather.argtypes = [C.POINTER(GemmArgs), C.POINTER(GatherArgs), C.c_void_p]
+        lib.lb_gemm_gather.restype = C.c_int
     lib.lb_launch_count.restype = C.c_longlong
     lib.lb_launch_count_add.argtypes = [C.c_longlong]
     _declare(lib)

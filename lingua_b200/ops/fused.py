@@ -18,7 +18,7 @@ import torch
 
 from . import functional as F
 from .attention import flash_bwd, flash_fwd
-from .gemm import gemm, gemm_scatter, mm_nn, mm_nt, mm_tn
+from .gemm import gemm, gemm_gather, gemm_scatter, mm_nn, mm_nt, mm_tn
 
 
 # Statistics probe (lingua_b200.probe.AutoProbeD): when set, the functions below report their
@@ -60,13 +60,37 @@ def fused_view(ws: Sequence[torch.Tensor]) -> Optional[torch.Tensor]:
     return torch.as_strided(base, (rows, K), (K, 1), base.storage_offset())
 
 
+def _stale_targets(ws: Sequence[torch.Tensor]):
+    """Gather handles of weights whose remote rows have not been fetched since the last optimiser step (the sharded
+    engine leaves the all-gather of some matrices to their first forward GEMM), or None."""
+    t0 = getattr(ws[0], "lb_gather", None)
+    if t0 is None or not t0.group.gather_stale:
+        return None
+    targets = [w.lb_gather for w in ws if hasattr(w, "lb_gather")]
+    return targets if t0.engine.gather_is_stale(targets) else None
+
+
 def _weights(ws: Sequence[torch.Tensor]) -> torch.Tensor:
+    stale = _stale_targets(ws)
+    if stale is not None:
+        stale[0].engine.ensure_gathered(stale)
     v = fused_view([w.detach() for w in ws])
     return v if v is not None else torch.cat([w.detach() for w in ws], dim=0)
 
 
 def _fwd_mm(x: torch.Tensor, ws: Sequence[torch.Tensor]) -> torch.Tensor:
-    """x @ [W_0; W_1; ...]^T - in e4m3 with row-wise scales when the weights are marked for float8."""
+    """x @ [W_0; W_1; ...]^T - in e4m3 with row-wise scales when the weights are marked for float8. The first
+    product with a weight after an optimiser step may also be the one that gathers it from the other ranks."""
+    stale = _stale_targets(ws)
+    if (stale is not None and len(stale) == len(ws) and x.is_cuda and x.dim() == 2 and x.shape[0] >= 256
+            and not getattr(ws[0], "lb_fp8", False)):
+        engine = stale[0].engine
+        plan = engine.gather_plan(stale)
+        v = fused_view([w.detach() for w in ws])
+        if plan is not None and v is not None and x.stride(1) == 1:
+            out = gemm_gather(x, v, plan[0], plan[1])
+            engine.mark_gathered(stale)
+            return out
     w = _weights(ws)
     if getattr(ws[0], "lb_fp8", False) and x.is_cuda and x.shape[0] >= 16:
         from ..float8 import fp8_forward_mm

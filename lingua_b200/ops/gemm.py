@@ -151,6 +151,58 @@ def gemm_scatter(a: torch.Tensor, b: torch.Tensor, blocks: torch.Tensor, dst_ptr
     _lib.check(rc, f"lb_gemm_scatter(M={M},N={N},K={K})")
 
 
+class GatherPlan:
+    """Device-side tables of one weight matrix for ``gemm_gather``: which rank owns each 128-row block, the order in
+    which the column tiles are computed (own rows first, then the next ranks') and the order in which remote blocks
+    are pulled."""
+
+    def __init__(self, owners: Sequence[int], rank: int, world: int, K: int, device):
+        nblk = len(owners)
+        dist_of = [(o - rank) % world for o in owners]  # 0 = own, then the ring
+        n_tiles = (nblk + 1) // 2
+        tile_key = [max(dist_of[2 * t:2 * t + 2]) for t in range(n_tiles)]
+        order = sorted(range(n_tiles), key=lambda t: (tile_key[t], t))
+        # pull blocks in the order the tile walk reaches them
+        remote = [(b, owners[b]) for t in order for b in (2 * t, 2 * t + 1) if b < nblk and owners[b] != rank]
+        ppb = K // 64
+        self.rank, self.world, self.n_remote = rank, world, len(remote)
+        self.n_order = torch.tensor(order, dtype=torch.int32, device=device)
+        self.remote_blocks = torch.tensor(remote if remote else [(0, 0)], dtype=torch.int32, device=device)
+        self.flags_init = torch.tensor([ppb if o == rank else 0 for o in owners] + [0], dtype=torch.int32, device=device)
+        self.flags = torch.zeros(nblk + 1, dtype=torch.int32, device=device)
+
+
+def gemm_gather(x: torch.Tensor, w: torch.Tensor, plan: GatherPlan, peer_ptrs: Sequence[int],
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x @ w^T`` ([M, K] x [N, K]^T, bf16) where only this rank's 128-row blocks of ``w`` are current: the other
+    blocks are pulled out of their owners' copies (``peer_ptrs[r]`` = address of the same matrix on rank r) into ``w``
+    by the GEMM kernel itself while it computes the tiles that need only local rows. ``w`` is complete afterwards."""
+    assert x.is_cuda and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and w.dim() == 2
+    M, K = x.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and w.is_contiguous() and x.stride(1) == 1 and N % 128 == 0 and K % 64 == 0
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    args = _lib.GemmArgs()
+    args.A, args.B, args.C = x.data_ptr(), w.data_ptr(), out.data_ptr()
+    args.status = _lib.status_word(x.device).data_ptr()
+    args.M, args.N, args.K = M, N, K
+    args.a_major = args.b_major = 0
+    args.in_dtype = args.out_dtype = _lib.LB_BF16
+    args.accumulate, args.alpha, args.force_bn = 0, 1.0, 0
+    args.lda, args.ldb, args.ldc = x.stride(0), K, out.stride(0)
+    args.nb0 = args.nb1 = 1
+    ga = _lib.GatherArgs()
+    ga.world, ga.rank, ga.n_remote = plan.world, plan.rank, plan.n_remote
+    ga.n_order, ga.remote_blocks = plan.n_order.data_ptr(), plan.remote_blocks.data_ptr()
+    ga.flags_init, ga.flags = plan.flags_init.data_ptr(), plan.flags.data_ptr()
+    for r, ptr in enumerate(peer_ptrs):
+        ga.b_peers[r] = ptr
+    rc = _lib.load().lb_gemm_gather(C.byref(args), C.byref(ga), _lib.stream_ptr())
+    _lib.check(rc, f"lb_gemm_gather(M={M},N={N},K={K})")
+    return out
+
+
 def mm_nt(x: torch.Tensor, w: torch.Tensor, **kw) -> torch.Tensor:
     """x[M,K] @ w[N,K]^T -> [M,N] (linear forward)."""
     return gemm(x, w, **kw)

@@ -71,10 +71,17 @@ def row_bounds(rows: int, world: int) -> List[int]:
 
 
 class ScatterTarget:
-    """Attached to a scatter parameter as ``p.lb_scatter`` when its gradient has no local matrix."""
+    """Attached to a scatter parameter as ``p.lb_scatter`` when its gradient has no local matrix, and as
+    ``p.lb_gather`` when its remote rows are fetched by the first GEMM that multiplies with it."""
 
     def __init__(self, engine: "ShardedEngine", group: "ParamGroup", index: int):
         self.engine, self.group, self.index = engine, group, index
+
+
+# Weights whose first use in a step is a forward GEMM of the native transformer block: their all-gather is fused
+# into that GEMM (the kernel pulls the peers' row blocks while it computes), everything else is pushed by the
+# copy engines right after the optimiser step.
+DEFAULT_GATHER_IN_GEMM = ("attention.wq", "attention.wk", "attention.wv", "feed_forward.w1", "feed_forward.w3")
 
 
 class ParamGroup:
@@ -142,6 +149,10 @@ class ParamGroup:
         self.peer_full: Optional[List[torch.Tensor]] = None      # every rank's ``full`` buffer, when peer-visible
         self.plain_stage: Optional[torch.Tensor] = None           # [world-1, plain_shard] slots for plain slices
         self.peer_plain_stage: Optional[List[torch.Tensor]] = None
+        self.full_ptrs: Optional[List[int]] = None   # peer-visible addresses of every rank's ``full``
+        self.gather_idx: List[int] = []          # matrices whose all-gather happens inside their first forward GEMM
+        self.gather_stale: set = set()           # ... and whose remote rows have not been fetched yet in this step
+        self.push_segments: List[Tuple[int, int]] = []  # (offset in full, n) pushed to the peers after the step
         self.area: Optional[int] = None          # dedicated staging area of the matrix part (None: from the pool)
         self.area_active: Optional[int] = None   # staging area in use by the current backward pass
         self.area_use: int = -1
@@ -214,7 +225,7 @@ class ShardedEngine:
                  compute_dtype: torch.dtype = torch.bfloat16, optim: Optional[EngineOptim] = None,
                  device: Optional[torch.device] = None, p2p_gather: bool = True, replicate_group=None,
                  tp_group=None, scatter_filter: Optional[Callable] = None, accumulate: bool = False,
-                 n_pool_areas: int = 3):
+                 n_pool_areas: int = 3, gather_in_gemm: Optional[Sequence[str]] = None):
         self.model = model
         self.pg = process_group
         self.world = dist.get_world_size(process_group) if (dist.is_initialized() and process_group is not False) else 1
@@ -232,6 +243,9 @@ class ShardedEngine:
         # gradient accumulation over micro-batches keeps every group's staging slots alive for the whole step
         self.accumulate = accumulate
         self.n_pool_areas = max(2, n_pool_areas)
+        if gather_in_gemm is None:
+            gather_in_gemm = () if os.environ.get("LB_GATHER_IN_GEMM", "1") == "0" else DEFAULT_GATHER_IN_GEMM
+        self.gather_in_gemm = tuple(gather_in_gemm)
         # True while micro-batches are still being accumulated: a group's backward must not start its
         # gradient reduction before the last micro-batch has added its share
         self.defer_reduce = False
@@ -326,6 +340,7 @@ class ShardedEngine:
         W = self.world
         if self._symm is not None:
             g.peer_full = [holder["h"].get_buffer(r, (g.padded,), self.compute_dtype) for r in range(W)]
+            g.full_ptrs = [int(p) for p in holder["h"].buffer_ptrs]
             if g.plain_shard:
                 g.plain_grad = torch.zeros(g.plain_padded, dtype=torch.float32, device=self.device)
                 g.plain_stage, h2 = self._symm_tensor((W - 1) * g.plain_shard, torch.float32)
@@ -342,9 +357,74 @@ class ShardedEngine:
                 p.main_grad = g.plain_grad[o - g.plain_off:o - g.plain_off + n].view(p.shape)
             else:
                 p.lb_scatter = ScatterTarget(self, g, i)
+                stem = fqn[:-len(".weight")] if fqn.endswith(".weight") else fqn
+                if (any(stem.endswith(pat) for pat in self.gather_in_gemm) and p.shape[0] % BLOCK_ROWS == 0
+                        and p.shape[1] % 64 == 0 and self.compute_dtype == torch.bfloat16):
+                    p.lb_gather = p.lb_scatter
+                    g.gather_idx.append(i)
             owner_path, _, attr = fqn.rpartition(".")
             self.model.get_submodule(owner_path)._parameters[attr] = p
+        # what the copy engines push after a step: this rank's pieces of everything that is not gathered in a GEMM
+        r = self.rank
+        for i, (fqn, p) in enumerate(g.params[:g.n_mats]):
+            n = (g.bounds[i][r + 1] - g.bounds[i][r]) * p.shape[1]
+            if n and i not in g.gather_idx:
+                g.push_segments.append((g.offsets[fqn][0] + g.bounds[i][r] * p.shape[1], n))
+        if g.plain_shard:
+            g.push_segments.append((g.plain_off + r * g.plain_shard, g.plain_shard))
+        g.push_segments = [(fo, n) for fo, n, _ in ParamGroup._merge([(fo, n, fo) for fo, n in g.push_segments])]
         self.groups.append(g)
+
+    # -- parameter all-gather inside the first forward GEMM
+    def gather_plan(self, targets: Sequence[ScatterTarget]):
+        """(GatherPlan, peer addresses of the fused weight) for adjacent gather parameters, or None."""
+        from ..ops.gemm import GatherPlan
+
+        g = targets[0].group
+        idx = [t.index for t in targets]
+        if any(t.group is not g for t in targets) or idx != list(range(idx[0], idx[0] + len(idx))):
+            return None
+        mats = [g.params[i][1] for i in idx]
+        K = mats[0].shape[1]
+        if any(m.shape[1] != K or m.shape[0] % BLOCK_ROWS or m.numel() % 8 for m in mats) or g.full_ptrs is None:
+            return None
+        key = ("gather",) + tuple(idx)
+        plan = g._tables.get(key)
+        if plan is None:
+            owners = []
+            for i, m in zip(idx, mats):
+                b = g.bounds[i]
+                owners += [max(r for r in range(self.world) if b[r] <= blk * BLOCK_ROWS)
+                           for blk in range(m.shape[0] // BLOCK_ROWS)]
+            plan = GatherPlan(owners, self.rank, self.world, K, self.device)
+            g._tables[key] = plan
+        off = g.offsets[g.params[idx[0]][0]][0] * g.full.element_size()
+        return plan, [ptr + off for ptr in g.full_ptrs]
+
+    def gather_is_stale(self, targets: Sequence[ScatterTarget]) -> bool:
+        return any(t.index in t.group.gather_stale for t in targets)
+
+    def mark_gathered(self, targets: Sequence[ScatterTarget]) -> None:
+        for t in targets:
+            t.group.gather_stale.discard(t.index)
+
+    def ensure_gathered(self, targets: Sequence[ScatterTarget]) -> None:
+        """Fetch the remote rows of gather parameters that some consumer other than the fused GEMM needs (a float8
+        quantiser, an evaluation path): plain peer -> local copies on the current stream."""
+        for t in targets:
+            g, i = t.group, t.index
+            if i not in g.gather_stale:
+                continue
+            fqn, p = g.params[i]
+            K = p.shape[1]
+            for o in range(self.world):
+                if o == self.rank:
+                    continue
+                r0, r1 = g.bounds[i][o], g.bounds[i][o + 1]
+                if r1 > r0:
+                    lo = g.offsets[fqn][0] + r0 * K
+                    g.full[lo:lo + (r1 - r0) * K].copy_(g.peer_full[o][lo:lo + (r1 - r0) * K], non_blocking=True)
+            g.gather_stale.discard(i)
 
     def _setup_areas(self) -> None:
         """Staging areas for the matrix gradients: [world-1 slots] x [largest matrix shard]. Groups of the most
@@ -684,9 +764,12 @@ class ShardedEngine:
                 if g.peer_full is not None:
                     for k in range(1, self.world):  # start with the next rank so that links are used evenly
                         r = (self.rank + k) % self.world
-                        for fo, n, _ in g.my_segments:
+                        for fo, n in g.push_segments:
                             g.peer_full[r][fo:fo + n].copy_(g.full[fo:fo + n], non_blocking=True)
-                    self._peer_barrier()  # every rank's pushes, mine included, have landed
+                    # every rank's pushes, mine included, have landed, and every rank's own rows of the matrices
+                    # that are gathered inside their first GEMM are final
+                    self._peer_barrier()
+                    g.gather_stale = set(g.gather_idx)
                 else:
                     self._gather_by_collective(g)
                 g.params_ready = torch.cuda.Event()

@@ -96,3 +96,20 @@ def test_fp8_model_matches_bf16_and_trains():
         losses.append(loss.item())
     _lib.check_status()
     assert losses[-1] < losses[0] - 0.5, losses
+
+
+@pytest.mark.parametrize("M,N,K", [(2048, 4096, 1024), (8192, 2560, 512), (2304, 2304, 4096)])
+@pytest.mark.parametrize("fmt", ["e4m3", "e5m2"])
+def test_scaled_mm_on_sm_pairs_and_e5m2(M, N, K, fmt):
+    """Problems large enough for the SM-pair kernel (256 x 256 tiles, scales applied in its TMA-store epilogue);
+    the activation operand in either float8 format."""
+    torch.manual_seed(4)
+    a8, sa = F8.quant_rows(torch.randn(M, K, device="cuda").to(bf), fmt)
+    assert a8.dtype == (torch.float8_e5m2 if fmt == "e5m2" else torch.float8_e4m3fn)
+    b8, sb = F8.quant_rows(torch.randn(N, K, device="cuda").to(bf))
+    for dt in (bf, torch.float32):
+        out = F8.scaled_mm(a8, sa, b8, sb, dt)
+        torch.cuda.synchronize()
+        _lib.check_status()
+        ref = F8.scaled_mm_ref(a8, sa, b8, sb, torch.float32)
+        assert (out.float() - ref).abs().max().item() < 1e-2 * ref.abs().max().item()

@@ -130,3 +130,40 @@ def test_gemm_scatter_rows_to_owners(W, M, N, K):
     for o in range(W):
         if rows[o]:
             _check(dst[o][:rows[o]], 1.5 * ref[bounds[o]:bounds[o + 1]], K)
+
+
+@pytest.mark.parametrize("W,rank", [(1, 0), (2, 1), (4, 2), (8, 7)])
+@pytest.mark.parametrize("M,N,K", [(512, 1024, 512), (2048, 1408, 256), (8192, 4096, 1024)])
+def test_gemm_gather_pulls_remote_weight_blocks(W, rank, M, N, K):
+    """Only this rank's blocks of the weight are valid locally; the kernel fetches the rest from the "peers" (buffers
+    of this GPU here) while it multiplies, and leaves the local copy complete."""
+    torch.manual_seed(W + rank)
+    x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w_true = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    nblk = N // 128
+    bounds = [round(r * nblk / W) for r in range(W + 1)]
+    owners = [max(r for r in range(W) if bounds[r] <= b) for b in range(nblk)]
+    w_local = torch.full_like(w_true, float("nan"))
+    for b, o in enumerate(owners):
+        if o == rank:
+            w_local[b * 128:(b + 1) * 128] = w_true[b * 128:(b + 1) * 128]
+    # every peer's copy is valid only in the blocks that peer owns
+    peers = []
+    for r in range(W):
+        if r == rank:
+            peers.append(w_local)
+            continue
+        c = torch.full_like(w_true, float("nan"))
+        for b, o in enumerate(owners):
+            if o == r:
+                c[b * 128:(b + 1) * 128] = w_true[b * 128:(b + 1) * 128]
+        peers.append(c)
+    plan = G.GatherPlan(owners, rank, W, K, "cuda")
+    out = G.gemm_gather(x, w_local, plan, [p.data_ptr() for p in peers])
+    torch.cuda.synchronize()
+    assert torch.equal(w_local, w_true), "the local copy of the weight is not complete after the call"
+    _check(out, _ref(x, w_true), K)
+    # a second call on the same plan (flags are re-initialised by the launch) gives the same result
+    out2 = G.gemm_gather(x, w_local, plan, [p.data_ptr() for p in peers])
+    torch.cuda.synchronize()
+    assert torch.equal(out, out2)
