@@ -69,7 +69,7 @@ __device__ __forceinline__ Tile tile_of(int tile, const Params& p, int first) {
   return t;
 }
 
-template <int MODE>
+template <int MODE, int BMAJ = 0>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_gather,
                const __grid_constant__ CUtensorMap tma_b, const __grid_constant__ TmapSet owners,
@@ -148,7 +148,14 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           mbar_arrive_expect_tx(full_bar(s), STAGE_BYTES);
           const uint32_t sa = smem_base + s * STAGE_BYTES;
           tma_load_4d(sa, amap, full_bar(s), kb * BK, m0, 0, 0);
-          tma_load_4d(sa + A_BYTES, &tma_b, full_bar(s), kb * BK, n0, 0, 0);
+          if (BMAJ == 0) {
+            tma_load_4d(sa + A_BYTES, &tma_b, full_bar(s), kb * BK, n0, 0, 0);
+          } else {
+            // B stored [K, N] (N contiguous): BK rows of 64-element chunks, one chunk column per load
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_4d(sa + A_BYTES + c * (BK * ROW_BYTES), &tma_b, full_bar(s), n0 + c * 64, kb * BK, 0, 0);
+          }
         }
         if (!ok) break;
       }
@@ -156,7 +163,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   } else if (warp == 1) {
     if (lane == 0) {
       // ------------------------------------------------ MMA issuer
-      constexpr uint32_t idesc = make_idesc(BM, BN, 1u, 1u, 0, 0);
+      constexpr uint32_t idesc = make_idesc(BM, BN, 1u, 1u, 0, BMAJ);
       uint32_t it = 0, tile_iter = 0;
       for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tile_iter) {
         const int acc = tile_iter & 1;
@@ -176,7 +183,8 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t ad = make_smem_desc(sa + k * 32u, 16u, 1024u);
-            const uint64_t bd = make_smem_desc(sb + k * 32u, 16u, 1024u);
+            const uint64_t bd = BMAJ == 0 ? make_smem_desc(sb + k * 32u, 16u, 1024u)
+                                          : make_smem_desc(sb + k * (16u * ROW_BYTES), BK * ROW_BYTES, 1024u);
             umma_f16(tmem_d, ad, bd, idesc, (kb | k) != 0);
           }
           umma_commit(empty_bar(s));
@@ -334,7 +342,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   }
 }
 
-template <int MODE>
+template <int MODE, int BMAJ = 0>
 static int launch(const LbTpGemmArgs& a, cudaStream_t stream) {
   const int W = a.world;
   const int rows = a.M / W;
@@ -358,7 +366,10 @@ static int launch(const LbTpGemmArgs& a, cudaStream_t stream) {
       if (rc) return 120 + rc;
     }
   }
-  rc = make_tmap_4d(&tb, a.B, 2, a.K, a.N, a.ldb, 1, 0, 1, 0, BK, BN);
+  if (BMAJ == 0)
+    rc = make_tmap_4d(&tb, a.B, 2, a.K, a.N, a.ldb, 1, 0, 1, 0, BK, BN);
+  else
+    rc = make_tmap_4d(&tb, a.B, 2, a.N, a.K, a.ldb, 1, 0, 1, 0, 64, BK);
   if (rc) return 200 + rc;
 
   Params p;
@@ -379,8 +390,8 @@ static int launch(const LbTpGemmArgs& a, cudaStream_t stream) {
   }
   const long long tiles = (long long)W * p.tiles_per_slab * p.tiles_n;
   const int grid = (int)(tiles < num_sms() ? tiles : num_sms());
-  auto kern = gemm_tp_kernel<MODE>;
-  if (ensure_dyn_smem<gemm_tp_kernel<MODE>>(SMEM)) return 300;
+  auto kern = gemm_tp_kernel<MODE, BMAJ>;
+  if (ensure_dyn_smem<gemm_tp_kernel<MODE, BMAJ>>(SMEM)) return 300;
   kern<<<grid, THREADS, SMEM, stream>>>(ta, tg, tb, owners, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   cudaError_t e = cudaGetLastError();
@@ -399,8 +410,8 @@ extern "C" int lb_gemm_tp(const LbTpGemmArgs* a, void* stream) {
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (a->mode == 1) {
     if (!a->C || (a->world > 1 && (!a->gather || !a->flags))) return 6;
-    return lb::tp::launch<1>(*a, s);
+    return a->b_major ? lb::tp::launch<1, 1>(*a, s) : lb::tp::launch<1, 0>(*a, s);
   }
   if (!a->A || a->lda % 8 != 0 || a->slot_stride % 8 != 0) return 7;
-  return lb::tp::launch<2>(*a, s);
+  return a->b_major ? lb::tp::launch<2, 1>(*a, s) : lb::tp::launch<2, 0>(*a, s);
 }

@@ -131,6 +131,9 @@ typedef struct LbTpGemmArgs {
   long long lda;
   void* c_peers[LB_MAX_PEERS];
   long long slot_stride;
+  // 0: B is [N, K] with K contiguous (ldb = row pitch); 1: B is stored [K, N] with N contiguous (ldb = pitch between
+  // consecutive k), which is how a weight [out, in] enters the products of its backward pass without a transpose
+  int b_major;
 } LbTpGemmArgs;
 int lb_gemm_tp(const LbTpGemmArgs* a, void* stream);
 

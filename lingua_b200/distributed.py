@@ -38,6 +38,9 @@ class DistributedArgs:
     dp_replicate: int = 1  # replicas of that group (outer data-parallel dim)
     tp_size: int = 1
     fused_tp_forward: bool = True  # no-grad TP passes use the fused all-gather / reduce-scatter GEMMs
+    # TP training keeps the residual stream sharded by rows inside a TP group and runs its all-gathers and
+    # reduce-scatters inside the GEMM kernels (parallel/tp_train.py); off: all-reduce formulation
+    tp_sequence_parallel: bool = True
     p2p_param_gather: bool = True  # parameter all-gather by NVLink copy engines instead of NCCL kernels
     selective_activation_checkpointing: bool = False
     compile: bool = False
@@ -366,6 +369,13 @@ def parallelize_model(model, mesh: Mesh, model_args, distributed_args: Distribut
     from .ops import fused
 
     fused.set_recompute(distributed_args.selective_activation_checkpointing)
+    if distributed_args.tp_size > 1 and distributed_args.tp_sequence_parallel and device.type == "cuda" \
+            and hasattr(model, "tok_embeddings") and dtype == torch.bfloat16:
+        # training with a row-sharded residual stream and the TP collectives inside the GEMM kernels
+        from .parallel.tp_train import enable_sp_training
+
+        if enable_sp_training(model, mesh.group("tp"), device):
+            engine.tp_partial = True  # replicated weights see one rank's rows only: their gradients are summed
     if distributed_args.tp_size > 1 and distributed_args.fused_tp_forward and device.type == "cuda" \
             and hasattr(model, "tok_embeddings"):
         # evaluation / scoring passes run with the TP collectives inside the GEMM kernels

@@ -405,6 +405,11 @@ class LMTransformer(BaseTransformer):
                     and doc_start is None and tpf.accepts(B, S) and self.layers[0].attention.kv_cache is None):
                 # tensor-parallel scoring / evaluation: collectives fused into the GEMM kernels
                 return tpf(token_values, target)
+            sp = getattr(self, "tp_sp", None)
+            if (sp is not None and causal and tok_idx is None and sp.accepts(B * S)
+                    and self.layers[0].attention.kv_cache is None and self.layers[0].attention.head_dim == 128):
+                # tensor parallel with a row-sharded residual stream, collectives inside the GEMM kernels
+                return self._forward_sp(sp, token_values, target, doc_start, doc_end, window, causal, cs, B, S)
             return self._forward_native(token_values, target, tok_idx, doc_start, doc_end, window, causal, cs, B, S)
         h = self.tok_embeddings(token_values)
         for layer in self.layers:
@@ -440,6 +445,42 @@ class LMTransformer(BaseTransformer):
             return fused.LinearCrossEntropyFn.apply(y, w_out, target.reshape(-1), self.loss_chunk, gs)
         y, _ = _final_norm(x, pending, self.norm)
         return fused.LinearFn.apply(y, w_out).view(B, S, -1)
+
+    def _forward_sp(self, sp, tokens, target, doc_start, doc_end, window, causal, cs, B, S):
+        """Sequence-parallel tensor-parallel pass (``parallel/tp_train.py``): every TP rank carries ``B*S / tp``
+        consecutive rows of the residual stream; every rank of the group is given the same tokens."""
+        from ..parallel.tp_train import SumOverGroupFn, sp_block_forward
+
+        T = B * S
+        sp.setup(T, self.dim)
+        rows = slice(sp.rank * sp.Tl, (sp.rank + 1) * sp.Tl)
+        if doc_start is not None:
+            doc_start = doc_start.reshape(-1).int().contiguous()
+        if doc_end is not None:
+            doc_end = doc_end.reshape(-1).int().contiguous()
+        eng = getattr(self, "_engine", None)
+        if eng is not None:
+            eng.boundary("tok_embeddings")
+        x = fused.EmbeddingFn.apply(tokens.reshape(-1)[rows].contiguous(), self.tok_embeddings.weight)
+        for i, layer in enumerate(self.layers):
+            if eng is not None:
+                (x,) = eng.boundary(f"layers.{i}", x)
+            x = sp_block_forward(layer, sp, x, cs, B, S, doc_start, doc_end, window, None, causal)
+        if eng is not None:
+            (x,) = eng.boundary("output", x)
+            eng.boundary("")
+        y, _ = _final_norm(x, None, self.norm)
+        w_out = self.output.weight
+        if target is not None:
+            tgt = target.reshape(-1)
+            n_valid = (tgt >= 0).sum().clamp(min=1).float()  # over all rows: every rank sees the same targets
+            gs = getattr(self, "loss_grad_scale", None) if torch.is_grad_enabled() else None
+            part = fused.LinearCrossEntropyFn.apply(y, w_out, tgt[rows].contiguous(), self.loss_chunk, gs, n_valid)
+            return SumOverGroupFn.apply(part, sp.group)
+        local = fused.LinearFn.apply(y, w_out)
+        full = torch.empty(T, local.shape[1], dtype=local.dtype, device=local.device)
+        torch.distributed.all_gather_into_tensor(full, local.contiguous(), group=sp.group)
+        return full.view(B, S, -1)
 
     def reset_parameters(self, init_std=None):
         super().reset_parameters()

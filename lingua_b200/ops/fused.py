@@ -397,12 +397,15 @@ class LinearCrossEntropyFn(torch.autograd.Function):
     backward only hands out the stored input gradient."""
 
     @staticmethod
-    def forward(ctx, y, w, target, chunk, grad_scale=None):
+    def forward(ctx, y, w, target, chunk, grad_scale=None, n_valid=None):
+        # n_valid: number of rows the mean is taken over when ``y`` holds only a share of them (the rows of one
+        # sequence-parallel rank); default: the valid rows of ``target``
         M = y.shape[0]
         wd = w.detach()
         tgt = target.reshape(-1)
         total = torch.zeros((), dtype=torch.float32, device=y.device)
-        n_valid = (tgt >= 0).sum().clamp(min=1).float()
+        if n_valid is None:
+            n_valid = (tgt >= 0).sum().clamp(min=1).float()
         fused_bwd = grad_scale is not None and (ctx.needs_input_grad[0] or w.requires_grad)
         ctx.fused_bwd, ctx.w, ctx.chunk, ctx.grad_scale = fused_bwd, w, chunk, grad_scale
         if not fused_bwd:
@@ -473,7 +476,7 @@ class LinearCrossEntropyFn(torch.autograd.Function):
         w, chunk = ctx.w, ctx.chunk
         if ctx.fused_bwd:
             dy, dw_acc = ctx.saved_tensors
-            return dy, (None if dw_acc is None else dw_acc.to(w.dtype)), None, None, None
+            return dy, (None if dw_acc is None else dw_acc.to(w.dtype)), None, None, None, None
         y, tgt, lse, n_valid = ctx.saved_tensors
         wd = w.detach()
         M = y.shape[0]
@@ -499,4 +502,4 @@ class LinearCrossEntropyFn(torch.autograd.Function):
                     mm_tn(dl, y[r0:r1], out=dw_acc, accumulate=True)
             del dl
         dw = None if (has_mg or dw_acc is None) else dw_acc.to(w.dtype)
-        return dy, dw, None, None, None
+        return dy, dw, None, None, None, None

@@ -234,6 +234,9 @@ class ShardedEngine:
         self.rep_pg = replicate_group if replicate_group not in (None, False) else None
         self.rep_world = dist.get_world_size(self.rep_pg) if self.rep_pg is not None else 1
         self.tp_pg = tp_group if tp_group not in (None, False) else None
+        # Sequence-parallel TP: every TP rank computes the gradients of the replicated weights (norms, embedding,
+        # head) from its own rows only, so they are partial sums that still have to be added over the TP group.
+        self.tp_partial = False
         self.optim = optim or EngineOptim()
         self.device = device or next(model.parameters()).device
         self.compute_dtype = compute_dtype
@@ -663,7 +666,7 @@ class ShardedEngine:
             self.comm_stream.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(self.comm_stream):
                 parts.zero_()
-                fused_norm = self.rep_world == 1
+                fused_norm = self.rep_world == 1 and not self.tp_partial
                 if self.p2p:
                     ps = g.plain_shard
                     for k in range(1, W):
@@ -694,6 +697,7 @@ class ShardedEngine:
                 if self.rep_world > 1:
                     dist.all_reduce(g.grad_shard, op=dist.ReduceOp.SUM, group=self.rep_pg)
                     g.grad_shard.mul_(1.0 / self.rep_world)
+                self._sum_tp_partials(g)
                 if not fused_norm:
                     parts.zero_()
                     self._sumsq_classes(g, gi)
@@ -705,8 +709,18 @@ class ShardedEngine:
         if self.rep_world > 1:
             dist.all_reduce(g.grad_shard, op=dist.ReduceOp.SUM, group=self.rep_pg)
             g.grad_shard.mul_(1.0 / self.rep_world)
+        self._sum_tp_partials(g)
         parts.zero_()
         self._sumsq_classes(g, gi)
+
+    def _sum_tp_partials(self, g: ParamGroup) -> None:
+        """Add up, over the TP group, this rank's shard of the gradients of weights that are replicated inside it
+        (sequence-parallel training only; after the data-parallel reduction, so only shard-sized pieces travel)."""
+        if not self.tp_partial or self.tp_pg is None:
+            return
+        for so, n, cls in g.classes():
+            if cls == 1:
+                dist.all_reduce(g.grad_shard[so:so + n], op=dist.ReduceOp.SUM, group=self.tp_pg)
 
     def _reduce_by_collective(self, g: ParamGroup) -> None:
         """Fallback without peer memory: all-reduce the whole-group gradient and keep the owned pieces."""

@@ -48,6 +48,7 @@ class TpGemmArgs(C.Structure):
         ("A", C.c_void_p), ("lda", C.c_longlong),
         ("c_peers", C.c_void_p * MAX_PEERS),
         ("slot_stride", C.c_longlong),
+        ("b_major", C.c_int),
     ]
 
 
@@ -69,6 +70,15 @@ def _lib_tp():
 
 
 # ------------------------------------------------------------------ raw ops
+def _b_layout(w: torch.Tensor):
+    """(b_major, ldb) of a [N, K] weight operand: K contiguous, or - the transposed view of a [K, N] matrix -
+    N contiguous, which the kernels read in place."""
+    if w.stride(1) == 1:
+        return 0, w.stride(0)
+    assert w.stride(0) == 1, "weight operand needs a unit stride in one dim"
+    return 1, w.stride(1)
+
+
 def ag_gemm(a_ptrs: Sequence[int], rank: int, rows_per_rank: int, w: torch.Tensor,
             gather: Optional[torch.Tensor], flags: Optional[torch.Tensor], out: Optional[torch.Tensor] = None,
             alpha: float = 1.0) -> torch.Tensor:
@@ -76,13 +86,14 @@ def ag_gemm(a_ptrs: Sequence[int], rank: int, rows_per_rank: int, w: torch.Tenso
     world = len(a_ptrs)
     N, K = w.shape
     M = rows_per_rank * world
-    assert w.dtype == torch.bfloat16 and w.stride(1) == 1
+    assert w.dtype == torch.bfloat16
+    b_major, ldb = _b_layout(w)
     assert rows_per_rank % ROW_TILE == 0, "rows per rank must be a multiple of 128"
     if out is None:
         out = torch.empty(M, N, dtype=torch.bfloat16, device=w.device)
     a = TpGemmArgs()
     a.mode, a.world, a.rank, a.M, a.N, a.K, a.alpha = 1, world, rank, M, N, K, alpha
-    a.B, a.ldb, a.status = w.data_ptr(), w.stride(0), _lib.status_word().data_ptr()
+    a.B, a.ldb, a.b_major, a.status = w.data_ptr(), ldb, b_major, _lib.status_word().data_ptr()
     for r in range(world):
         a.a_peers[r] = a_ptrs[r]
     if world > 1:
@@ -100,11 +111,12 @@ def gemm_scatter(x: torch.Tensor, w: torch.Tensor, c_ptrs: Sequence[int], rank: 
     world = len(c_ptrs)
     M, K = x.shape
     N = w.shape[0]
-    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.stride(1) == 1
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1
     assert M % (ROW_TILE * world) == 0, "rows per rank must be a multiple of 128"
+    b_major, ldb = _b_layout(w)
     a = TpGemmArgs()
     a.mode, a.world, a.rank, a.M, a.N, a.K, a.alpha = 2, world, rank, M, N, K, alpha
-    a.B, a.ldb, a.status = w.data_ptr(), w.stride(0), _lib.status_word().data_ptr()
+    a.B, a.ldb, a.b_major, a.status = w.data_ptr(), ldb, b_major, _lib.status_word().data_ptr()
     a.A, a.lda = x.data_ptr(), x.stride(0)
     for r in range(world):
         a.c_peers[r] = c_ptrs[r]

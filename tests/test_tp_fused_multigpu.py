@@ -39,3 +39,15 @@ def test_engine_fused_gradient_scatter(world, grad_acc):
     r = subprocess.run(cmd, env=dict(os.environ, LB_TEST_GRAD_ACC=str(grad_acc)), capture_output=True, text=True,
                        timeout=600)
     assert r.returncode == 0 and "ENGINE_P2P_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("world", [w for w in (2, 4) if w <= max(2, torch.cuda.device_count())])
+def test_tensor_parallel_training_sequence_parallel(world):
+    """TP 2 (and data parallel 2 x TP 2) training with the row-sharded residual stream and the all-gather /
+    reduce-scatter inside the GEMM kernels: same losses and gradient norms as the all-reduce TP path."""
+    worker = Path(__file__).with_name("tp_train_worker.py")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", "29655", str(worker)]
+    r = subprocess.run(cmd, env=dict(os.environ), capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "TP_TRAIN_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]

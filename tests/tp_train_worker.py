@@ -1,0 +1,67 @@
+"""One rank of the multi-GPU check of tensor-parallel training with a sequence-sharded residual stream (collectives
+inside the GEMM kernels) against the all-reduce formulation of the same tensor-parallel model. Started by torchrun
+from test_tp_fused_multigpu.py with TP degree 2 (2 ranks) or data parallel 2 x TP 2 (4 ranks)."""
+import os
+import sys
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
+
+from lingua_b200.api import Trainer  # noqa: E402
+from lingua_b200.distributed import DistributedArgs  # noqa: E402
+from lingua_b200.models.transformer import LMTransformerArgs  # noqa: E402
+from lingua_b200.ops import _lib  # noqa: E402
+from lingua_b200.optim import OptimArgs  # noqa: E402
+
+
+def run(sp: bool, world: int, dev, act: str):
+    tp = 2
+    args = LMTransformerArgs(dim=512, n_layers=2, n_heads=4, n_kv_heads=2, vocab_size=1024, max_seqlen=256,
+                             ffn_activation=act)
+    tr = Trainer(args, DistributedArgs(dp_shard=world // tp, tp_size=tp, fsdp_type="full_shard",
+                                       tp_sequence_parallel=sp, fused_tp_forward=False),
+                 OptimArgs(lr=3e-3, warmup=1, clip=1.0), total_steps=100, device=dev)
+    assert (getattr(tr.model, "tp_sp", None) is not None) == sp
+    dp_rank = tr.mesh.local_rank("dp")
+    g = torch.Generator().manual_seed(100 + dp_rank)  # the two ranks of a TP group read the same batch
+    tok = torch.randint(0, 1024, (2, 257), generator=g)
+    batch = torch.stack((tok[:, :-1], tok[:, 1:]), dim=-1)
+    ds = torch.zeros(2, 256, dtype=torch.int32)
+    ds[:, 96:] = 96  # two documents per sequence: block-causal attention
+    de = torch.full((2, 256), 96, dtype=torch.int32)
+    de[:, 96:] = 256
+    losses, norms = [], []
+    for _ in range(6):
+        losses.append(tr.train_step(batch, doc_start=ds.to(dev), doc_end=de.to(dev)))
+        norms.append(float(tr.last_grad_norm))
+    tr.engine.wait_all_params()
+    torch.cuda.synchronize()
+    _lib.check_status()
+    return losses, norms
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    dist.init_process_group("nccl", device_id=dev)
+    for act in ("swiglu", "relu2"):
+        l_sp, n_sp = run(True, world, dev, act)
+        l_ar, n_ar = run(False, world, dev, act)
+        ok = all(abs(a - b) <= (3e-3 if i < 3 else 5e-2) * abs(b) for i, (a, b) in enumerate(zip(l_sp, l_ar)))
+        ok = ok and all(abs(a - b) <= (2e-2 if i < 3 else 1e-1) * abs(b) for i, (a, b) in enumerate(zip(n_sp, n_ar)))
+        if not ok:
+            print(f"TP_TRAIN_MISMATCH rank {rank} {act} losses {l_sp} vs {l_ar} norms {n_sp} vs {n_ar}", flush=True)
+            raise SystemExit(1)
+        assert l_sp[-1] < l_sp[0]
+    dist.barrier()
+    if rank == 0:
+        print("TP_TRAIN_OK", l_sp, n_sp)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
