@@ -21,7 +21,8 @@ def available() -> str | None:
     return None
 
 
-def build(model_kwargs: dict, n_gpus: int, lr: float, total_steps: int, compile_model: bool, sac: bool):
+def build(model_kwargs: dict, n_gpus: int, lr: float, total_steps: int, compile_model: bool, sac: bool,
+          tp: int = 1, float8: bool = False):
     """Returns (step_fn(tokens[B,S+1] on device) -> loss tensor, info dict)."""
     for p in (str(HERE / "shims"), str(REF)):
         if p not in sys.path:
@@ -33,9 +34,12 @@ def build(model_kwargs: dict, n_gpus: int, lr: float, total_steps: int, compile_
     from lingua.optim import OptimArgs, build_optimizer
     from torch.distributed._tensor import DTensor
 
-    dist_args = DistributedArgs(dp_shard=n_gpus, dp_replicate=1, tp_size=1, fsdp_type="full_shard",
-                                model_dtype="bf16", compile=compile_model,
-                                selective_activation_checkpointing=sac)
+    # the reference's own switches: tensor parallelism (which it runs without torch.compile) and its row-wise float8
+    # recipe on the linear layers of the blocks (lingua/distributed.py:403-417)
+    dist_args = DistributedArgs(dp_shard=n_gpus // tp, dp_replicate=1, tp_size=tp, fsdp_type="full_shard",
+                                model_dtype="bf16", compile=compile_model and tp == 1,
+                                selective_activation_checkpointing=sac,
+                                float8_recipe="rowwise" if float8 else None)
     mesh = get_device_mesh(dist_args)
     margs = LMTransformerArgs(**model_kwargs)
     torch.manual_seed(777)
@@ -61,4 +65,4 @@ def build(model_kwargs: dict, n_gpus: int, lr: float, total_steps: int, compile_
         optimizer.zero_grad()
         return loss.detach()
 
-    return step_fn, {"compile": compile_model, "sac": sac}
+    return step_fn, {"compile": compile_model and tp == 1, "sac": sac}

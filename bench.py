@@ -150,6 +150,9 @@ def main() -> None:
                          "'reduced_depth' and is not a benchmark value)")
     ap.add_argument("--float8", action="store_true",
                     help="ours only: row-wise e4m3 forward / input-gradient products in the blocks (reported as dtype fp8)")
+    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel degree (the other ranks shard data-parallel)")
+    ap.add_argument("--doc-mask", action="store_true",
+                    help="block-causal attention over documents of uniform random length in [256, seq_len]")
     ap.add_argument("--fp8-steps", type=int, default=-1,
                     help="timed steps of the additional float8 measurement reported under 'fp8' (Llama arms of this "
                          "library only; -1 = min(steps, 10), 0 = skip)")
@@ -208,12 +211,36 @@ def main() -> None:
                               "unavailable": "the reference's mamba_ssm / causal_conv1d / accelerated_scan kernels are not installable offline"}))
         return
     dev = torch.device("cuda", local_rank)
-    gen = torch.Generator().manual_seed(1234 + rank)
+    tp = a.tp
+    assert world % tp == 0, "--tp must divide the number of GPUs"
+    dp = world // tp
+    if a.impl == "reference" and a.doc_mask:
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "n_gpus": a.gpus, "unavailable":
+                              "block-causal masks need xformers' fmha (not installable offline) or flex_attention under "
+                              "torch.compile, which the reference forbids together with tensor parallelism"}))
+        return
+    gen = torch.Generator().manual_seed(1234 + rank // tp)  # the ranks of a TP group read the same batch
     n_host = 4  # distinct host batches, cycled
     host = [torch.randint(0, mcfg["vocab_size"], (B, SEQ + 1), generator=gen).pin_memory() for _ in range(n_host)]
 
     def views(t):  # [B, S+1] -> [B, S, 2] (the loader's n_views=2 layout)
         return torch.stack((t[:, :-1], t[:, 1:]), dim=-1)
+
+    doc_bounds = None
+    if a.doc_mask:
+        # document lengths uniform in [256, seq_len], cut at the sequence end; int32 [B, S] first / past-last index
+        doc_bounds = []
+        for _ in range(n_host):
+            ds, de = torch.zeros(B, SEQ, dtype=torch.int32), torch.zeros(B, SEQ, dtype=torch.int32)
+            for b in range(B):
+                pos = 0
+                while pos < SEQ:
+                    n = int(torch.randint(256, SEQ + 1, (1,), generator=gen))
+                    end = min(SEQ, pos + n)
+                    ds[b, pos:end], de[b, pos:end] = pos, end
+                    pos = end
+            doc_bounds.append((ds, de))
 
     launches = None
     extra = {}
@@ -247,7 +274,7 @@ def main() -> None:
                     else:
                         margs, kw = LMTransformerArgs(**mcfg), {}
                     tr = Trainer(margs,
-                                 DistributedArgs(dp_shard=world, fsdp_type="full_shard",
+                                 DistributedArgs(dp_shard=dp, tp_size=tp, fsdp_type="full_shard",
                                                  selective_activation_checkpointing=sac, p2p_param_gather=p2p,
                                                  float8_recipe="rowwise" if a.float8 else None),
                                  OptimArgs(lr=1e-3, warmup=2000, clip=1.0), total_steps=100000, device=dev, **kw)
@@ -283,10 +310,17 @@ def main() -> None:
                                     "slots over NVLink + one slot-sum kernel per group; all-gather: copy engines")
             host_batches = [views(h).contiguous().pin_memory() for h in host]
 
+            dev_docs = [(ds.to(dev), de.to(dev)) for ds, de in doc_bounds] if doc_bounds else None
+
             def dev_step(i):
-                tr.train_step_async(dev_batches[i % n_host])
+                if dev_docs:
+                    tr.train_step_async(dev_batches[i % n_host], *dev_docs[i % n_host])
+                else:
+                    tr.train_step_async(dev_batches[i % n_host])
 
             def e2e_step(i):
+                if dev_docs:
+                    return tr.train_step(host_batches[i % n_host], *dev_docs[i % n_host])
                 return tr.train_step(host_batches[i % n_host])
 
             h2d = host_batches[0].numel() * host_batches[0].element_size()
@@ -296,7 +330,8 @@ def main() -> None:
             errs = []
             for compile_model, sac in ((not a.ref_eager, False), (not a.ref_eager, True), (False, True)):
                 try:
-                    step_fn, extra = reference_arm.build(mcfg, world, 1e-3, 100000, compile_model, sac)
+                    step_fn, extra = reference_arm.build(mcfg, world, 1e-3, 100000, compile_model and tp == 1, sac,
+                                                         tp=tp, float8=a.float8)
                     step_fn(host[0].to(dev))  # first step: compilation and allocator growth
                     torch.cuda.synchronize()
                     break
@@ -348,7 +383,7 @@ def main() -> None:
         # input-gradient products, measured in the same process right after the bf16 run
         fp8_info, peak_bytes = None, None
         n8 = min(a.steps, 10) if a.fp8_steps < 0 else a.fp8_steps
-        if a.impl == "ours" and not other and not a.float8 and n8 > 0 and a.layers == 0:
+        if a.impl == "ours" and not other and not a.float8 and n8 > 0 and a.layers == 0 and tp == 1:
             import gc
 
             peak_bytes = torch.cuda.max_memory_allocated()
@@ -375,8 +410,8 @@ def main() -> None:
                     dev_step(i)
                 ms8 = timed(torch, dist, dev_step, n8, world)
                 ms8_e2e = timed(torch, dist, e2e_step, n8, world)
-                fp8_info = {"value": round(B * SEQ * world / ms8 * 1e3, 1), "unit": "tokens/s", "steps": n8,
-                            "ms_per_step": round(ms8, 3), "e2e_value": round(B * SEQ * world / ms8_e2e * 1e3, 1),
+                fp8_info = {"value": round(B * SEQ * dp / ms8 * 1e3, 1), "unit": "tokens/s", "steps": n8,
+                            "ms_per_step": round(ms8, 3), "e2e_value": round(B * SEQ * dp / ms8_e2e * 1e3, 1),
                             "dtype": "fp8 (e4m3 row-wise fwd / dgrad in the blocks, bf16 wgrad and head)",
                             "speedup_over_bf16": round(ms / ms8, 4)}
             else:
@@ -386,7 +421,7 @@ def main() -> None:
             print(json.dumps({**base, "unavailable": f"out of memory: {str(e)[:200]}"}))
         return
 
-    tokens = B * SEQ * world
+    tokens = B * SEQ * dp
     value = tokens / ms * 1e3
     e2e_value = tokens / ms_e2e * 1e3
     peaks = {}
@@ -403,8 +438,9 @@ def main() -> None:
         "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "fp8 (e4m3 row-wise fwd / dgrad, bf16 wgrad)" if a.float8 else "bf16", "data": "synthetic uniform-random token ids, random-init weights",
         "impl": a.impl,
-        "config": {"model": a.model if other else f"llama_{a.model}", "global_batch": B * world, "seq_len": SEQ,
-                   "parallelism": f"fsdp{world}", "tokens_per_gpu_per_step": B * SEQ,
+        "config": {"model": a.model if other else f"llama_{a.model}", "global_batch": B * dp, "seq_len": SEQ,
+                   "parallelism": f"fsdp{dp}" + (f"xtp{tp}" if tp > 1 else ""), "tokens_per_gpu_per_step": B * SEQ // tp,
+                   "attention": "block-causal, document lengths U[256, seq_len]" if a.doc_mask else "causal",
                    "l2": "working set (>= 15 GB of weights re-read every step) exceeds the 126 MB L2; no explicit flush",
                    "optimizer": "AdamW fp32 states, clip 1.0, inside the timed region",
                    # everything that only one of the two arms has to say sits under "arm", so that both arms

@@ -834,6 +834,15 @@ class ShardedEngine:
         for gi in range(len(self.groups)):
             self.wait_params(gi)
 
+    def finish_param_gather(self) -> None:
+        """Make every rank's compute-dtype buffers complete now: wait for the pushes that are in flight and fetch the
+        rows of the matrices whose all-gather is otherwise left to their first forward GEMM. For consumers that read
+        the weights outside the model's forward pass."""
+        self.wait_all_params()
+        for g in self.groups:
+            if g.gather_stale:
+                self.ensure_gathered([g.params[i][1].lb_gather for i in sorted(g.gather_stale)])
+
     # ------------------------------------------------------------------ hooks for the model
     def boundary(self, module_path: str, *tensors):
         """Identity on ``tensors`` placed at the input of a group's module: its forward waits for

@@ -32,7 +32,7 @@ def run(p2p: bool, rank: int, world: int, dev):
     batch = torch.stack((tok[:, :-1], tok[:, 1:]), dim=-1)
     for _ in range(6 * acc):
         losses.append(tr.train_step(batch))
-    tr.engine.wait_all_params()
+    tr.engine.finish_param_gather()
     torch.cuda.synchronize()
     _lib.check_status()
     # every rank holds the same gathered parameters
