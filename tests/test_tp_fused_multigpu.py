@@ -38,7 +38,8 @@ def test_engine_fused_gradient_scatter(world, grad_acc):
            "--master-addr", "127.0.0.1", "--master-port", "29654", str(worker)]
     r = subprocess.run(cmd, env=dict(os.environ, LB_TEST_GRAD_ACC=str(grad_acc)), capture_output=True, text=True,
                        timeout=600)
-    assert r.returncode == 0 and "ENGINE_P2P_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+    fails = [l for l in r.stdout.splitlines() if "ENGINE_P2P_FAIL" in l]
+    assert r.returncode == 0 and "ENGINE_P2P_OK" in r.stdout, "\n".join(fails) + r.stdout[-1500:] + r.stderr[-1500:]
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
