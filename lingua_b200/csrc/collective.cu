@@ -283,20 +283,20 @@ extern "C" int lb_reduce_peers(const void* const* srcs, int n_src, float* out, l
   return e == cudaSuccess ? 0 : 400 + (int)e;
 }
 
-extern "C" int lb_reduce_slots(const float* own, const float* slots, int n_slots, long long slot_stride, float* out,
-                               long long n, float scale, float* sumsq, void* stream) {
+// max_blocks > 0 caps the grid: a reduction that runs beside the backward GEMMs has a whole layer's time to finish and
+// should trickle (few blocks, little pressure on the SMs and on L2) rather than burst; 0 = LB_REDUCE_BLOCKS or 8 per SM.
+extern "C" int lb_reduce_slots_grid(const float* own, const float* slots, int n_slots, long long slot_stride, float* out,
+                                    long long n, float scale, float* sumsq, int max_blocks, void* stream) {
   if (!own || !out || n <= 0 || n_slots < 0 || (n_slots > 0 && !slots)) return 1;
   if (reinterpret_cast<uintptr_t>(own) % 16 || reinterpret_cast<uintptr_t>(out) % 16 ||
       reinterpret_cast<uintptr_t>(slots) % 16 || slot_stride % 4)
     return 2;
   long long blocks = (n / 4 + 255) / 256;
-  // The kernel runs beside the backward GEMMs: LB_REDUCE_BLOCKS caps its grid (a smaller grid takes longer but
-  // draws less memory bandwidth at a time). Default: 8 blocks per SM.
   static const long long env_cap = [] {
     const char* s = getenv("LB_REDUCE_BLOCKS");
     return s ? atoll(s) : 0LL;
   }();
-  const long long cap = env_cap > 0 ? env_cap : (long long)lb::num_sms() * 8;
+  const long long cap = max_blocks > 0 ? max_blocks : env_cap > 0 ? env_cap : (long long)lb::num_sms() * 8;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   lb::reduce_slots_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
@@ -304,4 +304,9 @@ extern "C" int lb_reduce_slots(const float* own, const float* slots, int n_slots
   lb::g_launches.fetch_add(1, std::memory_order_relaxed);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 400 + (int)e;
+}
+
+extern "C" int lb_reduce_slots(const float* own, const float* slots, int n_slots, long long slot_stride, float* out,
+                               long long n, float scale, float* sumsq, void* stream) {
+  return lb_reduce_slots_grid(own, slots, n_slots, slot_stride, out, n, scale, sumsq, 0, stream);
 }

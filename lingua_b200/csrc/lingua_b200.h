@@ -188,6 +188,10 @@ int lb_peer_barrier_limit(void* const* pads, int world, int rank, uint32_t epoch
 // the reduction half of a reduce-scatter whose slots were filled by peer copies.
 int lb_reduce_slots(const float* own, const float* slots, int n_slots, long long slot_stride, float* out,
                     long long n, float scale, float* sumsq, void* stream);
+// Same with the grid capped at max_blocks blocks of 256 threads (0 = default): a small grid lets the reduction trickle
+// beside compute kernels instead of competing with them.
+int lb_reduce_slots_grid(const float* own, const float* slots, int n_slots, long long slot_stride, float* out,
+                         long long n, float scale, float* sumsq, int max_blocks, void* stream);
 
 // out[i] = scale * sum_r srcs[r][i], *sumsq += sum out[i]^2 (fp32, n elements, n_src <= LB_MAX_PEERS): a
 // reduce-scatter without staging. srcs[r] is this rank's slice inside rank r's buffer (peer-visible addresses,

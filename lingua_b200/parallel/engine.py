@@ -246,6 +246,7 @@ class ShardedEngine:
         # gradient accumulation over micro-batches keeps every group's staging slots alive for the whole step
         self.accumulate = accumulate
         self.n_pool_areas = max(2, n_pool_areas)
+        self.reduce_blocks = int(os.environ.get("LB_REDUCE_TRICKLE_BLOCKS", "64"))
         if gather_in_gemm is None:
             gather_in_gemm = () if os.environ.get("LB_GATHER_IN_GEMM", "1") == "0" else DEFAULT_GATHER_IN_GEMM
         self.gather_in_gemm = tuple(gather_in_gemm)
@@ -674,6 +675,9 @@ class ShardedEngine:
                             r = (self.rank + k) % W
                             g.peer_plain_stage[r][k - 1].copy_(g.plain_grad[r * ps:(r + 1) * ps], non_blocking=True)
                     self._peer_barrier()
+                    # groups that are followed by more backward work have a layer's time for their slot sum: a small
+                    # grid keeps it from competing with the GEMMs; the last ones are on the critical path
+                    trickle = self.reduce_blocks if gi >= 2 else 0
                     if g.area_active is not None:
                         if g.area is None:
                             self._use_barrier[g.area_use] = self._barrier_epoch
@@ -681,7 +685,7 @@ class ShardedEngine:
                         cls = self._uniform_class(g, 0, g.n_mats) if fused_norm else None
                         if n:
                             self._reduce_slots(g.grad_shard[:n], self._areas[g.area_active], self._area_cap[g.area_active],
-                                               g.grad_shard[:n], None if cls is None else parts[cls:cls + 1])
+                                               g.grad_shard[:n], None if cls is None else parts[cls:cls + 1], trickle)
                         fused_norm = fused_norm and cls is not None
                         g.area_active = None
                     if ps:
@@ -800,20 +804,20 @@ class ShardedEngine:
                 g.unshard_into(g.full, gathered[r * g.shard_cap:(r + 1) * g.shard_cap], r)
 
     def _reduce_slots(self, own: torch.Tensor, slots: torch.Tensor, slot_stride: int, out: torch.Tensor,
-                      part: Optional[torch.Tensor]) -> None:
+                      part: Optional[torch.Tensor], max_blocks: int = 0) -> None:
         import ctypes as C
 
         from ..ops import _lib
 
         lib = _lib.load()
         if not getattr(lib, "_reduce_slots_declared", False):
-            lib.lb_reduce_slots.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_longlong, C.c_void_p, C.c_longlong,
-                                            C.c_float, C.c_void_p, C.c_void_p]
-            lib.lb_reduce_slots.restype = C.c_int
+            lib.lb_reduce_slots_grid.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_longlong, C.c_void_p,
+                                                 C.c_longlong, C.c_float, C.c_void_p, C.c_int, C.c_void_p]
+            lib.lb_reduce_slots_grid.restype = C.c_int
             lib._reduce_slots_declared = True
-        rc = lib.lb_reduce_slots(own.data_ptr(), slots.data_ptr(), self.world - 1, slot_stride, out.data_ptr(),
-                                 own.numel(), 1.0 / self.world, None if part is None else part.data_ptr(),
-                                 _lib.stream_ptr())
+        rc = lib.lb_reduce_slots_grid(own.data_ptr(), slots.data_ptr(), self.world - 1, slot_stride, out.data_ptr(),
+                                      own.numel(), 1.0 / self.world, None if part is None else part.data_ptr(),
+                                      max_blocks, _lib.stream_ptr())
         _lib.check(rc, "lb_reduce_slots")
 
     def _peer_barrier(self) -> None:
