@@ -5,7 +5,7 @@ than L2 or an L2 flush between iterations) and prints achieved TFLOP/s or GB/s n
 measured peaks of ``MEASURED_PEAKS.json`` when that file is present. It is also the small,
 self-terminating workload to put under ``ncu`` when profiling a single kernel.
 
-ops: gemm, gemm_wgrad, attn_fwd, attn_bwd, rmsnorm, rmsnorm_bwd, glu, ce, adamw, rope, scan, conv1d, decode
+ops: gemm, gemm_wgrad, gemm_gather, gemm_scatter, gemm_tp_ag, gemm_tp_rs, rglru_gates, ssm_update, ssd, attn_fwd, attn_bwd, rmsnorm, rmsnorm_bwd, glu, ce, adamw, rope, scan, conv1d, decode
 """
 from __future__ import annotations
 
@@ -57,6 +57,7 @@ def main(argv=None):
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--world", type=int, default=4, help="emulated group size of the fused-collective GEMMs")
     ap.add_argument("--bn", type=int, default=0, help="gemm tile selector: 0 auto, 128, 256, 512 (two-SM)")
     a = ap.parse_args(argv)
     dev, bf = "cuda", torch.bfloat16
@@ -76,6 +77,77 @@ def main(argv=None):
         # gemm_fp8: the scaled e4m3 product alone; linear_fp8: both quantisation passes included
         fn = (lambda: F8.scaled_mm(x8, sx, w8, sw)) if a.op == "gemm_fp8" else (lambda: F8.fp8_forward_mm(x, w))
         flops = 2.0 * M * N * K
+    elif a.op in ("gemm_gather", "gemm_scatter"):
+        # the fused-collective forms of the GEMM with every "peer" being a buffer of this GPU: what the fusion costs
+        # the kernel itself (shorter TMA ring, gather warp, flag waits / owner-directed stores), NVLink aside
+        W, rank = a.world, 0
+        if a.op == "gemm_gather":
+            x, w = torch.randn(M, K, device=dev, dtype=bf), torch.randn(N, K, device=dev, dtype=bf)
+            nblk = N // 128
+            owners = [min(W - 1, b * W // nblk) for b in range(nblk)]
+            peers = [w] + [w.clone() for _ in range(W - 1)]
+            plan = G.GatherPlan(owners, rank, W, K, dev)
+            ptrs = [t.data_ptr() for t in peers]
+            fn = lambda: G.gemm_gather(x, w, plan, ptrs)
+        else:
+            dy, x = torch.randn(K, M, device=dev, dtype=bf), torch.randn(K, N, device=dev, dtype=bf)
+            nblk = (M + 127) // 128
+            bounds = [round(r * nblk / W) * 128 for r in range(W)] + [M]
+            table = []
+            for b in range(nblk):
+                o = max(r for r in range(W) if bounds[r] <= b * 128)
+                table.append((o, b * 128 - bounds[o]))
+            blocks = torch.tensor(table, dtype=torch.int32, device=dev)
+            rows = [bounds[o + 1] - bounds[o] for o in range(W)]
+            dst = [torch.empty(max(r, 1), N, device=dev) for r in rows]
+            ptrs = [t.data_ptr() for t in dst]
+            fn = lambda: G.gemm_scatter(dy.t(), x.t(), blocks, ptrs, rows, ldc=N, m_rot=bounds[1 % W] // 256)
+        flops = 2.0 * M * N * K
+    elif a.op in ("gemm_tp_ag", "gemm_tp_rs"):
+        # tensor-parallel GEMMs with the collective inside (csrc/gemm_tp.cu), one emulated rank of --world, peers local:
+        # ag = all-gather of the activation rows -> column-parallel GEMM, rs = row-parallel GEMM -> scatter to owners
+        from ..parallel import tp_fused as TP
+
+        W = a.world
+        Tl = M // W
+        if a.op == "gemm_tp_ag":
+            slabs = [torch.randn(Tl, K, device=dev, dtype=bf) for _ in range(W)]
+            w = torch.randn(N, K, device=dev, dtype=bf)
+            gather = torch.empty(M, K, device=dev, dtype=bf)
+            flags = torch.zeros(M // 128 + 1, dtype=torch.int32, device=dev)
+            out = torch.empty(M, N, device=dev, dtype=bf)
+            fn = lambda: TP.ag_gemm([t.data_ptr() for t in slabs], 0, Tl, w, gather, flags, out=out)
+        else:
+            x, w = torch.randn(M, K, device=dev, dtype=bf), torch.randn(N, K, device=dev, dtype=bf)
+            stages = [torch.empty(W, Tl, N, device=dev, dtype=bf) for _ in range(W)]
+            fn = lambda: TP.gemm_scatter(x, w, [t.data_ptr() for t in stages], 0, Tl * N)
+        flops = 2.0 * M * N * K
+    elif a.op == "rglru_gates":
+        rows, C = a.batch * a.seq, 4096
+        gx, ga, x = (torch.randn(rows, C, device=dev, dtype=bf) for _ in range(3))
+        sp = torch.rand(C, device=dev) + 0.1
+        fn = lambda: Q.rglru_gates(gx, ga, x, sp)
+        bytes_ = 5.0 * rows * C * 2
+    elif a.op == "ssm_update":
+        from . import ssd as S
+
+        n, h, pd, Ns, g = 32, 64, 64, 128, 1
+        row = torch.randn(n, h * pd + 2 * g * Ns, device=dev, dtype=bf)
+        x, Bm, Cm = row[:, :h * pd].view(n, h, pd), row[:, h * pd:h * pd + g * Ns].view(n, g, Ns), row[:, h * pd + g * Ns:].view(n, g, Ns)
+        dt, A = torch.rand(n, h, device=dev) * 0.1, -torch.rand(h, device=dev)
+        state = torch.randn(n, h, pd, Ns, device=dev)
+        fn = lambda: S.selective_state_update(state, x, dt, A, Bm, Cm, None)
+        bytes_ = 2.0 * state.numel() * 4
+    elif a.op == "ssd":
+        from . import ssd as S
+
+        b, sq, h, pd, Ns = a.batch, a.seq, 64, 64, 128
+        x = torch.randn(b, sq, h, pd, device=dev, dtype=bf)
+        dt = torch.rand(b, sq, h, device=dev) * 0.1
+        A = -torch.rand(h, device=dev)
+        Bm, Cm = torch.randn(b, sq, 1, Ns, device=dev, dtype=bf), torch.randn(b, sq, 1, Ns, device=dev, dtype=bf)
+        fn = lambda: S.ssd_chunked(x, dt, A, Bm, Cm, None, 256)
+        flops = 2.0 * b * sq * h * (256 * Ns + 256 * pd + 2 * pd * Ns)  # the four chunk products
     elif a.op == "gemm_wgrad":
         dy, x = torch.randn(K, M, device=dev, dtype=bf), torch.randn(K, N, device=dev, dtype=bf)
         out = torch.zeros(M, N, device=dev)
