@@ -18,6 +18,7 @@ import torch
 from .distributed import DistributedArgs, Mesh, get_device_mesh, parallelize_model
 from .models.transformer import LMTransformer, LMTransformerArgs, build_fsdp_grouping_plan
 from .optim import LRScheduler, OptimArgs, build_engine_optim, build_lr_fn
+from .profiling import nvtx_range
 
 
 class Trainer:
@@ -75,11 +76,14 @@ class Trainer:
         if doc_end is not None:
             kw["doc_end"] = doc_end
         self.engine.defer_reduce = (self.acc_step + 1) % self.grad_acc_steps != 0
-        loss = self.loss_fn(self.model, inputs, labels) if self.loss_fn else self.model(inputs, labels, **kw)
-        (loss / self.grad_acc_steps if self.grad_acc_steps > 1 else loss).backward()
+        with nvtx_range("forward"):
+            loss = self.loss_fn(self.model, inputs, labels) if self.loss_fn else self.model(inputs, labels, **kw)
+        with nvtx_range("backward"):
+            (loss / self.grad_acc_steps if self.grad_acc_steps > 1 else loss).backward()
         self.acc_step = (self.acc_step + 1) % self.grad_acc_steps
         if self.acc_step == 0:
-            self.last_grad_norm = self.engine.step(self.scheduler.get_lr())
+            with nvtx_range("optimizer"):
+                self.last_grad_norm = self.engine.step(self.scheduler.get_lr())
             self.scheduler.step()
             self.step += 1
         return loss.detach()

@@ -46,8 +46,12 @@ def _digest(src: Path, headers: list[Path]) -> str:
     return h.hexdigest()[:16]
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile every kernel source and link the shared library. Returns its path."""
+def build(force: bool = False, verbose: bool = False, debug_bounds: bool = False) -> Path:
+    """Compile every kernel source and link the shared library. Returns its path. ``debug_bounds`` builds the
+    bounds-checked variant (``-DLB_DEBUG_BOUNDS``, see csrc/common.cuh) next to the regular one as
+    ``liblingua_b200_dbg.so``; ``LINGUA_B200_LIB`` selects which file ``ops/_lib.py`` loads."""
+    if debug_bounds:
+        return _build_variant(["-DLB_DEBUG_BOUNDS"], LIBDIR / "liblingua_b200_dbg.so", LIBDIR / "obj_dbg", verbose)
     nvcc = nvcc_path()
     OBJDIR.mkdir(parents=True, exist_ok=True)
     sources = sorted(CSRC.glob("*.cu"))
@@ -85,6 +89,29 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB
 
 
+def _build_variant(extra: list, lib: Path, objdir: Path, verbose: bool) -> Path:
+    nvcc = nvcc_path()
+    objdir.mkdir(parents=True, exist_ok=True)
+    objs = []
+
+    def compile_one(src):
+        obj = objdir / f"{src.stem}.o"
+        r = subprocess.run([nvcc, *NVCC_FLAGS, *extra, "-I", str(CSRC), "-c", str(src), "-o", str(obj)],
+                           capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"nvcc failed for {src.name}:\n{r.stdout}\n{r.stderr}")
+        if verbose:
+            print(f"[build] {src.name} {' '.join(extra)}")
+        return obj
+
+    with ThreadPoolExecutor(max_workers=8) as ex:
+        objs = list(ex.map(compile_one, sorted(CSRC.glob("*.cu"))))
+    r = subprocess.run([nvcc, "-shared", "-o", str(lib), *map(str, objs), "-lcudart"], capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    return lib
+
+
 if __name__ == "__main__":
-    p = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
+    p = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, debug_bounds="--debug-bounds" in sys.argv)
     print(p)

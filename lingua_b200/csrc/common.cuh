@@ -23,6 +23,16 @@ enum : uint32_t {
   ST_BAD_ARG = 0x400u,
 };
 
+// Bounds-checked build (-DLB_DEBUG_BOUNDS, `python -m lingua_b200.build --debug-bounds`): indices that come out of
+// tables in memory (owner of a row block, destination row, block to pull) are validated before they are used to
+// form an address; a bad one is recorded in the status word (ST_BAD_ARG | site) and the access is skipped, so a
+// corrupted table shows up as a reported error instead of a stray store into a peer's memory.
+#ifdef LB_DEBUG_BOUNDS
+#define LB_CHECK_INDEX(cond, status, site) ((cond) ? true : ((status) ? (atomicOr((status), ST_BAD_ARG | (site)), false) : false))
+#else
+#define LB_CHECK_INDEX(cond, status, site) (true)
+#endif
+
 // Upper bound for any single wait, in nanoseconds of %globaltimer.
 #ifndef LB_WAIT_LIMIT_NS
 #define LB_WAIT_LIMIT_NS 2000000000ull

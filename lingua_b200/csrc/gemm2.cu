@@ -342,15 +342,17 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
         if (m0 < p.M) {
           const CUtensorMap* cmap = &tma_c;
           int drow = m0;
+          bool table_ok = true;
           if (p.scatter) {
             const int2 e = p.blocks[m0 / G2_ROWS];
-            cmap = &owners.m[e.x];
+            table_ok = LB_CHECK_INDEX(e.x >= 0 && e.x < LB_MAX_PEERS && e.y >= 0 && (e.y % 8) == 0, p.status, 0x41);
+            cmap = &owners.m[table_ok ? e.x : 0];
             drow = e.y;
           }
 #pragma unroll 1
           for (int c = 0; c < G2_BN / PC; ++c) {
             const int col0 = n0 + c * PC;
-            if (col0 >= p.N) break;  // uniform over the four warps
+            if (col0 >= p.N || !table_ok) break;  // uniform over the four warps
             const uint32_t buf = aux_base + (piece_iter & 1u) * G2_PIECE;
             if (issuer) tma_store_wait_read<1>();  // the store that last used this buffer has read it
             g2_epi_bar_sync();
@@ -464,7 +466,9 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
       return i < total ? (long long)i : -1ll;
     };
     auto locate = [&](long long piece, int& blk, int& owner, long long& off) {
-      const int2 e = p.g_blocks[piece / p.g_ppb];
+      int2 e = p.g_blocks[piece / p.g_ppb];
+      if (!LB_CHECK_INDEX(e.x >= 0 && e.x < p.n_blocks && e.y >= 0 && e.y < LB_MAX_PEERS && p.peer_b[e.y], p.status, 0x42))
+        e = make_int2(0, 0), abort_flag = 1;  // stop pulling: the producer's bounded wait reports the rest
       blk = e.x;
       owner = e.y;
       off = (long long)blk * block_bytes + (piece % p.g_ppb) * G2_COPY;

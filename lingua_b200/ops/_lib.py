@@ -12,7 +12,8 @@ from pathlib import Path
 
 import torch
 
-_LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "liblingua_b200.so"
+# LINGUA_B200_LIB: another build of the kernel library to load instead, e.g. the bounds-checked one
+_LIB_PATH = Path(os.environ.get("LINGUA_B200_LIB") or Path(__file__).resolve().parent.parent / "lib" / "liblingua_b200.so")
 _lib = None
 _status = {}
 

@@ -155,3 +155,29 @@ def maybe_run_profiler(dump_dir, module, config: ProfilerArgs):
         yield prof
     finally:
         prof.close()
+
+
+class nvtx_range:
+    """``with nvtx_range("forward"):`` marks a phase of the step for timeline tools (Nsight Systems, the PyTorch
+    profiler's NVTX view). A no-op without CUDA; costs about a microsecond per use with it."""
+
+    __slots__ = ("name", "on")
+
+    def __init__(self, name: str):
+        import torch
+
+        self.name, self.on = name, torch.cuda.is_available()
+
+    def __enter__(self):
+        if self.on:
+            import torch
+
+            torch.cuda.nvtx.range_push(self.name)
+        return self
+
+    def __exit__(self, *exc):
+        if self.on:
+            import torch
+
+            torch.cuda.nvtx.range_pop()
+        return False

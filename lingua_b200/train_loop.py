@@ -35,7 +35,7 @@ from .logger import init_logger
 from .metrics import GPUMemoryMonitor, LoggingArgs, MetricLogger, get_num_params, peak_flops
 from .ops import _lib as kernel_lib
 from .optim import LRScheduler, OptimArgs, build_engine_optim, build_lr_fn
-from .profiling import ProfilerArgs, maybe_run_profiler
+from .profiling import ProfilerArgs, maybe_run_profiler, nvtx_range
 from .tokenizer import build_tokenizer
 
 logger = logging.getLogger()
@@ -268,13 +268,16 @@ def run_training(args: TrainArgs, spec: ModelSpec) -> Dict[str, Any]:
             if train_state.acc_step == (1 % args.grad_acc_steps) or args.grad_acc_steps == 1:
                 engine.zero_grad()
             engine.defer_reduce = train_state.acc_step != 0  # reduce only after the last micro-batch
-            out = spec.loss_fn(model, input_ids, labels)
+            with nvtx_range("forward"):
+                out = spec.loss_fn(model, input_ids, labels)
             loss, extra_losses = out if isinstance(out, tuple) else (out, {})
-            (loss / args.grad_acc_steps if args.grad_acc_steps > 1 else loss).backward()
+            with nvtx_range("backward"):
+                (loss / args.grad_acc_steps if args.grad_acc_steps > 1 else loss).backward()
             loss = loss.detach() * 1.0
 
             if train_state.acc_step == 0:
-                grad_norm = engine.step(curr_lr)
+                with nvtx_range("optimizer"):
+                    grad_norm = engine.step(curr_lr)
                 scheduler.step()
                 train_state.step += 1
             if on_gpu:
