@@ -66,3 +66,60 @@ def build(model_kwargs: dict, n_gpus: int, lr: float, total_steps: int, compile_
         return loss.detach()
 
     return step_fn, {"compile": compile_model and tp == 1, "sac": sac}
+
+
+RECURRENT = {
+    "hawk_1b": ("apps.fastRNN.hawk.hawk", "LMHawk", "LMHawkArgs"),
+    "mingru_1b": ("apps.fastRNN.minGRU.mingru", "LMMinGRU", "LMMinGRUArgs"),
+    "minlstm_1b": ("apps.fastRNN.minLSTM.minlstm", "LMMinLSTM", "LMMinLSTMArgs"),
+}
+
+
+def build_recurrent(name: str, model_kwargs: dict, n_gpus: int, lr: float, total_steps: int, compile_model: bool,
+                    sac: bool):
+    """The reference's recurrent language models (apps/fastRNN) the way its own train script builds them
+    (apps/fastRNN/train.py:258-300): model on the meta device, ``parallelize_model`` with the default grouping plan,
+    ``init_weights``, ``build_optimizer``. Their third-party CUDA / Triton extensions (causal_conv1d, accelerated_scan)
+    cannot be built offline; ``baseline/shims`` restates exactly those calls in PyTorch ops, so this arm measures the
+    reference's model code on PyTorch-restated kernels."""
+    import importlib
+
+    for p in (str(HERE / "shims"), str(REF)):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    import torch
+    from lingua.distributed import DistributedArgs, get_device_mesh, parallelize_model
+    from lingua.optim import OptimArgs, build_optimizer
+    from torch.distributed._tensor import DTensor
+
+    mod_name, cls_name, args_name = RECURRENT[name]
+    mod = importlib.import_module(mod_name)
+    dist_args = DistributedArgs(dp_shard=n_gpus, dp_replicate=1, tp_size=1, fsdp_type="full_shard", model_dtype="bf16",
+                                compile=compile_model, selective_activation_checkpointing=sac)
+    mesh = get_device_mesh(dist_args)
+    margs = getattr(mod, args_name)(**model_kwargs)
+    torch.manual_seed(777)
+    with torch.device("meta"):
+        model = getattr(mod, cls_name)(margs)
+    model = parallelize_model(model, mesh, margs, dist_args, fsdp_grouping_plan=None, tp_parallelize=None,
+                              no_recompute_ops=model._get_no_recompute_ops())
+    model = model.to_empty(device="cuda")
+    with torch.random.fork_rng(devices=[torch.cuda.current_device()]):
+        torch.manual_seed(margs.seed)
+        model.init_weights()
+    oargs = OptimArgs(lr=lr, warmup=2000, clip=1.0)
+    optimizer, scheduler = build_optimizer(model, oargs, total_steps)
+
+    def step_fn(tokens):
+        input_ids, labels = tokens[:, :-1], tokens[:, 1:]
+        loss = model(input_ids, labels)
+        loss.backward()
+        grad_norm = torch.nn.utils.clip_grad_norm_(model.parameters(), max_norm=oargs.clip, foreach=True)
+        grad_norm = grad_norm.full_tensor() if isinstance(grad_norm, DTensor) else grad_norm
+        optimizer.step()
+        scheduler.step()
+        optimizer.zero_grad()
+        return loss.detach()
+
+    return step_fn, {"compile": compile_model, "sac": sac,
+                     "kernels": "causal_conv1d / accelerated_scan restated in PyTorch ops (baseline/shims)"}

@@ -1,0 +1,62 @@
+"""PyTorch restatement of the `causal_conv1d_cuda` extension for the reference arm of the benchmark.
+
+The reference's recurrent models call a CUDA extension that cannot be built offline. These functions keep its
+call signatures (as used by apps/mamba/component/causal_conv1d_compilable.py of the reference) and compute the
+same results with ordinary PyTorch ops, so that the reference's own model code can be timed as a baseline:
+depthwise causal convolution along the last dim of x [batch, channels, length] with weight [channels, width],
+optional bias, optional SiLU, and `seq_idx` [batch, length] document ids that the window must not cross.
+"""
+import torch
+import torch.nn.functional as F
+
+
+def _conv(x, weight, bias, seq_idx, activation):
+    B, C, L = x.shape
+    W = weight.shape[1]
+    xf = x.float()
+    if seq_idx is None:
+        out = F.conv1d(F.pad(xf, (W - 1, 0)), weight.float().unsqueeze(1), None if bias is None else bias.float(), groups=C)
+    else:
+        out = torch.zeros_like(xf)
+        for j in range(W):
+            shift = W - 1 - j
+            xs = F.pad(xf, (shift, 0))[..., :L]
+            ids = F.pad(seq_idx, (shift, 0), value=-1)[..., :L]
+            same = (ids == seq_idx).unsqueeze(1)
+            out = out + weight[:, j].float().view(1, C, 1) * torch.where(same, xs, torch.zeros_like(xs))
+        if bias is not None:
+            out = out + bias.float().view(1, C, 1)
+    if activation:
+        out = F.silu(out)
+    return out.to(x.dtype)
+
+
+def causal_conv1d_fwd(x, weight, bias, seq_idx, initial_states, final_states_out, activation):
+    assert initial_states is None and final_states_out is None
+    return _conv(x, weight, bias, seq_idx, activation)
+
+
+def causal_conv1d_bwd(x, weight, bias, dout, seq_idx, initial_states, dfinal_states, dx, return_dinitial_states,
+                      activation):
+    with torch.enable_grad():
+        xr = x.detach().requires_grad_(True)
+        wr = weight.detach().requires_grad_(True)
+        br = bias.detach().requires_grad_(True) if bias is not None else None
+        out = _conv(xr, wr, br, seq_idx, activation)
+        grads = torch.autograd.grad(out, [xr, wr] + ([br] if br is not None else []), dout)
+    dbias = grads[2] if br is not None else torch.empty((0,), device=x.device)
+    return grads[0], grads[1].to(weight.dtype), dbias, None
+
+
+def causal_conv1d_update(x, conv_state, weight, bias, activation, cache_seqlens):
+    """x [batch, channels, 1]; conv_state [batch, channels, state_len] shifted in place."""
+    assert cache_seqlens is None
+    W = weight.shape[1]
+    conv_state.copy_(torch.roll(conv_state, shifts=-1, dims=-1))
+    conv_state[:, :, -1] = x[:, :, 0]
+    out = (conv_state[:, :, -W:].float() * weight.float().unsqueeze(0)).sum(-1)
+    if bias is not None:
+        out = out + bias.float()
+    if activation:
+        out = F.silu(out)
+    return out.to(x.dtype).unsqueeze(-1)

@@ -205,10 +205,11 @@ def main() -> None:
         mcfg = dict(mcfg, n_layers=a.layers)
     B = BATCH[a.model]
     fpt = flops_per_token(mcfg) if not other else 0.0  # filled in from the parameter count below
-    if other and a.impl != "ours":
+    if other and a.impl != "ours" and a.model not in reference_arm.RECURRENT:
         if rank == 0:
             print(json.dumps({"impl": "reference", "n_gpus": a.gpus,
-                              "unavailable": "the reference's mamba_ssm / causal_conv1d / accelerated_scan kernels are not installable offline"}))
+                              "unavailable": "the reference's mamba_ssm kernels (Triton chunked SSD with hand-written "
+                                             "backward) are not installable offline and have no PyTorch restatement here"}))
         return
     dev = torch.device("cuda", local_rank)
     tp = a.tp
@@ -332,8 +333,12 @@ def main() -> None:
             errs = []
             for compile_model, sac in ((not a.ref_eager, False), (not a.ref_eager, True), (False, True)):
                 try:
-                    step_fn, extra = reference_arm.build(mcfg, world, 1e-3, 100000, compile_model and tp == 1, sac,
-                                                         tp=tp, float8=a.float8)
+                    if other:
+                        step_fn, extra = reference_arm.build_recurrent(a.model, mcfg, world, 1e-3, 100000,
+                                                                       compile_model, sac)
+                    else:
+                        step_fn, extra = reference_arm.build(mcfg, world, 1e-3, 100000, compile_model and tp == 1,
+                                                             sac, tp=tp, float8=a.float8)
                     step_fn(host[0].to(dev))  # first step: compilation and allocator growth
                     torch.cuda.synchronize()
                     break
