@@ -243,6 +243,9 @@ class ShardedEngine:
         self.is_cuda = self.device.type == "cuda"
         self.step_count = 0
         self.scatter_filter = scatter_filter or default_scatter_filter
+        if os.environ.get("LB_SCATTER_IN_GEMM", "1") == "0":
+            # every gradient is first written to a local fp32 buffer and its slices are pushed by the copy engines
+            self.scatter_filter = lambda fqn, p: False
         # gradient accumulation over micro-batches keeps every group's staging slots alive for the whole step
         self.accumulate = accumulate
         self.n_pool_areas = max(2, n_pool_areas)
