@@ -36,8 +36,11 @@ def test_engine_fused_gradient_scatter(world, grad_acc):
     worker = Path(__file__).with_name("engine_p2p_worker.py")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", "29654", str(worker)]
-    r = subprocess.run(cmd, env=dict(os.environ, LB_TEST_GRAD_ACC=str(grad_acc)), capture_output=True, text=True,
-                       timeout=600)
+    # accumulation runs push every parameter with the copy engines; the others also gather wq|wk|wv and w1|w3 inside
+    # their first forward GEMM
+    r = subprocess.run(cmd, env=dict(os.environ, LB_TEST_GRAD_ACC=str(grad_acc),
+                                     LB_GATHER_IN_GEMM="1" if grad_acc == 1 else "0"),
+                       capture_output=True, text=True, timeout=600)
     fails = [l for l in r.stdout.splitlines() if "ENGINE_P2P_FAIL" in l]
     assert r.returncode == 0 and "ENGINE_P2P_OK" in r.stdout, "\n".join(fails) + r.stdout[-1500:] + r.stderr[-1500:]
 
