@@ -144,9 +144,10 @@ class SSM(nn.Module):
                 # packed prefill: documents are scanned separately so that each final state is kept
                 y, states = _ssd_per_document(xs, dtp, A, B, C, self.D, self.chunk_size, cache.lengths, init)
                 cache.state_cache.copy_(states)
-            elif torch.is_grad_enabled() and xs.requires_grad:
-                # the decay / mask tensors of the chunked scan ([b, h, chunks, L, L] fp32) are rebuilt in
-                # backward instead of being kept for every layer: only x, dt, B, C stay alive
+            elif torch.is_grad_enabled() and xs.requires_grad and not (xs.is_cuda and xs.dtype == torch.bfloat16):
+                # PyTorch formulation (CPU, fp32): the decay / mask tensors of the chunked scan ([b, h, chunks, L, L]
+                # fp32) are rebuilt in backward instead of being kept for every layer. The native path keeps only
+                # bf16 operands of its GEMMs and needs no recomputation.
                 from torch.utils.checkpoint import checkpoint
 
                 y, _ = checkpoint(ssd_chunked, xs, dtp, A, B, C, self.D, self.chunk_size, doc_start, init,

@@ -174,6 +174,184 @@ def ssd_ref(x, dt, A, B, C, D=None, doc_start=None, initial_states=None):
     return y.to(x.dtype), state
 
 
+# ----------------------------------------------------------------------------- fused glue of the chunked scan
+def _lib_glue():
+    import ctypes as C
+
+    from . import _lib
+
+    lib = _lib.load()
+    if not getattr(lib, "_ssd_glue_declared", False):
+        vp, i, ll = C.c_void_p, C.c_int, C.c_longlong
+        lib.lb_ssd_prep_fwd.argtypes = [vp, ll, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, vp]
+        lib.lb_ssd_prep_bwd.argtypes = [vp, ll, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, vp]
+        lib.lb_ssd_carry_fwd.argtypes = [vp, vp, vp, vp, vp, i, i, i, ll, vp]
+        lib.lb_ssd_carry_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, i, i, i, ll, vp]
+        lib.lb_ssd_combine_fwd.argtypes = [vp, vp, vp, vp, vp, ll, vp, i, vp, i, i, i, i, i, i, i, vp]
+        lib.lb_ssd_combine_bwd.argtypes = [vp, vp, vp, vp, vp, ll, vp, i, vp, vp, vp, vp, vp, i, i, i, i, i, i, i, vp]
+        for name in ("prep_fwd", "prep_bwd", "carry_fwd", "carry_bwd", "combine_fwd", "combine_bwd"):
+            getattr(lib, "lb_ssd_" + name).restype = C.c_int
+        lib._ssd_glue_declared = True
+    return lib
+
+
+def _p(t):
+    return None if t is None else t.data_ptr()
+
+
+class SsdPrepFn(torch.autograd.Function):
+    """(x [b,s,h,p] bf16 with any token pitch, dt [b,s,h] fp32, A [h] fp32, doc int32 [b,nc,L] | None) ->
+    cs fp32 [b,h,nc,L], xdt = x dt and xw = xdt exp(cs_last - cs) (bf16, [b,s,h,p] contiguous). One kernel each way."""
+
+    @staticmethod
+    def forward(ctx, x, dt, A, doc, L):
+        from . import _lib
+
+        b, s, h, p = x.shape
+        nc = s // L
+        dt, A = dt.contiguous(), A.contiguous()
+        cs = torch.empty(b, h, nc, L, dtype=torch.float32, device=x.device)
+        xdt = torch.empty(b, s, h, p, dtype=torch.bfloat16, device=x.device)
+        xw = torch.empty_like(xdt)
+        _lib.check(_lib_glue().lb_ssd_prep_fwd(x.data_ptr(), x.stride(1), dt.data_ptr(), A.data_ptr(), _p(doc),
+                                               cs.data_ptr(), xdt.data_ptr(), xw.data_ptr(), b, s, h, p, nc, L,
+                                               _lib.stream_ptr()), "lb_ssd_prep_fwd")
+        ctx.save_for_backward(x, dt, A, doc, cs)
+        ctx.L = L
+        return cs, xdt, xw
+
+    @staticmethod
+    def backward(ctx, d_cs, d_xdt, d_xw):
+        from . import _lib
+
+        x, dt, A, doc, cs = ctx.saved_tensors
+        b, s, h, p = x.shape
+        L = ctx.L
+        d_cs = d_cs.contiguous() if d_cs is not None else None
+        d_xdt = d_xdt.contiguous() if d_xdt is not None else None
+        d_xw = d_xw.contiguous() if d_xw is not None else None
+        dx = torch.empty(b, s, h, p, dtype=torch.bfloat16, device=x.device)
+        ddt = torch.empty_like(dt)
+        dA = torch.zeros_like(A)
+        _lib.check(_lib_glue().lb_ssd_prep_bwd(x.data_ptr(), x.stride(1), dt.data_ptr(), A.data_ptr(), _p(doc),
+                                               cs.data_ptr(), _p(d_cs), _p(d_xdt), _p(d_xw), dx.data_ptr(),
+                                               ddt.data_ptr(), dA.data_ptr(), b, s, h, p, s // L, L,
+                                               _lib.stream_ptr()), "lb_ssd_prep_bwd")
+        return dx, ddt, dA, None, None
+
+
+class SsdCarryFn(torch.autograd.Function):
+    """State handed from chunk to chunk. T bf16 [b,nc,h,p,n] (state contributed by each chunk), a fp32 [b,h,nc]
+    (decay over the chunk, zero where the chunk starts a new document), init fp32 [b,h,p,n] | None ->
+    prev bf16 [b,nc,h,p,n] (state entering each chunk), final fp32 [b,h,p,n]."""
+
+    @staticmethod
+    def forward(ctx, T, a, init):
+        from . import _lib
+
+        b, nc, h, p, n = T.shape
+        T, a = T.contiguous(), a.contiguous()
+        init = init.float().contiguous() if init is not None else None
+        prev = torch.empty_like(T)
+        fin = torch.empty(b, h, p, n, dtype=torch.float32, device=T.device)
+        _lib.check(_lib_glue().lb_ssd_carry_fwd(T.data_ptr(), a.data_ptr(), _p(init), prev.data_ptr(), fin.data_ptr(),
+                                                b, h, nc, p * n, _lib.stream_ptr()), "lb_ssd_carry_fwd")
+        ctx.save_for_backward(prev, a)
+        ctx.has_init = init is not None
+        return prev, fin
+
+    @staticmethod
+    def backward(ctx, d_prev, d_fin):
+        from . import _lib
+
+        prev, a = ctx.saved_tensors
+        b, nc, h, p, n = prev.shape
+        d_prev = d_prev.contiguous() if d_prev is not None else None
+        d_fin = d_fin.float().contiguous() if d_fin is not None else None
+        dT = torch.empty_like(prev)
+        da = torch.zeros_like(a)
+        d_init = torch.empty(b, h, p, n, dtype=torch.float32, device=prev.device) if ctx.has_init else None
+        _lib.check(_lib_glue().lb_ssd_carry_bwd(prev.data_ptr(), a.data_ptr(), _p(d_prev), _p(d_fin), dT.data_ptr(),
+                                                da.data_ptr(), _p(d_init), b, h, nc, p * n, _lib.stream_ptr()),
+                   "lb_ssd_carry_bwd")
+        return dT, da, d_init
+
+
+class SsdCombineFn(torch.autograd.Function):
+    """y = y_diag + y_off exp(cs) (for tokens that continue the carried document) + D x, as bf16 [b,s,h,p].
+    y_diag bf16 [b,nc,h,L,p], y_off bf16 [b,nc,g,L,(h/g) p], cs fp32 [b,h,nc,L], x [b,s,h,p], D [h] | [h,p] | None."""
+
+    @staticmethod
+    def forward(ctx, y_diag, y_off, cs, doc, x, D):
+        from . import _lib
+
+        b, nc, h, L, p = y_diag.shape
+        g = y_off.shape[2]
+        y_diag, y_off = y_diag.contiguous(), y_off.contiguous()
+        Df = D.float().contiguous() if D is not None else None
+        y = torch.empty(b, nc * L, h, p, dtype=torch.bfloat16, device=x.device)
+        _lib.check(_lib_glue().lb_ssd_combine_fwd(y_diag.data_ptr(), y_off.data_ptr(), cs.data_ptr(), _p(doc),
+                                                  x.data_ptr(), x.stride(1), _p(Df), int(Df is not None and Df.dim() == 2),
+                                                  y.data_ptr(), b, nc * L, h, g, p, nc, L, _lib.stream_ptr()),
+                   "lb_ssd_combine_fwd")
+        ctx.save_for_backward(y_off, cs, doc, x, Df)
+        ctx.dims = (b, nc, h, L, p, g)
+        ctx.d_dtype = D.dtype if D is not None else None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from . import _lib
+
+        y_off, cs, doc, x, Df = ctx.saved_tensors
+        b, nc, h, L, p, g = ctx.dims
+        dy = dy.contiguous()
+        d_ydiag = torch.empty(b, nc, h, L, p, dtype=torch.bfloat16, device=dy.device)
+        d_yoff = torch.empty_like(y_off)
+        dcs = torch.empty_like(cs)
+        dx_d = torch.empty(b, nc * L, h, p, dtype=torch.bfloat16, device=dy.device) if Df is not None else None
+        dD = torch.zeros_like(Df) if Df is not None else None
+        _lib.check(_lib_glue().lb_ssd_combine_bwd(dy.data_ptr(), y_off.data_ptr(), cs.data_ptr(), _p(doc), x.data_ptr(),
+                                                  x.stride(1), _p(Df), int(Df is not None and Df.dim() == 2),
+                                                  d_ydiag.data_ptr(), d_yoff.data_ptr(), dcs.data_ptr(), _p(dx_d), _p(dD),
+                                                  b, nc * L, h, g, p, nc, L, _lib.stream_ptr()), "lb_ssd_combine_bwd")
+        return d_ydiag, d_yoff, dcs, None, dx_d, (dD.to(ctx.d_dtype) if dD is not None else None)
+
+
+def _glue_ok(x, dt, B, C, L) -> bool:
+    b, s, h, p = x.shape
+    return (_native(x) and _native(B) and _native(C) and dt.dtype == torch.float32 and s % L == 0 and L <= 1024
+            and p % 8 == 0 and p <= 256 and 32 % (p // 8) == 0 and (p * B.shape[3]) % 4 == 0
+            and x.stride(3) == 1 and x.stride(2) == p and x.stride(0) == s * x.stride(1) and x.stride(1) % 8 == 0)
+
+
+def _ssd_chunked_fused(x, dt, A, B, C, D, L, doc_start, initial_states):
+    """The chunked scan as four batched tcgen05 GEMMs, the decay kernel and the three glue kernels of
+    ``csrc/ssd_glue.cu``; every step has a hand-written backward, nothing else runs per token."""
+    b, s, h, p = x.shape
+    g, n = B.shape[2], B.shape[3]
+    rep, nc, hp = h // g, s // L, (h // g) * p
+    doc = doc_start.reshape(b, nc, L).int().contiguous() if doc_start is not None else None
+    cs, xdt, xw = SsdPrepFn.apply(x, dt, A.float(), doc, L)
+    Cg = C.view(b, nc, L, g, n).permute(0, 1, 3, 2, 4).reshape(b * nc, g, L, n)  # views: (b, nc) merge without a copy
+    Bg = B.view(b, nc, L, g, n).permute(0, 1, 3, 2, 4).reshape(b * nc, g, L, n)
+    scores = mm_views(Cg, Bg)  # [b*nc, g, L, L]
+    w = decay_weights(scores.view(b, nc, g, L, L), cs, doc)  # [b, nc, h, L, L]
+    xh = xdt.view(b, nc, L, h, p).permute(0, 1, 3, 4, 2).reshape(b * nc, h, p, L)
+    y_diag = mm_views(w.reshape(b * nc, h, L, L), xh)  # [b*nc, h, L, p]
+    xw_g = xw.view(b * nc, L, g, hp).permute(0, 2, 3, 1)  # [b*nc, g, M=hp, K=l]
+    Bt = B.reshape(b * nc, L, g, n).permute(0, 2, 3, 1)  # [b*nc, g, N=n, K=l]
+    T = mm_views(xw_g, Bt).reshape(b, nc, h, p, n)
+    a = torch.exp(cs[..., -1])  # b h c: decay over a whole chunk
+    if doc is not None:
+        prev_last = torch.cat([torch.full_like(doc[:, :1, -1], -1), doc[:, :-1, -1]], dim=1)
+        a = a * (doc[:, :, -1] == prev_last).unsqueeze(1)
+    prev, final = SsdCarryFn.apply(T, a, initial_states)
+    y_off = mm_views(Cg, prev.view(b * nc, g, hp, n))  # [b*nc, g, L, hp]
+    y = SsdCombineFn.apply(y_diag.view(b, nc, h, L, p), y_off.view(b, nc, g, L, hp), cs, doc, x, D)
+    return y, final
+
+
 def ssd_chunked(x, dt, A, B, C, D=None, chunk: int = 256, doc_start: Optional[torch.Tensor] = None,
                 initial_states: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """Returns (y [b,s,h,p], final state [b,h,p,n] fp32). ``dt`` is already positive (softplus applied)."""
@@ -194,6 +372,10 @@ def ssd_chunked(x, dt, A, B, C, D=None, chunk: int = 256, doc_start: Optional[to
     sp = s + pad
     nc = sp // L
     cdt = x.dtype
+    if _glue_ok(x, dt, B, C, L) and L % 8 == 0 and L <= 512:
+        y, state = _ssd_chunked_fused(x, dt, A, B.contiguous() if not B.is_contiguous() else B,
+                                      C.contiguous() if not C.is_contiguous() else C, D, L, doc_start, initial_states)
+        return y[:, :s], state
     dtf = dt.float()
     dA = (dtf * A.float().view(1, 1, h)).view(b, nc, L, h).permute(0, 3, 1, 2)  # b h c l
     cs = torch.cumsum(dA, dim=-1)
