@@ -92,6 +92,7 @@ def build_recurrent(name: str, model_kwargs: dict, n_gpus: int, lr: float, total
     from lingua.optim import OptimArgs, build_optimizer
     from torch.distributed._tensor import DTensor
 
+    torch.set_grad_enabled(True)  # a failed traced attempt can leave gradient recording switched off
     mod_name, cls_name, args_name = RECURRENT[name]
     mod = importlib.import_module(mod_name)
     dist_args = DistributedArgs(dp_shard=n_gpus, dp_replicate=1, tp_size=1, fsdp_type="full_shard", model_dtype="bf16",

@@ -10,7 +10,7 @@ import torch
 import torch.nn.functional as F
 
 
-def _conv(x, weight, bias, seq_idx, activation):
+def _conv_math(x, weight, bias, seq_idx, activation):
     B, C, L = x.shape
     W = weight.shape[1]
     xf = x.float()
@@ -28,7 +28,16 @@ def _conv(x, weight, bias, seq_idx, activation):
             out = out + bias.float().view(1, C, 1)
     if activation:
         out = F.silu(out)
-    return out.to(x.dtype)
+    return out
+
+
+def _conv(x, weight, bias, seq_idx, activation):
+    out = _conv_math(x, weight, bias, seq_idx, activation)
+    # same memory layout as the input (the extension writes channel-last outputs for channel-last inputs, and the
+    # reference's traced graph relies on it)
+    res = torch.empty_like(x)
+    res.copy_(out)
+    return res
 
 
 def causal_conv1d_fwd(x, weight, bias, seq_idx, initial_states, final_states_out, activation):
@@ -42,10 +51,12 @@ def causal_conv1d_bwd(x, weight, bias, dout, seq_idx, initial_states, dfinal_sta
         xr = x.detach().requires_grad_(True)
         wr = weight.detach().requires_grad_(True)
         br = bias.detach().requires_grad_(True) if bias is not None else None
-        out = _conv(xr, wr, br, seq_idx, activation)
-        grads = torch.autograd.grad(out, [xr, wr] + ([br] if br is not None else []), dout)
+        out = _conv_math(xr, wr, br, seq_idx, activation)
+        grads = torch.autograd.grad(out, [xr, wr] + ([br] if br is not None else []), dout.float())
     dbias = grads[2] if br is not None else torch.empty((0,), device=x.device)
-    return grads[0], grads[1].to(weight.dtype), dbias, None
+    dx = torch.empty_like(x)
+    dx.copy_(grads[0])
+    return dx, grads[1].to(weight.dtype), dbias, None
 
 
 def causal_conv1d_update(x, conv_state, weight, bias, activation, cache_seqlens):
