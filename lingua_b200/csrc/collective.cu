@@ -283,6 +283,24 @@ extern "C" int lb_reduce_peers(const void* const* srcs, int n_src, float* out, l
   return e == cudaSuccess ? 0 : 400 + (int)e;
 }
 
+// dst[i] += src[i] with fp32 reductions that are atomic at the destination (dst may be a peer's memory: several
+// ranks add into the same shard at the same time).
+namespace lb {
+__global__ void __launch_bounds__(256) red_add_kernel(float* __restrict__ dst, const float* __restrict__ src, long long n) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst + i), "f"(src[i]) : "memory");
+}
+}  // namespace lb
+extern "C" int lb_red_add(float* dst, const float* src, long long n, void* stream) {
+  if (!dst || !src || n <= 0) return 1;
+  long long blocks = (n + 255) / 256;
+  if (blocks > (long long)lb::num_sms() * 4) blocks = (long long)lb::num_sms() * 4;
+  lb::red_add_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(dst, src, n);
+  lb::g_launches.fetch_add(1, std::memory_order_relaxed);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 400 + (int)e;
+}
+
 // max_blocks > 0 caps the grid: a reduction that runs beside the backward GEMMs has a whole layer's time to finish and
 // should trickle (few blocks, little pressure on the SMs and on L2) rather than burst; 0 = LB_REDUCE_BLOCKS or 8 per SM.
 extern "C" int lb_reduce_slots_grid(const float* own, const float* slots, int n_slots, long long slot_stride, float* out,

@@ -193,6 +193,9 @@ int lb_reduce_slots(const float* own, const float* slots, int n_slots, long long
 int lb_reduce_slots_grid(const float* own, const float* slots, int n_slots, long long slot_stride, float* out,
                          long long n, float scale, float* sumsq, int max_blocks, void* stream);
 
+// dst[i] += src[i] (fp32, n elements) with reductions that are atomic at the destination, which may be peer memory.
+int lb_red_add(float* dst, const float* src, long long n, void* stream);
+
 // out[i] = scale * sum_r srcs[r][i], *sumsq += sum out[i]^2 (fp32, n elements, n_src <= LB_MAX_PEERS): a
 // reduce-scatter without staging. srcs[r] is this rank's slice inside rank r's buffer (peer-visible addresses,
 // read with plain loads); order the ranks with lb_peer_barrier before (sources final) and after (readers done).

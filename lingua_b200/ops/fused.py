@@ -124,6 +124,8 @@ def _emit_scatter(ws: Sequence[torch.Tensor], dy2d: torch.Tensor, x2d: torch.Ten
     written = [getattr(w, "grad_written", False) for w in ws]
     if not dy2d.is_cuda:
         return False
+    if engine.grad_mode == "atomic":
+        written = [True] * len(ws)  # every contribution is added into the owner's shard (which starts at zero)
     plan = engine.scatter_plan(targets) if (all(written) or not any(written)) else None
     if plan is not None:
         blocks, ptrs, rows, K, m_rot = plan

@@ -250,6 +250,13 @@ class ShardedEngine:
         self.accumulate = accumulate
         self.n_pool_areas = max(2, n_pool_areas)
         self.reduce_blocks = int(os.environ.get("LB_REDUCE_TRICKLE_BLOCKS", "64"))
+        # How the weight-gradient blocks of the ranks are combined at their owner: "slots" - every source rank stores
+        # into a slot of its own and one kernel sums the slots in a fixed order (bitwise repeatable); "atomic" - every
+        # rank's epilogue adds straight into the owner's gradient shard with TMA reductions (fp32 adds that are atomic
+        # at the destination): no staging memory and no slot-sum traffic, but the order of the additions, and with it
+        # the last bits of the result, varies from run to run.
+        self.grad_mode = os.environ.get("LB_GRAD_REDUCE", "slots")
+        assert self.grad_mode in ("slots", "atomic")
         # Which groups leave the all-gather of their first-use weights to the consuming GEMM: those the grouping plan
         # marks ``reshard_after_forward`` (their weights are fetched on demand), all with LB_GATHER_IN_GEMM=1, none
         # with =0. Groups whose weights stay gathered for the whole step (the main app's plan for its blocks) get
@@ -311,7 +318,7 @@ class ShardedEngine:
         rest = [(n, p) for n, p in model.named_parameters() if n not in taken]
         if rest:
             self._add_group("", rest, gather_on_demand=self.gather_all_groups)
-        if self._symm is not None:
+        if self._symm is not None and self.grad_mode == "slots":
             self._setup_areas()
         # squared gradient norm per group, split into [tensor-parallel sharded, replicated inside a TP group]
         self.sumsq = torch.zeros(1, dtype=torch.float32, device=self.device)
@@ -355,6 +362,10 @@ class ShardedEngine:
         if self._symm is not None:
             g.peer_full = [holder["h"].get_buffer(r, (g.padded,), self.compute_dtype) for r in range(W)]
             g.full_ptrs = [int(p) for p in holder["h"].buffer_ptrs]
+            if self.grad_mode == "atomic" and g.mat_cap:
+                g.grad_shard, hg = self._symm_tensor(g.shard_cap, torch.float32)
+                g.grad_shard_ptrs = [int(p) for p in hg.buffer_ptrs]
+                g.peer_grad_shard = [hg.get_buffer(r, (g.shard_cap,), torch.float32) for r in range(W)]
             if g.plain_shard:
                 g.plain_grad = torch.zeros(g.plain_padded, dtype=torch.float32, device=self.device)
                 g.plain_stage, h2 = self._symm_tensor((W - 1) * g.plain_shard, torch.float32)
@@ -596,6 +607,9 @@ class ShardedEngine:
             cached = (blocks, rows, K, first_blk // 2)
             g._tables[key] = cached
         blocks, rows, K, m_rot = cached
+        if self.grad_mode == "atomic":
+            g.area_active = -1  # marks the group as having contributions in flight
+            return blocks, [p + g.mat_shard_off[o][idx[0]] * 4 for o, p in enumerate(g.grad_shard_ptrs)], rows, K, m_rot
         a = self._acquire_area(g)
         cap = self._area_cap[a]
         ptrs = []
@@ -612,9 +626,25 @@ class ShardedEngine:
         """A scatter parameter whose gradient did not come out of the fused GEMM (plain autograd, or no gradient at
         all): deliver its row slabs with device-to-device copies so that every slot holds defined data."""
         fqn, p = g.params[i]
-        a = self._acquire_area(g)
         K = p.shape[1]
         gf = None if grad is None else grad.to(torch.float32).contiguous()
+        if self.grad_mode == "atomic":
+            g.area_active = -1
+            if gf is not None:  # nothing to deliver for a parameter without a gradient: the shards start at zero
+                from ..ops import _lib
+
+                lib = _lib.load()
+                import ctypes as C
+
+                lib.lb_red_add.argtypes = [C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p]
+                lib.lb_red_add.restype = C.c_int
+                for o in range(self.world):
+                    r0, r1 = g.bounds[i][o], g.bounds[i][o + 1]
+                    if r1 > r0:
+                        dst = g.grad_shard_ptrs[o] + g.mat_shard_off[o][i] * 4
+                        _lib.check(lib.lb_red_add(dst, gf[r0:r1].data_ptr(), (r1 - r0) * K, _lib.stream_ptr()), "lb_red_add")
+            return
+        a = self._acquire_area(g)
         for o in range(self.world):
             r0, r1 = g.bounds[i][o], g.bounds[i][o + 1]
             n = (r1 - r0) * K
@@ -688,7 +718,16 @@ class ShardedEngine:
                     # groups that are followed by more backward work have a layer's time for their slot sum: a small
                     # grid keeps it from competing with the GEMMs; the last ones are on the critical path
                     trickle = self.reduce_blocks if gi >= 2 else 0
-                    if g.area_active is not None:
+                    if g.area_active is not None and self.grad_mode == "atomic":
+                        # every rank's additions into this shard have landed (barrier): scale and take the norm
+                        n = g.mat_numel[self.rank]
+                        cls = self._uniform_class(g, 0, g.n_mats) if fused_norm else None
+                        if n:
+                            self._reduce_slots(g.grad_shard[:n], None, 0, g.grad_shard[:n],
+                                               None if cls is None else parts[cls:cls + 1], trickle, n_slots=0)
+                        fused_norm = fused_norm and cls is not None
+                        g.area_active = None
+                    elif g.area_active is not None:
                         if g.area is None:
                             self._use_barrier[g.area_use] = self._barrier_epoch
                         n = g.mat_numel[self.rank]
@@ -770,6 +809,9 @@ class ShardedEngine:
                              g.full[fo:fo + n], step=self.step_count, lr=lr, beta1=o.beta1, beta2=o.beta2, eps=o.eps,
                              wd=o.weight_decay, sumsq_t=self.sumsq, max_norm=o.clip, grad_mul=grad_mul)
             if self.world > 1:
+                if self.grad_mode == "atomic" and self.p2p and g.mat_cap:
+                    # the shard starts the next step at zero; the barrier of the gather below tells every peer so
+                    g.grad_shard[:g.mat_numel[self.rank]].zero_()
                 self._gather_group(g)  # overlaps the AdamW launches of the groups that follow
         return self.sumsq.sqrt() * grad_mul
 
@@ -813,8 +855,8 @@ class ShardedEngine:
             if r != self.rank:
                 g.unshard_into(g.full, gathered[r * g.shard_cap:(r + 1) * g.shard_cap], r)
 
-    def _reduce_slots(self, own: torch.Tensor, slots: torch.Tensor, slot_stride: int, out: torch.Tensor,
-                      part: Optional[torch.Tensor], max_blocks: int = 0) -> None:
+    def _reduce_slots(self, own: torch.Tensor, slots: Optional[torch.Tensor], slot_stride: int, out: torch.Tensor,
+                      part: Optional[torch.Tensor], max_blocks: int = 0, n_slots: Optional[int] = None) -> None:
         import ctypes as C
 
         from ..ops import _lib
@@ -825,7 +867,8 @@ class ShardedEngine:
                                                  C.c_longlong, C.c_float, C.c_void_p, C.c_int, C.c_void_p]
             lib.lb_reduce_slots_grid.restype = C.c_int
             lib._reduce_slots_declared = True
-        rc = lib.lb_reduce_slots_grid(own.data_ptr(), slots.data_ptr(), self.world - 1, slot_stride, out.data_ptr(),
+        rc = lib.lb_reduce_slots_grid(own.data_ptr(), None if slots is None else slots.data_ptr(),
+                                      self.world - 1 if n_slots is None else n_slots, slot_stride, out.data_ptr(),
                                       own.numel(), 1.0 / self.world, None if part is None else part.data_ptr(),
                                       max_blocks, _lib.stream_ptr())
         _lib.check(rc, "lb_reduce_slots")

@@ -118,11 +118,17 @@ def main():
     n1, m1 = run_mlp(True, rank, world, dev)
     n2, m2 = run_mlp(True, rank, world, dev)
     _check(torch.allclose(n1, n2, rtol=1e-5), "norms of the repeated linear-only run", n1, n2)
-    bad = [i for i, (a, b) in enumerate(zip(m1, m2)) if not torch.equal(a, b)]
-    _check(not bad, "bitwise repeat of the linear-only run", bad,
-           [float((m1[i] - m2[i]).abs().max()) for i in bad])
+    atomic = os.environ.get("LB_GRAD_REDUCE", "slots") == "atomic"
+    if atomic:
+        # additions into the owner's shard arrive in any order: repeatable to rounding only
+        rel = [float((a - b).abs().mean() / b.abs().mean()) for a, b in zip(m1, m2)]
+        _check(max(rel) < 1e-3, "repeat of the linear-only run (atomic mode)", rel)
+    else:
+        bad = [i for i, (a, b) in enumerate(zip(m1, m2)) if not torch.equal(a, b)]
+        _check(not bad, "bitwise repeat of the linear-only run", bad,
+               [float((m1[i] - m2[i]).abs().max()) for i in bad])
     n3, m3 = run_mlp(False, rank, world, dev)
-    if world == 2:
+    if world == 2 and not atomic:
         bad = [i for i, (a, b) in enumerate(zip(m1, m3)) if not torch.equal(a, b)]
         _check(not bad, "bitwise agreement with the NCCL path at two ranks", bad)
         _check(torch.allclose(n1, n3, rtol=1e-5), "norms against the NCCL path", n1, n3)
