@@ -157,17 +157,56 @@ def scaled_mm(a8: torch.Tensor, sa: torch.Tensor, b8: torch.Tensor, sb: torch.Te
 
 
 # ------------------------------------------------------------------ the three products of a linear layer
+# Quantised weights of the current optimiser step: {(address, shape): (epoch, version, weight, e4m3 rows, row scales)}. The forward product of
+# a step quantises a weight row-wise once; further products of the same step with the same weight (gradient
+# accumulation) reuse the result, and the input-gradient product takes its single tensor scale as the maximum of
+# the row scales instead of a separate pass over the weight. ``new_weight_epoch`` (called by the training engine
+# after every optimiser step and after loading weights) invalidates everything.
+_WEIGHT_EPOCH = 0
+_WEIGHT_CACHE = {}
+
+
+def new_weight_epoch() -> None:
+    global _WEIGHT_EPOCH
+    _WEIGHT_EPOCH += 1
+    _WEIGHT_CACHE.clear()
+
+
+def _cached_weight(w: torch.Tensor):
+    """Cache entry of ``w`` if it is still valid: same optimiser-step epoch (the engine's AdamW writes through raw
+    pointers) and same tensor version (in-place PyTorch updates). The entry keeps ``w`` alive, so its address cannot
+    be handed to another tensor while the entry exists."""
+    hit = _WEIGHT_CACHE.get((w.data_ptr(), tuple(w.shape)))
+    if hit is not None and hit[0] == _WEIGHT_EPOCH and hit[1] == w._version:
+        return hit
+    return None
+
+
+def _quant_weight_rows(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    hit = _cached_weight(w)
+    if hit is not None:
+        return hit[3], hit[4]
+    w8, sw = quant_rows(w)
+    if w.is_cuda:
+        _WEIGHT_CACHE[(w.data_ptr(), tuple(w.shape))] = (_WEIGHT_EPOCH, w._version, w, w8, sw)
+    return w8, sw
+
+
 def fp8_forward_mm(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """x [M, K] @ w[N, K]^T with row-wise scales on both operands."""
     x8, sx = quant_rows(x)
-    w8, sw = quant_rows(w)
+    w8, sw = _quant_weight_rows(w)
     return scaled_mm(x8, sx, w8, sw, x.dtype if x.dtype != torch.float32 else torch.float32)
 
 
 def fp8_dgrad_mm(dy: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """dy [M, N] @ w [N, K]: row-wise scales for dy, one scale for the weight."""
     dy8, sdy = quant_rows(dy, _GRAD_FORMAT)
-    sw = (w.detach().abs().amax().float().clamp(min=EPS) / E4M3_MAX).reshape(1)
+    hit = _cached_weight(w)
+    if hit is not None:
+        sw = hit[4].max().reshape(1)  # max_r(amax_r / 448) = amax / 448: the row scales already hold the answer
+    else:
+        sw = (w.detach().abs().amax().float().clamp(min=EPS) / E4M3_MAX).reshape(1)
     wt8 = quant_transpose(w, sw)
     return scaled_mm(dy8, sdy, wt8, sw, dy.dtype if dy.dtype != torch.float32 else torch.float32)
 

@@ -512,6 +512,9 @@ class ShardedEngine:
         g.shard_of(flat, out=getattr(g, which))
         if which == "master":
             g.full.copy_(flat)
+            from .. import float8
+
+            float8.new_weight_epoch()
 
     def export_group_fp32(self, gi: int, which: str = "master") -> torch.Tensor:
         """The whole group's fp32 tensor in parameter order, assembled from every rank's shard."""
@@ -802,6 +805,9 @@ class ShardedEngine:
         if self.world > 1:
             dist.all_reduce(self.sumsq, op=dist.ReduceOp.SUM, group=self.pg)
         self.step_count += 1
+        from .. import float8
+
+        float8.new_weight_epoch()  # quantised copies of the weights are stale from here on
         o = self.optim
         for g in self.groups:
             for fo, n, so in g.my_segments:
