@@ -72,7 +72,28 @@ struct Gemm2Params {
   uint8_t* local_b;
   uint32_t* flags;                     // [blocks of N] pieces landed, then the piece counter
   int n_blocks;
+  // grouped products (lb_gemm_grouped): mode 1 = the B matrix of a row tile is chosen by grp_sel[row tile];
+  // mode 2 = batch g contracts over the K range (grp_sel[2g], 64 * grp_sel[2g + 1]) of unbatched A and B
+  int grp_mode, grp_n;
+  const int* grp_sel;
 };
+
+// group of a row tile (mode 1), always checked: a bad entry is reported and replaced by group 0
+__device__ __forceinline__ int g2_row_group(const Gemm2Params& p, int mt) {
+  const int g = __ldg(p.grp_sel + mt);
+  if (g >= 0 && g < p.grp_n) return g;
+  if (p.status) atomicOr(p.status, ST_BAD_ARG | 0x43);
+  return 0;
+}
+// (first k, number of 64-wide k blocks) of batch g (mode 2), clamped to the operands' K extent
+__device__ __forceinline__ int2 g2_k_range(const Gemm2Params& p, int g) {
+  int2 r = make_int2(__ldg(p.grp_sel + 2 * g), __ldg(p.grp_sel + 2 * g + 1));
+  if (r.x < 0 || r.y < 0 || (long long)r.x + 64ll * r.y > (long long)((p.K + 63) / 64) * 64) {
+    if (p.status) atomicOr(p.status, ST_BAD_ARG | 0x44);
+    r = make_int2(0, 0);
+  }
+  return r;
+}
 
 // tile index inside one batch -> (row tile, column tile)
 __device__ __forceinline__ void g2_tile_coords(int t, const Gemm2Params& p, int& mt, int& nt) {
@@ -234,6 +255,15 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
         const int m0 = mt * G2_BM + rank * G2_ROWS;
         const int n0 = nt * G2_BN + rank * G2_ROWS;
         const int b0 = batch % p.nb0, b1 = batch / p.nb0;
+        int ab0 = b0, bb0 = b0, k_first = 0, kb_n = num_kb;
+        if (p.grp_mode == 1) {
+          bb0 = g2_row_group(p, mt);
+        } else if (p.grp_mode == 2) {
+          const int2 kr = g2_k_range(p, b0);
+          ab0 = bb0 = 0;
+          k_first = kr.x;
+          kb_n = kr.y;
+        }
         if (GATHER && p.g_n_remote > 0) {
           // this CTA's half of the B tile is one 128-row block of the weight: if another rank owns it, its pieces
           // must have landed in the local copy (written by bulk copies of any CTA's gather warp)
@@ -244,7 +274,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
             fence_proxy_async_all();
           }
         }
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = 0; kb < kb_n; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
           ok = mbar_wait(empty_bar(s), ph ^ 1u, &abort_flag, p.status, 0x31);
@@ -253,20 +283,20 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
           const uint32_t lead_full = mapa(full_bar(s), 0);
           const uint32_t sa = smem_base + s * G2_STAGE_BYTES;
           const uint32_t sb = sa + G2_A_BYTES;
-          const int k0 = kb * BK_ELEMS;
+          const int k0 = k_first + kb * BK_ELEMS;
           if (AMAJ == 0) {
-            tma_load_4d_pair(sa, &tma_a, lead_full, k0, m0, b0, b1);
+            tma_load_4d_pair(sa, &tma_a, lead_full, k0, m0, ab0, b1);
           } else {
 #pragma unroll
             for (int c = 0; c < 2; ++c)
-              tma_load_4d_pair(sa + c * (G2_BK * 128), &tma_a, lead_full, m0 + c * 64, k0, b0, b1);
+              tma_load_4d_pair(sa + c * (G2_BK * 128), &tma_a, lead_full, m0 + c * 64, k0, ab0, b1);
           }
           if (BMAJ == 0) {
-            tma_load_4d_pair(sb, &tma_b, lead_full, k0, n0, b0, b1);
+            tma_load_4d_pair(sb, &tma_b, lead_full, k0, n0, bb0, b1);
           } else {
 #pragma unroll
             for (int c = 0; c < 2; ++c)
-              tma_load_4d_pair(sb + c * (G2_BK * 128), &tma_b, lead_full, n0 + c * 64, k0, b0, b1);
+              tma_load_4d_pair(sb + c * (G2_BK * 128), &tma_b, lead_full, n0 + c * 64, k0, bb0, b1);
           }
         }
       }
@@ -287,7 +317,9 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
         if (!ok) break;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * G2_BN;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        int kb_n = num_kb;
+        if (p.grp_mode == 2) kb_n = g2_k_range(p, (tile / tiles_per_batch) % p.nb0).y;
+        for (int kb = 0; kb < kb_n; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
           ok = mbar_wait(full_bar(s), ph, &abort_flag, p.status, 0x33);
@@ -329,6 +361,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
       const int m0 = mt * G2_BM + rank * G2_ROWS;
       const int n0 = nt * G2_BN;
       const int b0 = batch % p.nb0, b1 = batch / p.nb0;
+      // a group without rows issued no product: its accumulator holds whatever the previous tile left
+      const bool empty = p.grp_mode == 2 && g2_k_range(p, b0).y == 0;
       if (!mbar_wait(tfull_bar(acc), acc_ph, &abort_flag, p.status, 0x34)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * G2_BN + (static_cast<uint32_t>(quarter * 32) << 16);
@@ -362,6 +396,10 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
               uint32_t r[32];
               tmem_ld32(taddr + c * 32, r);
               tmem_wait_ld();
+              if (empty) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) r[i] = 0u;
+              }
 #pragma unroll
               for (int g = 0; g < 8; ++g) {
                 const uint32_t dst = rowbase + ((static_cast<uint32_t>(g) ^ sw) << 4);
@@ -379,6 +417,10 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
                 uint32_t r[32];
                 tmem_ld32(taddr + c * 64 + h * 32, r);
                 tmem_wait_ld();
+                if (empty) {
+#pragma unroll
+                  for (int i = 0; i < 32; ++i) r[i] = 0u;
+                }
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
                   const uint32_t dst = rowbase + ((static_cast<uint32_t>(h * 4 + g) ^ sw) << 4);
@@ -414,6 +456,10 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
           uint32_t r[32];
           tmem_ld32(taddr + c * 32, r);
           tmem_wait_ld();
+          if (empty) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = 0u;
+          }
           if (row < p.M) {
             if (sizeof(OutT) == 2) {
 #pragma unroll
@@ -536,24 +582,41 @@ struct F8Extra {
 };
 
 template <int AMAJ, int BMAJ, typename OutT, bool GATHER = false, bool F8 = false>
-static int launch_gemm2(const LbGemmArgs& a, const LbScatterArgs* sc, cudaStream_t stream,
-                        const LbGatherArgs* ga = nullptr, const F8Extra* f8 = nullptr) {
+static int launch_gemm2(const LbGemmArgs& a_in, const LbScatterArgs* sc, cudaStream_t stream,
+                        const LbGatherArgs* ga = nullptr, const F8Extra* f8 = nullptr,
+                        const LbGroupArgs* gr = nullptr) {
   CUtensorMap ta, tb, tc;
   OwnerMaps owners;
   int rc;
   constexpr int IN_ESZ = F8 ? 1 : 2;
   constexpr int BK_IN = 128 / IN_ESZ;
+  LbGemmArgs a = a_in;
+  // batch extents of the operands' maps: a grouped product batches only B (mode 1) or only C (mode 2)
+  int a_nb0 = a.nb0, b_nb0 = a.nb0;
+  long long a_bs0 = a.a_bs0, b_bs0 = a.b_bs0;
+  if (gr && gr->mode == 1) {
+    b_nb0 = gr->n_groups;
+    b_bs0 = gr->group_stride;
+  } else if (gr && gr->mode == 2) {
+    a.nb0 = gr->n_groups;
+    a.c_bs0 = gr->group_stride;
+    a_nb0 = b_nb0 = 1;
+    a_bs0 = b_bs0 = 0;
+  }
   if (AMAJ == 0)
-    rc = make_tmap_4d(&ta, a.A, IN_ESZ, a.K, a.M, a.lda, a.nb0, a.a_bs0, a.nb1, a.a_bs1, BK_IN, G2_ROWS);
+    rc = make_tmap_4d(&ta, a.A, IN_ESZ, a.K, a.M, a.lda, a_nb0, a_bs0, a.nb1, a.a_bs1, BK_IN, G2_ROWS);
   else
-    rc = make_tmap_4d(&ta, a.A, 2, a.M, a.K, a.lda, a.nb0, a.a_bs0, a.nb1, a.a_bs1, 64, G2_BK);
+    rc = make_tmap_4d(&ta, a.A, 2, a.M, a.K, a.lda, a_nb0, a_bs0, a.nb1, a.a_bs1, 64, G2_BK);
   if (rc) return 100 + rc;
   if (BMAJ == 0)
-    rc = make_tmap_4d(&tb, a.B, IN_ESZ, a.K, a.N, a.ldb, a.nb0, a.b_bs0, a.nb1, a.b_bs1, BK_IN, G2_ROWS);
+    rc = make_tmap_4d(&tb, a.B, IN_ESZ, a.K, a.N, a.ldb, b_nb0, b_bs0, a.nb1, a.b_bs1, BK_IN, G2_ROWS);
   else
-    rc = make_tmap_4d(&tb, a.B, 2, a.N, a.K, a.ldb, a.nb0, a.b_bs0, a.nb1, a.b_bs1, 64, G2_BK);
+    rc = make_tmap_4d(&tb, a.B, 2, a.N, a.K, a.ldb, b_nb0, b_bs0, a.nb1, a.b_bs1, 64, G2_BK);
   if (rc) return 200 + rc;
   Gemm2Params p;
+  p.grp_mode = gr ? gr->mode : 0;
+  p.grp_n = gr ? gr->n_groups : 0;
+  p.grp_sel = gr ? gr->sel : nullptr;
   p.row_scale = f8 ? f8->row_scale : nullptr;
   p.col_scale = f8 ? f8->col_scale : nullptr;
   p.idesc_f8 = f8 ? make_idesc(G2_BM, G2_BN, (uint32_t)f8->a_fmt, (uint32_t)f8->b_fmt, 0, 0) : 0u;
@@ -679,6 +742,26 @@ extern "C" int lb_gemm_scatter(const LbGemmArgs* args, const LbScatterArgs* sc, 
   if ((a.ldc % 4) || (a.lda % 8) || (a.ldb % 8) || a.ldc < a.N || (a.N % 4)) return 3;
   if (sc->world < 1 || sc->world > LB_MAX_PEERS || !sc->blocks) return 4;
   return dispatch2<float>(a, sc, reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int lb_gemm_grouped(const LbGemmArgs* args, const LbGroupArgs* gr, void* stream) {
+  using namespace lb;
+  if (!args || !gr || !gr->sel) return 1;
+  const LbGemmArgs& a = *args;
+  if (a.M <= 0 || a.N <= 0 || a.K <= 0 || a.nb0 != 1 || a.nb1 != 1) return 1;
+  if (a.in_dtype != LB_BF16) return 2;
+  if ((a.lda % 8) || (a.ldb % 8) || gr->n_groups < 1 || gr->group_stride % 8) return 3;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (gr->mode == 1) {
+    if (a.a_major != 0 || a.out_dtype != LB_BF16 || a.accumulate) return 4;
+    return a.b_major == 0 ? launch_gemm2<0, 0, __nv_bfloat16>(a, nullptr, s, nullptr, nullptr, gr)
+                          : launch_gemm2<0, 1, __nv_bfloat16>(a, nullptr, s, nullptr, nullptr, gr);
+  }
+  if (gr->mode == 2) {
+    if (a.a_major != 1 || a.b_major != 1 || a.out_dtype != LB_F32 || (a.ldc % 4)) return 5;
+    return launch_gemm2<1, 1, float>(a, nullptr, s, nullptr, nullptr, gr);
+  }
+  return 6;
 }
 
 extern "C" int lb_gemm_gather(const LbGemmArgs* args, const LbGatherArgs* ga, void* stream) {

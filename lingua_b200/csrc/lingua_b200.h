@@ -177,6 +177,25 @@ typedef struct LbGatherArgs {
 } LbGatherArgs;
 int lb_gemm_gather(const LbGemmArgs* args, const LbGatherArgs* ga, void* stream);
 
+// Grouped products on the SM-pair kernel: one launch for a bank of matrices, with the grouping read from device
+// memory (no host copy of group sizes). bf16 operands, no batch dims in `args` (nb0 = nb1 = 1).
+//   mode 1, grouped rows: C[m, :] = A[m, :] x B_g^T with g = sel[m / 256]: every 256-row tile of A uses the
+//           matrix of its group; B_g = args->B + g * group_stride elements (K- or N-contiguous as args->b_major
+//           says). Callers lay rows out group by group, each group padded to a multiple of 256 rows.
+//   mode 2, grouped contraction: C_g = A[:, rows_g]^T-style product over a range of K only:
+//           C_g (+)= sum over k in [sel[2g], sel[2g] + 64 * sel[2g+1]) of A[k, m] B[k, n], C_g = args->C +
+//           g * group_stride elements; a_major = b_major = 1 (K is the row index of both operands). A group with
+//           zero blocks writes zeros (adds nothing when args->accumulate).
+// sel is int32 device memory: [ceil(M / 256)] in mode 1, [n_groups][2] in mode 2; group indices are checked
+// against n_groups in the kernel (out of range: status word, tile computed with group 0).
+typedef struct LbGroupArgs {
+  int mode;
+  int n_groups;
+  long long group_stride;
+  const int* sel;
+} LbGroupArgs;
+int lb_gemm_grouped(const LbGemmArgs* args, const LbGroupArgs* gr, void* stream);
+
 // Barrier over the ranks of a group. pads[r] is the peer-visible address of rank r's pad
 // (uint32[world], zero before first use); epoch is the number of this barrier on these pads,
 // counted from 1 by every rank alike. Bounded wait: on timeout the status word is set.

@@ -52,6 +52,10 @@ class GatherArgs(C.Structure):
     ]
 
 
+class GroupArgs(C.Structure):
+    _fields_ = [("mode", C.c_int), ("n_groups", C.c_int), ("group_stride", C.c_longlong), ("sel", C.c_void_p)]
+
+
 class AttnArgs(C.Structure):
     _fields_ = [
         ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("o", C.c_void_p), ("lse", C.c_void_p),
@@ -94,6 +98,9 @@ def load():
     if hasattr(lib, "lb_gemm_scatter"):
         lib.lb_gemm_scatter.argtypes = [C.POINTER(GemmArgs), C.POINTER(ScatterArgs), C.c_void_p]
         lib.lb_gemm_scatter.restype = C.c_int
+    if hasattr(lib, "lb_gemm_grouped"):
+        lib.lb_gemm_grouped.argtypes = [C.POINTER(GemmArgs), C.POINTER(GroupArgs), C.c_void_p]
+        lib.lb_gemm_grouped.restype = C.c_int
     if hasattr(lib, "lb_gemm_gather"):
         lib.lb_gemm_gather.argtypes = [C.POINTER(GemmArgs), C.POINTER(GatherArgs), C.c_void_p]
         lib.lb_gemm_gather.restype = C.c_int

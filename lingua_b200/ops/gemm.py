@@ -203,6 +203,70 @@ def gemm_gather(x: torch.Tensor, w: torch.Tensor, plan: GatherPlan, peer_ptrs: S
     return out
 
 
+GROUP_ROWS = 256  # row granularity of a grouped product: the kernel's row tile (two SMs x 128 rows)
+
+
+def _grouped_args(a_t, b_t, out, M, N, K, a_major, b_major, lda, ldb, out_f32, accumulate):
+    args = _lib.GemmArgs()
+    args.A, args.B, args.C = a_t.data_ptr(), b_t.data_ptr(), out.data_ptr()
+    args.status = _lib.status_word(a_t.device).data_ptr()
+    args.M, args.N, args.K = M, N, K
+    args.a_major, args.b_major = a_major, b_major
+    args.in_dtype = _lib.LB_BF16
+    args.out_dtype = _lib.LB_F32 if out_f32 else _lib.LB_BF16
+    args.accumulate, args.alpha, args.force_bn = int(accumulate), 1.0, 0
+    args.lda, args.ldb, args.ldc = lda, ldb, out.stride(-2)
+    args.nb0 = args.nb1 = 1
+    return args
+
+
+def gemm_grouped_rows(x: torch.Tensor, bank: torch.Tensor, sel: torch.Tensor, transpose_bank: bool = False,
+                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One launch for ``out[m] = x[m] @ bank[sel[m // 256]]^T`` (or ``@ bank[...]`` with ``transpose_bank``).
+
+    ``x`` [Mp, K] bf16 with rows laid out group by group, every group padded to a multiple of 256 rows;
+    ``bank`` [G, N, K] (``transpose_bank``: [G, K, N]) bf16 contiguous; ``sel`` int32 [Mp / 256] on the device.
+    The grouping never reaches the host."""
+    assert x.is_cuda and x.dtype == torch.bfloat16 and bank.dtype == torch.bfloat16 and bank.is_contiguous()
+    Mp, K = x.shape
+    G = bank.shape[0]
+    N = bank.shape[2] if transpose_bank else bank.shape[1]
+    assert (bank.shape[1] if transpose_bank else bank.shape[2]) == K
+    assert Mp % GROUP_ROWS == 0 and sel.dtype == torch.int32 and sel.numel() >= Mp // GROUP_ROWS and sel.is_contiguous()
+    assert x.stride(1) == 1 and x.stride(0) % 8 == 0 and bank.shape[2] % 8 == 0
+    if out is None:
+        out = torch.empty(Mp, N, dtype=torch.bfloat16, device=x.device)
+    args = _grouped_args(x, bank, out, Mp, N, K, 0, 1 if transpose_bank else 0, x.stride(0), bank.shape[2], False, False)
+    gr = _lib.GroupArgs()
+    gr.mode, gr.n_groups, gr.group_stride, gr.sel = 1, G, bank.stride(0), sel.data_ptr()
+    rc = _lib.load().lb_gemm_grouped(C.byref(args), C.byref(gr), _lib.stream_ptr())
+    _lib.check(rc, f"lb_gemm_grouped(rows, M={Mp},N={N},K={K},G={G})")
+    return out
+
+
+def gemm_grouped_k(dy: torch.Tensor, x: torch.Tensor, k_range: torch.Tensor, out: torch.Tensor,
+                   accumulate: bool = False) -> torch.Tensor:
+    """One launch for ``out[g] (+)= dy[r0:r1]^T @ x[r0:r1]`` with ``(r0, (r1 - r0) / 64) = k_range[g]``.
+
+    ``dy`` [Mp, N] and ``x`` [Mp, K] bf16 row-major (rows are the contraction index), ``k_range`` int32 [G, 2]
+    on the device, ``out`` [G, N, K] fp32 contiguous. A group with zero blocks gets zeros (nothing added when
+    accumulating)."""
+    assert dy.is_cuda and dy.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and out.dtype == torch.float32
+    Mp, N = dy.shape
+    K = x.shape[1]
+    G = out.shape[0]
+    assert x.shape[0] == Mp and out.shape[1:] == (N, K) and out.is_contiguous()
+    assert dy.stride(1) == 1 and x.stride(1) == 1 and dy.stride(0) % 8 == 0 and x.stride(0) % 8 == 0
+    assert k_range.dtype == torch.int32 and k_range.is_contiguous() and k_range.numel() >= 2 * G
+    # operands of the kernel: A[k, m] = dy (m contiguous), B[k, n] = x (n contiguous); its "K" is the row count
+    args = _grouped_args(dy, x, out, N, K, Mp, 1, 1, dy.stride(0), x.stride(0), True, accumulate)
+    gr = _lib.GroupArgs()
+    gr.mode, gr.n_groups, gr.group_stride, gr.sel = 2, G, out.stride(0), k_range.data_ptr()
+    rc = _lib.load().lb_gemm_grouped(C.byref(args), C.byref(gr), _lib.stream_ptr())
+    _lib.check(rc, f"lb_gemm_grouped(k, M={N},N={K},K={Mp},G={G})")
+    return out
+
+
 def mm_nt(x: torch.Tensor, w: torch.Tensor, **kw) -> torch.Tensor:
     """x[M,K] @ w[N,K]^T -> [M,N] (linear forward)."""
     return gemm(x, w, **kw)
