@@ -75,53 +75,186 @@ __device__ __forceinline__ void st8(__nv_bfloat16* p, const bf16x8& v) {
 }
 
 // ------------------------------------------------------------------ RMSNorm
-// One block per row. h = x (+ res); y = h * rsqrt(mean(h^2) + eps) * w.
+// h = x (+ res); y = h * rsqrt(mean(h^2) + eps) * w.
 // If res != null the sum h is also written to h_out (the new residual stream).
-constexpr int NORM_MAX_VEC = 4;  // per-thread 8-element vectors kept in registers: D <= 256*8*4
+constexpr int NORM_MAX_VEC = 4;  // widest row: D <= 256 * 8 * 4
 
-__global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(
+// One warp per row (eight rows per block): every lane keeps its part of the row packed in registers, all loads
+// of a row are in flight together and the only exchange is a shuffle reduction -- no block barrier. VPL is the
+// number of 16-byte vectors per lane (D <= 256 * VPL).
+__device__ __forceinline__ void unpack8(const uint4& raw, float (&f)[8]) {
+  bf16x8 v;
+  v.raw = raw;
+  v.unpack(f);
+}
+// WPR warps share a row (its halves); their partial sums meet in shared memory.
+// Keeps the packed form live across a phase boundary: without it the compiler carries the unpacked fp32 values of
+// the first pass over the row into the second one, which costs four times the registers.
+__device__ __forceinline__ void keep_packed(uint4& v) {
+  asm volatile("" : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w));
+}
+template <int WPR>
+__device__ __forceinline__ float row_sum(float v, float* part) {
+  v = warp_sum(v);
+  if (WPR == 1) return v;
+  const int w = threadIdx.x >> 5;
+  if ((threadIdx.x & 31) == 0) part[w] = v;
+  __syncthreads();
+  return part[w] + part[w ^ 1];
+}
+template <int VPL, int WPR>
+__global__ void __launch_bounds__(256, 2) rmsnorm_fwd_warp_kernel(
     const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
     const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
-    __nv_bfloat16* __restrict__ h_out, float* __restrict__ rstd_out, int D, float eps) {
-  __shared__ float red[33];
-  const long long row = blockIdx.x;
-  const __nv_bfloat16* xr = x + row * D;
-  const int nvec = D / 8;
-  float vals[NORM_MAX_VEC][8];
-  float ss = 0.f;
+    __nv_bfloat16* __restrict__ h_out, float* __restrict__ rstd_out, long long M, int D, float eps) {
+  __shared__ float part[8];
+  const int sub = (threadIdx.x >> 5) % WPR;  // which part of the row this warp holds
+  const int lane = (threadIdx.x & 31) + 32 * sub;
+  constexpr int LPR = 32 * WPR;  // lanes per row
+  long long row = blockIdx.x * (long long)(8 / WPR) + (threadIdx.x >> 5) / WPR;
+  // rows past the end are computed on the last row and not stored (no early exit: the block meets at a barrier)
+  const int nvec = row < M ? D / 8 : 0;
+  if (row >= M) row = M - 1;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * D);
+  uint4 h[VPL];
 #pragma unroll
-  for (int i = 0; i < NORM_MAX_VEC; ++i) {
-    const int v = threadIdx.x + i * blockDim.x;
-    if (v < nvec) {
-      ld8(xr + v * 8).unpack(vals[i]);
-      if (res) {
-        float r[8];
-        ld8(res + row * D + v * 8).unpack(r);
+  for (int i = 0; i < VPL; ++i) {
+    const int v = lane + i * LPR;
+    h[i] = v < nvec ? xr[v] : make_uint4(0u, 0u, 0u, 0u);
+  }
+  if (res) {
+    const uint4* rr = reinterpret_cast<const uint4*>(res + row * D);
+    uint4* ho = reinterpret_cast<uint4*>(h_out + row * D);
+    constexpr int CH = VPL < 8 ? VPL : (VPL > 8 ? 4 : 8);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) vals[i][j] += r[j];
-        bf16x8 o;
-        o.pack(vals[i]);
-        st8(h_out + row * D + v * 8, o);
-        o.unpack(vals[i]);  // the normalised value uses the rounded residual, as a reload would
+    for (int c = 0; c < VPL; c += CH) {
+      uint4 r[CH];
+#pragma unroll
+      for (int i = 0; i < CH; ++i) {
+        const int v = lane + (c + i) * LPR;
+        r[i] = v < nvec ? rr[v] : make_uint4(0u, 0u, 0u, 0u);
       }
 #pragma unroll
-      for (int j = 0; j < 8; ++j) ss += vals[i][j] * vals[i][j];
+      for (int i = 0; i < CH; ++i) {
+        const int v = lane + (c + i) * LPR;
+        float a[8], b[8];
+        unpack8(h[c + i], a);
+        unpack8(r[i], b);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a[j] += b[j];
+        bf16x8 o;
+        o.pack(a);
+        h[c + i] = o.raw;  // the normalised value uses the rounded residual, as a reload would
+        if (v < nvec) ho[v] = o.raw;
+      }
     }
   }
-  ss = block_sum(ss, red);
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    float a[8];
+    unpack8(h[i], a);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += a[j] * a[j];
+  }
+  ss = row_sum<WPR>(ss, part);
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) keep_packed(h[i]);
   const float rstd = rsqrtf(ss / D + eps);
-  if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
+  if (lane == 0 && nvec && rstd_out) rstd_out[row] = rstd;
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  uint4* yr = reinterpret_cast<uint4*>(y + row * D);
 #pragma unroll
-  for (int i = 0; i < NORM_MAX_VEC; ++i) {
-    const int v = threadIdx.x + i * blockDim.x;
+  for (int i = 0; i < VPL; ++i) {
+    const int v = lane + i * LPR;
     if (v < nvec) {
-      float wv[8], o[8];
-      ld8(w + v * 8).unpack(wv);
+      float a[8], wv[8];
+      unpack8(h[i], a);
+      unpack8(__ldg(wr + v), wv);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) o[j] = vals[i][j] * rstd * wv[j];
-      bf16x8 ov;
-      ov.pack(o);
-      st8(y + row * D + v * 8, ov);
+      for (int j = 0; j < 8; ++j) a[j] = a[j] * rstd * wv[j];
+      bf16x8 o;
+      o.pack(a);
+      yr[v] = o.raw;
+    }
+  }
+}
+
+template <int VPL, int WPR>
+__global__ void __launch_bounds__(256, 2) rmsnorm_bwd_dx_warp_kernel(
+    const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
+    const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx, long long M, int D) {
+  __shared__ float part[8];
+  const int sub = (threadIdx.x >> 5) % WPR;
+  const int lane = (threadIdx.x & 31) + 32 * sub;
+  constexpr int LPR = 32 * WPR;
+  long long row = blockIdx.x * (long long)(8 / WPR) + (threadIdx.x >> 5) / WPR;
+  const int nvec = row < M ? D / 8 : 0;
+  if (row >= M) row = M - 1;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * D);
+  const uint4* dr = reinterpret_cast<const uint4*>(dy + row * D);
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  uint4 xv[VPL], dv[VPL];
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int v = lane + i * LPR;
+    xv[i] = v < nvec ? xr[v] : make_uint4(0u, 0u, 0u, 0u);
+    dv[i] = v < nvec ? dr[v] : make_uint4(0u, 0u, 0u, 0u);
+  }
+  const float rs = rstd[row];
+  float dot = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int v = lane + i * LPR;
+    if (v < nvec) {
+      float a[8], g[8], wv[8];
+      unpack8(xv[i], a);
+      unpack8(dv[i], g);
+      unpack8(__ldg(wr + v), wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) dot += g[j] * wv[j] * (a[j] * rs);
+    }
+  }
+  dot = row_sum<WPR>(dot, part) / D;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    keep_packed(xv[i]);
+    keep_packed(dv[i]);
+  }
+  uint4* ox = reinterpret_cast<uint4*>(dx + row * D);
+  const uint4* rr = reinterpret_cast<const uint4*>(dres ? dres + row * D : dy);
+  constexpr int CH = VPL < 8 ? VPL : 8;
+#pragma unroll
+  for (int c = 0; c < VPL; c += CH) {
+    uint4 r[CH];
+    if (dres) {
+#pragma unroll
+      for (int i = 0; i < CH; ++i) {
+        const int v = lane + (c + i) * LPR;
+        r[i] = v < nvec ? rr[v] : make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+      const int v = lane + (c + i) * LPR;
+      if (v < nvec) {
+        float a[8], g[8], wv[8], o[8];
+        unpack8(xv[c + i], a);
+        unpack8(dv[c + i], g);
+        unpack8(__ldg(wr + v), wv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = rs * (g[j] * wv[j] - a[j] * rs * dot);
+        if (dres) {
+          float b[8];
+          unpack8(r[i], b);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += b[j];
+        }
+        bf16x8 ov;
+        ov.pack(o);
+        ox[v] = ov.raw;
+      }
     }
   }
 }
@@ -215,33 +348,54 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_dw_kernel(
 // In-place rotation of interleaved pairs of the first n_rot_heads heads of every token row
 // (row stride `ld` elements). cs[pos][i] = (cos, sin) of pos * theta^(-2i/Dh).
 // sign = +1 forward, -1 backward (the transpose of a rotation is the opposite rotation).
-__global__ void rope_kernel(__nv_bfloat16* __restrict__ qk, const float2* __restrict__ cs,
-                            const int* __restrict__ pos_idx, long long n_tok, int seq_len, int ld,
-                            int n_rot_heads, int head_dim, float sign) {
+// A thread owns one 16-byte vector position of the head (4 rotation pairs) for one token and walks over the heads:
+// the cos / sin values are loaded once per token instead of once per head, and eight heads are in flight at a time.
+__global__ void __launch_bounds__(256) rope_kernel(__nv_bfloat16* __restrict__ qk, const float2* __restrict__ cs,
+                                                   const int* __restrict__ pos_idx, long long n_tok, int seq_len,
+                                                   int ld, int n_rot_heads, int head_dim, float sign) {
   const int vec_per_head = head_dim / 8;
-  const long long total = n_tok * n_rot_heads * vec_per_head;
+  const long long total = n_tok * vec_per_head;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
     const int v = i % vec_per_head;
-    const long long th = i / vec_per_head;
-    const int h = th % n_rot_heads;
-    const long long tok = th / n_rot_heads;
+    const long long tok = i / vec_per_head;
     const int pos = pos_idx ? pos_idx[tok] : (int)(tok % seq_len);
-    __nv_bfloat16* p = qk + tok * ld + h * head_dim + v * 8;
-    float f[8], o[8];
-    ld8(p).unpack(f);
     const float4* c4 = reinterpret_cast<const float4*>(cs + (long long)pos * (head_dim / 2) + v * 4);
-    const float4 c01 = c4[0], c23 = c4[1];
+    const float4 c01 = __ldg(c4), c23 = __ldg(c4 + 1);
     const float cc[4] = {c01.x, c01.z, c23.x, c23.z};
     const float sn[4] = {c01.y * sign, c01.w * sign, c23.y * sign, c23.w * sign};
+    __nv_bfloat16* base = qk + tok * ld + v * 8;
+    int h = 0;
+    for (; h + 8 <= n_rot_heads; h += 8) {
+      bf16x8 in[8];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      o[2 * j] = f[2 * j] * cc[j] - f[2 * j + 1] * sn[j];
-      o[2 * j + 1] = f[2 * j] * sn[j] + f[2 * j + 1] * cc[j];
+      for (int u = 0; u < 8; ++u) in[u] = ld8(base + (h + u) * head_dim);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        float f[8], o[8];
+        in[u].unpack(f);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          o[2 * j] = f[2 * j] * cc[j] - f[2 * j + 1] * sn[j];
+          o[2 * j + 1] = f[2 * j] * sn[j] + f[2 * j + 1] * cc[j];
+        }
+        bf16x8 ov;
+        ov.pack(o);
+        st8(base + (h + u) * head_dim, ov);
+      }
     }
-    bf16x8 ov;
-    ov.pack(o);
-    st8(p, ov);
+    for (; h < n_rot_heads; ++h) {
+      float f[8], o[8];
+      ld8(base + h * head_dim).unpack(f);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        o[2 * j] = f[2 * j] * cc[j] - f[2 * j + 1] * sn[j];
+        o[2 * j + 1] = f[2 * j] * sn[j] + f[2 * j + 1] * cc[j];
+      }
+      bf16x8 ov;
+      ov.pack(o);
+      st8(base + h * head_dim, ov);
+    }
   }
 }
 
@@ -565,16 +719,31 @@ extern "C" int lb_rmsnorm_fwd(const void* x, const void* res, const void* w, voi
                               float* rstd, long long M, int D, float eps, void* stream) {
   if (D % 8 || D > 256 * 8 * NORM_MAX_VEC) return 1;
   if (M == 0) return 0;
-  rmsnorm_fwd_kernel<<<(unsigned)M, 256, 0, S_(stream)>>>((const bf16*)x, (const bf16*)res, (const bf16*)w,
-                                                          (bf16*)y, (bf16*)h_out, rstd, D, eps);
+  if (res && !h_out) return 2;
+#define LB_NORM_FWD(V, W)                                                                                  \
+  rmsnorm_fwd_warp_kernel<V, W><<<(unsigned)((M + 8 / W - 1) / (8 / W)), 256, 0, S_(stream)>>>(              \
+      (const bf16*)x, (const bf16*)res, (const bf16*)w, (bf16*)y, (bf16*)h_out, rstd, M, D, eps)
+  if (D <= 256 * 4) LB_NORM_FWD(4, 1);
+  else if (D <= 256 * 8) LB_NORM_FWD(8, 1);
+  else if (D <= 256 * 16) LB_NORM_FWD(8, 2);
+  else LB_NORM_FWD(16, 2);
+#undef LB_NORM_FWD
   LB_LAUNCH_END();
 }
 extern "C" int lb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd,
                               const void* dres, void* dx, float* dw, long long M, int D, void* stream) {
   if (D % 8 || D > 256 * 8 * NORM_MAX_VEC) return 1;
   if (M == 0) return 0;
-  rmsnorm_bwd_dx_kernel<<<(unsigned)M, 256, 0, S_(stream)>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd,
-                                                            (const bf16*)dres, (bf16*)dx, D);
+#define LB_NORM_BWD(V, W)                                                                                  \
+  rmsnorm_bwd_dx_warp_kernel<V, W><<<(unsigned)((M + 8 / W - 1) / (8 / W)), 256, 0, S_(stream)>>>(           \
+      (const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd, (const bf16*)dres, (bf16*)dx, M, D)
+  if (D <= 256 * 4) LB_NORM_BWD(4, 1);
+  else if (D <= 256 * 8) LB_NORM_BWD(8, 1);
+  else if (D <= 256 * 16) LB_NORM_BWD(8, 2);
+  else  // two packed operands of a wider row do not fit the lanes' registers: one block per row
+    rmsnorm_bwd_dx_kernel<<<(unsigned)M, 256, 0, S_(stream)>>>((const bf16*)dy, (const bf16*)x, (const bf16*)w, rstd,
+                                                              (const bf16*)dres, (bf16*)dx, D);
+#undef LB_NORM_BWD
   if (dw) {
     dim3 grid((D / 8 + 31) / 32, (unsigned)((M + DW_ROWS_PER_BLOCK - 1) / DW_ROWS_PER_BLOCK));
     rmsnorm_bwd_dw_kernel<<<grid, dim3(32, 8), 0, S_(stream)>>>((const bf16*)dy, (const bf16*)x, rstd, dw, M, D);
@@ -585,8 +754,8 @@ extern "C" int lb_rmsnorm_bwd(const void* dy, const void* x, const void* w, cons
 extern "C" int lb_rope(void* qk, const void* cs, const int* pos_idx, long long n_tok, int seq_len, int ld,
                        int n_rot_heads, int head_dim, int backward, void* stream) {
   if (head_dim % 8 || ld % 8) return 1;
-  const long long total = n_tok * n_rot_heads * (head_dim / 8);
-  if (total == 0) return 0;
+  const long long total = n_tok * (head_dim / 8);
+  if (total == 0 || n_rot_heads == 0) return 0;
   rope_kernel<<<grid_for(total, 256), 256, 0, S_(stream)>>>((bf16*)qk, (const float2*)cs, pos_idx, n_tok, seq_len,
                                                             ld, n_rot_heads, head_dim, backward ? -1.f : 1.f);
   LB_LAUNCH_END();

@@ -134,9 +134,9 @@ def main(argv=None):
         n, h, pd, Ns, g = 32, 64, 64, 128, 1
         row = torch.randn(n, h * pd + 2 * g * Ns, device=dev, dtype=bf)
         x, Bm, Cm = row[:, :h * pd].view(n, h, pd), row[:, h * pd:h * pd + g * Ns].view(n, g, Ns), row[:, h * pd + g * Ns:].view(n, g, Ns)
-        dt, A = torch.rand(n, h, device=dev) * 0.1, -torch.rand(h, device=dev)
+        dt, A_log = torch.rand(n, h, device=dev) * 0.1, -torch.rand(h, device=dev)
         state = torch.randn(n, h, pd, Ns, device=dev)
-        fn = lambda: S.selective_state_update(state, x, dt, A, Bm, Cm, None)
+        fn = lambda: S.selective_state_update(state, x, dt, A_log, Bm, Cm, None)
         bytes_ = 2.0 * state.numel() * 4
     elif a.op == "ssd":
         from . import ssd as S
@@ -144,9 +144,9 @@ def main(argv=None):
         b, sq, h, pd, Ns = a.batch, a.seq, 64, 64, 128
         x = torch.randn(b, sq, h, pd, device=dev, dtype=bf)
         dt = torch.rand(b, sq, h, device=dev) * 0.1
-        A = -torch.rand(h, device=dev)
+        A_log = -torch.rand(h, device=dev)
         Bm, Cm = torch.randn(b, sq, 1, Ns, device=dev, dtype=bf), torch.randn(b, sq, 1, Ns, device=dev, dtype=bf)
-        fn = lambda: S.ssd_chunked(x, dt, A, Bm, Cm, None, 256)
+        fn = lambda: S.ssd_chunked(x, dt, A_log, Bm, Cm, None, 256)
         flops = 2.0 * b * sq * h * (256 * Ns + 256 * pd + 2 * pd * Ns)  # the four chunk products
     elif a.op == "gemm_wgrad":
         dy, x = torch.randn(K, M, device=dev, dtype=bf), torch.randn(K, N, device=dev, dtype=bf)

@@ -27,6 +27,36 @@ def test_indexed_matmul_bf16_vs_fp32_oracle():
     assert (gw.float() - rw.float()).abs().max() < 0.03 * rw.abs().max() and gw[7].abs().max() == 0
 
 
+def test_indexed_matmul_grouped_launch_matches_the_group_loop():
+    """The single-launch grouped path against the loop of plain products, with repeated source rows and an
+    engine-style fp32 gradient buffer that is accumulated into over two backward passes."""
+    from lingua_b200.ops.indexed_matmul import indexed_matmul, plan_groups
+
+    torch.manual_seed(5)
+    dev = "cuda"
+    x = (torch.randn(700, 256, device=dev) * 0.5).bfloat16().requires_grad_()
+    idx = torch.randint(0, 16, (2, 1500), device=dev)
+    idx[idx == 2] = 9
+    rows = torch.randint(0, 700, (2, 1500), device=dev)
+    outs = []
+    for grouped in (True, False):
+        w = (torch.randn(16, 128, 256, generator=torch.Generator().manual_seed(6)) * 0.06).bfloat16().to(dev).requires_grad_()
+        w.main_grad = torch.full((16, 128, 256), float("nan"), device=dev)
+        plan = plan_groups(idx, 16, grouped=grouped)
+        assert plan.grouped == grouped and (not grouped or plan._counts is None)
+        gx = 0
+        for rep in range(2):
+            y = indexed_matmul(x, w, idx, plan, rows)
+            g = torch.randn(y.shape, generator=torch.Generator().manual_seed(7 + rep)).to(dev).bfloat16()
+            gx = gx + torch.autograd.grad(y, x, g)[0].float()
+        assert plan._counts is None or not grouped  # the grouped path never reads the sizes
+        outs.append((y.float(), gx, w.main_grad.clone()))
+    (y1, gx1, gw1), (y0, gx0, gw0) = outs
+    assert (y1 - y0).abs().max() < 0.02 * y0.abs().max()
+    assert (gx1 - gx0).abs().max() < 0.02 * gx0.abs().max()
+    assert torch.isfinite(gw1).all() and (gw1 - gw0).abs().max() < 0.01 * gw0.abs().max() and gw1[2].abs().max() == 0
+
+
 def test_gemm_operands_with_ragged_pitch():
     """A byte-vocabulary head has 258 outputs: its gradient has a row pitch that TMA cannot address."""
     from lingua_b200.ops.gemm import mm_nn, mm_tn

@@ -15,7 +15,7 @@ def close(a, b, tol=2e-2):
     assert err / ref < tol, f"rel {err / ref:.4g}"
 
 
-@pytest.mark.parametrize("M,D", [(64, 256), (300, 4096), (17, 2048)])
+@pytest.mark.parametrize("M,D", [(64, 256), (300, 4096), (17, 2048), (33, 8192), (21, 1000), (9, 5120), (3, 3072)])
 @pytest.mark.parametrize("with_res", [False, True])
 def test_rmsnorm_fwd_bwd(M, D, with_res):
     torch.manual_seed(0)
@@ -39,21 +39,22 @@ def test_rmsnorm_fwd_bwd(M, D, with_res):
 
 def test_rope_roundtrip_and_ref():
     torch.manual_seed(0)
-    B, S, H, Dh = 2, 96, 6, 128
+    B, S, H, Dh = 2, 96, 13, 128  # eleven rotated heads: one group of eight and three single ones
     qkv = torch.randn(B * S, H * Dh, device=DEV, dtype=torch.bfloat16)
+    R = 11
     cs = F.rope_table(Dh, S, 10000.0, DEV)
-    ref = F.rope_ref(qkv[:, : 4 * Dh].reshape(B, S, 4, Dh), cs)
+    ref = F.rope_ref(qkv[:, : R * Dh].reshape(B, S, R, Dh), cs)
     orig = qkv.clone()
-    F.rope_(qkv, cs, 4, Dh, S)
-    close(qkv[:, : 4 * Dh].reshape(B, S, 4, Dh), ref)
-    assert torch.equal(qkv[:, 4 * Dh:], orig[:, 4 * Dh:])
-    F.rope_(qkv, cs, 4, Dh, S, backward=True)
+    F.rope_(qkv, cs, R, Dh, S)
+    close(qkv[:, : R * Dh].reshape(B, S, R, Dh), ref)
+    assert torch.equal(qkv[:, R * Dh:], orig[:, R * Dh:])
+    F.rope_(qkv, cs, R, Dh, S, backward=True)
     close(qkv, orig, 3e-2)
     pos = torch.randint(0, S, (B * S,), device=DEV, dtype=torch.int32)
     q2 = orig.clone()
-    F.rope_(q2, cs, 4, Dh, S, pos=pos)
-    ref2 = F.rope_ref(orig[:, : 4 * Dh].reshape(B, S, 4, Dh), cs, pos)
-    close(q2[:, : 4 * Dh].reshape(B, S, 4, Dh), ref2)
+    F.rope_(q2, cs, R, Dh, S, pos=pos)
+    ref2 = F.rope_ref(orig[:, : R * Dh].reshape(B, S, R, Dh), cs, pos)
+    close(q2[:, : R * Dh].reshape(B, S, R, Dh), ref2)
 
 
 @pytest.mark.parametrize("mode", [F.ACT_SILU, F.ACT_RELU2])

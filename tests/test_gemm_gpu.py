@@ -167,3 +167,63 @@ def test_gemm_gather_pulls_remote_weight_blocks(W, rank, M, N, K):
     out2 = G.gemm_gather(x, w_local, plan, [p.data_ptr() for p in peers])
     torch.cuda.synchronize()
     assert torch.equal(out, out2)
+
+
+def _group_layout(counts, dev):
+    """Padded layout the grouped kernels expect: every group starts on a 256-row boundary."""
+    R = G.GROUP_ROWS
+    padded = [(c + R - 1) // R * R for c in counts]
+    offs = [sum(padded[:g]) for g in range(len(counts))]
+    Mp = sum(padded) + R  # one spare tile past the last group, as the device-side plan leaves
+    sel = torch.full((Mp // R,), len(counts) - 1, dtype=torch.int32)
+    for g, (o, p) in enumerate(zip(offs, padded)):
+        sel[o // R:(o + p) // R] = g
+    k_range = torch.tensor([[o, p // 64] for o, p in zip(offs, padded)], dtype=torch.int32)
+    return offs, Mp, sel.to(dev), k_range.to(dev)
+
+
+@pytest.mark.parametrize("transpose_bank", [False, True])
+def test_grouped_rows_picks_the_matrix_of_each_row_tile(transpose_bank):
+    torch.manual_seed(3)
+    dev = "cuda"
+    counts = [300, 0, 17, 1024, 255, 256]
+    K, N = 192, 136
+    offs, Mp, sel, _ = _group_layout(counts, dev)
+    x = torch.zeros(Mp, K, device=dev, dtype=torch.bfloat16)
+    bank = (torch.randn(len(counts), *((K, N) if transpose_bank else (N, K)), device=dev) * 0.1).bfloat16()
+    for o, c in zip(offs, counts):
+        x[o:o + c] = (torch.randn(c, K, device=dev) * 0.5).bfloat16()
+    y = G.gemm_grouped_rows(x, bank, sel, transpose_bank=transpose_bank)
+    assert y.shape == (Mp, N)
+    for g, (o, c) in enumerate(zip(offs, counts)):
+        w = bank[g].float().t() if transpose_bank else bank[g].float()
+        if c:
+            _check(y[o:o + c], x[o:o + c].float() @ w.t(), K)
+    assert y[offs[-1] + counts[-1]:].abs().max() == 0  # padding rows are zero rows
+    from lingua_b200.ops import _lib
+    _lib.check_status()
+
+
+@pytest.mark.parametrize("accumulate", [False, True])
+def test_grouped_contraction_over_row_ranges(accumulate):
+    torch.manual_seed(4)
+    dev = "cuda"
+    counts = [300, 0, 17, 1024, 255, 256]
+    N, K = 136, 192
+    offs, Mp, _, k_range = _group_layout(counts, dev)
+    dy = torch.zeros(Mp, N, device=dev, dtype=torch.bfloat16)
+    x = torch.zeros(Mp, K, device=dev, dtype=torch.bfloat16)
+    for o, c in zip(offs, counts):
+        dy[o:o + c] = (torch.randn(c, N, device=dev) * 0.5).bfloat16()
+        x[o:o + c] = (torch.randn(c, K, device=dev) * 0.5).bfloat16()
+    base = torch.randn(len(counts), N, K, device=dev)
+    out = base.clone() if accumulate else torch.full_like(base, float("nan"))  # stale values must not survive
+    G.gemm_grouped_k(dy, x, k_range, out, accumulate=accumulate)
+    for g, (o, c) in enumerate(zip(offs, counts)):
+        want = dy[o:o + c].float().t() @ x[o:o + c].float() + (base[g] if accumulate else 0)
+        if c:
+            _check(out[g], want, max(c, 256))
+        else:
+            assert torch.equal(out[g], base[g] if accumulate else torch.zeros_like(base[g]))
+    from lingua_b200.ops import _lib
+    _lib.check_status()
