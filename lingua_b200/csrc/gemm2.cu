@@ -78,10 +78,11 @@ struct Gemm2Params {
   const int* grp_sel;
 };
 
-// group of a row tile (mode 1), always checked: a bad entry is reported and replaced by group 0
+// group of a row tile (mode 1), always checked: -1 marks a tile without rows (nothing is loaded, multiplied or
+// stored for it), any other bad entry is reported and replaced by group 0
 __device__ __forceinline__ int g2_row_group(const Gemm2Params& p, int mt) {
   const int g = __ldg(p.grp_sel + mt);
-  if (g >= 0 && g < p.grp_n) return g;
+  if (g >= -1 && g < p.grp_n) return g;
   if (p.status) atomicOr(p.status, ST_BAD_ARG | 0x43);
   return 0;
 }
@@ -258,6 +259,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
         int ab0 = b0, bb0 = b0, k_first = 0, kb_n = num_kb;
         if (p.grp_mode == 1) {
           bb0 = g2_row_group(p, mt);
+          if (bb0 < 0) kb_n = 0;
         } else if (p.grp_mode == 2) {
           const int2 kr = g2_k_range(p, b0);
           ab0 = bb0 = 0;
@@ -319,6 +321,11 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
         const uint32_t tmem_d = tmem_base + acc * G2_BN;
         int kb_n = num_kb;
         if (p.grp_mode == 2) kb_n = g2_k_range(p, (tile / tiles_per_batch) % p.nb0).y;
+        if (p.grp_mode == 1) {
+          int mt, nt;
+          g2_tile_coords(tile % tiles_per_batch, p, mt, nt);
+          if (g2_row_group(p, mt) < 0) kb_n = 0;
+        }
         for (int kb = 0; kb < kb_n; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
@@ -363,6 +370,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
       const int b0 = batch % p.nb0, b1 = batch / p.nb0;
       // a group without rows issued no product: its accumulator holds whatever the previous tile left
       const bool empty = p.grp_mode == 2 && g2_k_range(p, b0).y == 0;
+      const bool dead = p.grp_mode == 1 && g2_row_group(p, mt) < 0;  // a row tile past the last group
       if (!mbar_wait(tfull_bar(acc), acc_ph, &abort_flag, p.status, 0x34)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * G2_BN + (static_cast<uint32_t>(quarter * 32) << 16);
@@ -373,7 +381,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
         return (F8 && p.col_scale && col < p.N) ? __ldg(p.col_scale + col) : 1.f;
       };
       if (p.epi_tma) {
-        if (m0 < p.M) {
+        if (m0 < p.M && !dead) {
           const CUtensorMap* cmap = &tma_c;
           int drow = m0;
           bool table_ok = true;
@@ -460,7 +468,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
 #pragma unroll
             for (int i = 0; i < 32; ++i) r[i] = 0u;
           }
-          if (row < p.M) {
+          if (row < p.M && !dead) {
             if (sizeof(OutT) == 2) {
 #pragma unroll
               for (int g = 0; g < 4; ++g) {

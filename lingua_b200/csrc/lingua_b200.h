@@ -182,6 +182,7 @@ int lb_gemm_gather(const LbGemmArgs* args, const LbGatherArgs* ga, void* stream)
 //   mode 1, grouped rows: C[m, :] = A[m, :] x B_g^T with g = sel[m / 256]: every 256-row tile of A uses the
 //           matrix of its group; B_g = args->B + g * group_stride elements (K- or N-contiguous as args->b_major
 //           says). Callers lay rows out group by group, each group padded to a multiple of 256 rows.
+//           sel = -1 marks a row tile without rows: it is skipped and its output rows are left untouched.
 //   mode 2, grouped contraction: C_g = A[:, rows_g]^T-style product over a range of K only:
 //           C_g (+)= sum over k in [sel[2g], sel[2g] + 64 * sel[2g+1]) of A[k, m] B[k, n], C_g = args->C +
 //           g * group_stride elements; a_major = b_major = 1 (K is the row index of both operands). A group with

@@ -226,7 +226,8 @@ def gemm_grouped_rows(x: torch.Tensor, bank: torch.Tensor, sel: torch.Tensor, tr
 
     ``x`` [Mp, K] bf16 with rows laid out group by group, every group padded to a multiple of 256 rows;
     ``bank`` [G, N, K] (``transpose_bank``: [G, K, N]) bf16 contiguous; ``sel`` int32 [Mp / 256] on the device.
-    The grouping never reaches the host."""
+    ``sel`` = -1 marks a tile without rows, which is skipped (its output rows are not written). The grouping never
+    reaches the host."""
     assert x.is_cuda and x.dtype == torch.bfloat16 and bank.dtype == torch.bfloat16 and bank.is_contiguous()
     Mp, K = x.shape
     G = bank.shape[0]

@@ -98,7 +98,8 @@ def plan_groups(indices: torch.Tensor, n: int, grouped: Optional[bool] = None) -
         plan.pos.index_copy_(0, order, plan.prow)
         plan.padded_rows = (T + n * (R - 1) + R - 1) // R * R
         tiles = torch.arange(plan.padded_rows // R, device=flat.device) * R
-        plan.sel = torch.searchsorted(pend, tiles, right=True).clamp_(max=n - 1).to(torch.int32)
+        sel = torch.searchsorted(pend, tiles, right=True)
+        plan.sel = torch.where(sel < n, sel, -1).to(torch.int32)  # -1: a tile past the last group, skipped
         plan.k_range = torch.stack((poff, padded // 64), dim=1).to(torch.int32).contiguous()
     return plan
 

@@ -175,7 +175,7 @@ def _group_layout(counts, dev):
     padded = [(c + R - 1) // R * R for c in counts]
     offs = [sum(padded[:g]) for g in range(len(counts))]
     Mp = sum(padded) + R  # one spare tile past the last group, as the device-side plan leaves
-    sel = torch.full((Mp // R,), len(counts) - 1, dtype=torch.int32)
+    sel = torch.full((Mp // R,), -1, dtype=torch.int32)  # -1: no rows in this tile
     for g, (o, p) in enumerate(zip(offs, padded)):
         sel[o // R:(o + p) // R] = g
     k_range = torch.tensor([[o, p // 64] for o, p in zip(offs, padded)], dtype=torch.int32)
@@ -193,13 +193,15 @@ def test_grouped_rows_picks_the_matrix_of_each_row_tile(transpose_bank):
     bank = (torch.randn(len(counts), *((K, N) if transpose_bank else (N, K)), device=dev) * 0.1).bfloat16()
     for o, c in zip(offs, counts):
         x[o:o + c] = (torch.randn(c, K, device=dev) * 0.5).bfloat16()
-    y = G.gemm_grouped_rows(x, bank, sel, transpose_bank=transpose_bank)
-    assert y.shape == (Mp, N)
+    y = torch.full((Mp, N), 7.0, device=dev, dtype=torch.bfloat16)
+    G.gemm_grouped_rows(x, bank, sel, transpose_bank=transpose_bank, out=y)
     for g, (o, c) in enumerate(zip(offs, counts)):
         w = bank[g].float().t() if transpose_bank else bank[g].float()
         if c:
             _check(y[o:o + c], x[o:o + c].float() @ w.t(), K)
-    assert y[offs[-1] + counts[-1]:].abs().max() == 0  # padding rows are zero rows
+    assert y[offs[-1] + counts[-1]:Mp - G.GROUP_ROWS].abs().max() == 0 if counts[-1] % G.GROUP_ROWS else True
+    assert y[offs[2] + counts[2]:offs[3]].abs().max() == 0  # padding rows of a group are zero rows
+    assert (y[Mp - G.GROUP_ROWS:] == 7.0).all()  # the tile past the last group is skipped
     from lingua_b200.ops import _lib
     _lib.check_status()
 
