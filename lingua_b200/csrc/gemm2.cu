@@ -76,7 +76,26 @@ struct Gemm2Params {
   // mode 2 = batch g contracts over the K range (grp_sel[2g], 64 * grp_sel[2g + 1]) of unbatched A and B
   int grp_mode, grp_n;
   const int* grp_sel;
+  // Tail split: when the last wave of the persistent walk would keep at most half of the SM pairs busy, its tiles
+  // are issued as two half-width tiles each (256 x 128), which halves the time the other pairs sit idle.
+  int tail_first;        // first tile of the split region (= number of tiles when nothing is split)
+  int num_work;          // work items of the walk: tail_first + 2 * split tiles
+  uint32_t idesc_f8_half;
 };
+
+// work item of the persistent walk -> (tile, column offset inside the tile, tile width)
+__device__ __forceinline__ void g2_work(int work, const Gemm2Params& p, int& tile, int& n_off, int& bn) {
+  if (work < p.tail_first) {
+    tile = work;
+    n_off = 0;
+    bn = G2_BN;
+  } else {
+    const int i = work - p.tail_first;
+    tile = p.tail_first + (i >> 1);
+    n_off = (i & 1) * (G2_BN / 2);
+    bn = G2_BN / 2;
+  }
+}
 
 // group of a row tile (mode 1), always checked: -1 marks a tile without rows (nothing is loaded, multiplied or
 // stored for it), any other bad entry is reported and replaced by group 0
@@ -241,20 +260,23 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
   constexpr int BK_ELEMS = F8 ? 128 : G2_BK;  // one 128-byte swizzle row along K per stage
   const int num_kb = (p.K + BK_ELEMS - 1) / BK_ELEMS;
   const int tiles_per_batch = p.tiles_m * p.tiles_n;
-  const int num_tiles = tiles_per_batch * p.nb0 * p.nb1;
 
   if (warp == 0) {
     if (lane == 0) {
       // ------------------------------------------------ TMA producer (both CTAs)
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = pair; ok && tile < num_tiles; tile += n_pairs) {
+      for (int work = pair; ok && work < p.num_work; work += n_pairs) {
+        int tile, n_off, bn;
+        g2_work(work, p, tile, n_off, bn);
         const int batch = tile / tiles_per_batch;
         const int t = tile - batch * tiles_per_batch;
         int mt, nt;
         g2_tile_coords(t, p, mt, nt);
         const int m0 = mt * G2_BM + rank * G2_ROWS;
-        const int n0 = nt * G2_BN + rank * G2_ROWS;
+        // each CTA of the pair supplies half of the tile's B rows; a half-width tile still loads a full box per
+        // CTA (the stage layout and byte count stay the same) and the MMA reads only its first bn / 2 rows
+        const int n0 = nt * G2_BN + n_off + rank * (bn / 2);
         const int b0 = batch % p.nb0, b1 = batch / p.nb0;
         int ab0 = b0, bb0 = b0, k_first = 0, kb_n = num_kb;
         if (p.grp_mode == 1) {
@@ -306,13 +328,18 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
   } else if (warp == 1) {
     if (lane == 0 && leader) {
       // ------------------------------------------------ MMA issuer (leader CTA only)
-      constexpr uint32_t idesc = make_idesc(G2_BM, G2_BN, 1, 1, AMAJ, BMAJ);
+      constexpr uint32_t idesc_full = make_idesc(G2_BM, G2_BN, 1, 1, AMAJ, BMAJ);
+      constexpr uint32_t idesc_half = make_idesc(G2_BM, G2_BN / 2, 1, 1, AMAJ, BMAJ);
       constexpr uint32_t SBO = 1024, LBO_MN = G2_BK * 128;
       constexpr uint32_t A_KSTEP = (AMAJ == 0) ? 32u : 16u * 128u;
       constexpr uint32_t B_KSTEP = (BMAJ == 0) ? 32u : 16u * 128u;
       uint32_t it = 0, tile_iter = 0;
       bool ok = true;
-      for (int tile = pair; ok && tile < num_tiles; tile += n_pairs, ++tile_iter) {
+      for (int work = pair; ok && work < p.num_work; work += n_pairs, ++tile_iter) {
+        int tile, n_off, bn;
+        g2_work(work, p, tile, n_off, bn);
+        const uint32_t idesc = bn == G2_BN ? idesc_full : idesc_half;
+        const uint32_t idesc8 = bn == G2_BN ? p.idesc_f8 : p.idesc_f8_half;
         const int acc = tile_iter & 1;
         const uint32_t acc_ph = (tile_iter >> 1) & 1u;
         ok = mbar_wait(tempty_bar(acc), acc_ph ^ 1u, &abort_flag, p.status, 0x32);
@@ -339,7 +366,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
             const uint64_t ad = make_smem_desc(sa + k * A_KSTEP, AMAJ ? LBO_MN : 16u, SBO);
             const uint64_t bd = make_smem_desc(sb + k * B_KSTEP, BMAJ ? LBO_MN : 16u, SBO);
             if (F8)
-              umma2_f8(tmem_d, ad, bd, p.idesc_f8, (kb | k) != 0);
+              umma2_f8(tmem_d, ad, bd, idesc8, (kb | k) != 0);
             else
               umma2_f16(tmem_d, ad, bd, idesc, (kb | k) != 0);
           }
@@ -358,7 +385,9 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
     const bool issuer = (warp == 2 && lane == 0);
     constexpr int PC = 128 / (int)sizeof(OutT);  // columns per piece: 32 fp32 or 64 bf16
     uint32_t tile_iter = 0, piece_iter = 0;
-    for (int tile = pair; tile < num_tiles; tile += n_pairs, ++tile_iter) {
+    for (int work = pair; work < p.num_work; work += n_pairs, ++tile_iter) {
+      int tile, n_off, bn;
+      g2_work(work, p, tile, n_off, bn);
       const int acc = tile_iter & 1;
       const uint32_t acc_ph = (tile_iter >> 1) & 1u;
       const int batch = tile / tiles_per_batch;
@@ -366,7 +395,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
       int mt, nt;
       g2_tile_coords(t, p, mt, nt);
       const int m0 = mt * G2_BM + rank * G2_ROWS;
-      const int n0 = nt * G2_BN;
+      const int n0 = nt * G2_BN + n_off;
       const int b0 = batch % p.nb0, b1 = batch / p.nb0;
       // a group without rows issued no product: its accumulator holds whatever the previous tile left
       const bool empty = p.grp_mode == 2 && g2_k_range(p, b0).y == 0;
@@ -394,7 +423,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
 #pragma unroll 1
           for (int c = 0; c < G2_BN / PC; ++c) {
             const int col0 = n0 + c * PC;
-            if (col0 >= p.N || !table_ok) break;  // uniform over the four warps
+            if (col0 >= p.N || c * PC >= bn || !table_ok) break;  // uniform over the four warps
             const uint32_t buf = aux_base + (piece_iter & 1u) * G2_PIECE;
             if (issuer) tma_store_wait_read<1>();  // the store that last used this buffer has read it
             g2_epi_bar_sync();
@@ -460,7 +489,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
 #pragma unroll 1
         for (int c = 0; c < G2_BN / 32; ++c) {
           const int col0 = n0 + c * 32;
-          if (col0 >= p.N) break;
+          if (col0 >= p.N || c * 32 >= bn) break;
           uint32_t r[32];
           tmem_ld32(taddr + c * 32, r);
           tmem_wait_ld();
@@ -635,7 +664,17 @@ static int launch_gemm2(const LbGemmArgs& a_in, const LbScatterArgs* sc, cudaStr
   p.ldc = a.ldc; p.c_bs0 = a.c_bs0; p.c_bs1 = a.c_bs1;
   p.alpha = a.alpha; p.accumulate = a.accumulate;
   p.C = a.C; p.status = a.status;
-  p.group_m = p.tiles_m < 8 ? p.tiles_m : 8;
+  // Row tiles per rasterisation group: the A rows of a group are re-used by every column tile and should stay in
+  // L2 while B streams past them, so take the largest group whose slice of A stays under 48 MB. Measured under the
+  // power cap at 8192 x 11008 x 4096: 16 tiles 1254 TFLOP/s, 8 tiles 1229, 32 tiles 1173; at K = 11008 eight tiles
+  // are best. LB_GEMM_GROUP_M overrides the choice for tuning runs.
+  int group_m = 32;
+  while (group_m > 4 && (long long)group_m * G2_BM * a.K * IN_ESZ > (48ll << 20)) group_m >>= 1;
+  if (const char* e = getenv("LB_GEMM_GROUP_M")) {
+    const int v = atoi(e);
+    if (v > 0) group_m = v;
+  }
+  p.group_m = p.tiles_m < group_m ? p.tiles_m : group_m;
   p.m_rot = 0;
   p.scatter = 0;
   p.blocks = nullptr;
@@ -702,7 +741,19 @@ static int launch_gemm2(const LbGemmArgs& a_in, const LbScatterArgs* sc, cudaStr
   }
   const long long tiles = (long long)p.tiles_m * p.tiles_n * a.nb0 * a.nb1;
   const int max_pairs = num_sms() / 2;
-  const int pairs = (int)(tiles < max_pairs ? tiles : max_pairs);
+  if (tiles > 0x3fffffffll) return 9;
+  p.tail_first = (int)tiles;
+  p.idesc_f8_half = f8 ? make_idesc(G2_BM, G2_BN / 2, (uint32_t)f8->a_fmt, (uint32_t)f8->b_fmt, 0, 0) : 0u;
+  {
+    // split the last wave when it would occupy at most half of the pairs (see Gemm2Params::tail_first); not in
+    // gather mode, whose producer waits per 128-row block of B, nor for batched or grouped launches
+    static const bool no_split = getenv("LB_GEMM_NO_TAIL_SPLIT") != nullptr;
+    const int rem = (int)(tiles % max_pairs);
+    if (!no_split && !GATHER && !gr && a.nb0 == 1 && a.nb1 == 1 && rem > 0 && 2 * rem <= max_pairs)
+      p.tail_first = (int)tiles - rem;
+  }
+  p.num_work = p.tail_first + 2 * ((int)tiles - p.tail_first);
+  const int pairs = p.num_work < max_pairs ? p.num_work : max_pairs;
   if (ensure_dyn_smem<gemm2_kernel<AMAJ, BMAJ, OutT, GATHER, F8>>(G2_SMEM)) return 300;
   gemm2_kernel<AMAJ, BMAJ, OutT, GATHER, F8>
       <<<2 * pairs, GATHER ? G2_THREADS_GATHER : G2_THREADS, G2_SMEM, stream>>>(ta, tb, tc, owners, p);

@@ -47,6 +47,63 @@ def _time(fn, iters, flush):
     return tot / iters
 
 
+def _sustained(name, fn, flops, iters):
+    """Back-to-back launches for a few seconds (no flush: the point is the power-capped steady state), CUDA
+    events around the whole run, SM clock and board power sampled through NVML while the queue drains."""
+    import time
+
+    import pynvml
+
+    pynvml.nvmlInit()
+    h = pynvml.nvmlDeviceGetHandleByIndex(torch.cuda.current_device())
+    for _ in range(20):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    clk, pw = [], []
+    while not e1.query():
+        clk.append(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM))
+        pw.append(pynvml.nvmlDeviceGetPowerUsage(h) / 1000)
+        time.sleep(0.05)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    med = lambda v: sorted(v[len(v) // 2:])[len(v[len(v) // 2:]) // 2] if v else 0  # second half: settled
+    print(f"{name:42s} {ms:.4f} ms {flops / ms / 1e9:6.0f} TFLOP/s  SM {med(clk)} MHz  {med(pw):.0f} W  "
+          f"ms x MHz {ms * med(clk):.0f}", flush=True)
+
+
+def _gemm_sustained(a):
+    """The three products of a linear layer (--m tokens, --n outputs, --k inputs) on this library's SM-pair
+    kernel and on torch.matmul (cuBLAS), each run long enough to sit at the board's power cap."""
+    dev, bf = "cuda", torch.bfloat16
+    T, D, H = a.m, a.n, a.k
+    it = a.iters if a.iters > 100 else 3000
+    x, dy = torch.randn(T, H, device=dev, dtype=bf) * 0.5, torch.randn(T, D, device=dev, dtype=bf) * 0.5
+    w = torch.randn(D, H, device=dev, dtype=bf) * 0.02
+    wt = w.t().contiguous()
+    dw32 = torch.empty(D, H, device=dev, dtype=torch.float32)
+    dw16 = torch.empty(D, H, device=dev, dtype=bf)
+    fl = 2.0 * T * D * H
+    _sustained("ours forward x @ w^T (K-major, K-major)", lambda: G.gemm(x, w), fl, it)
+    _sustained("ours input grad dy @ w (K, N-major)", lambda: G.gemm(dy, w.t()), fl, it)
+    _sustained("ours input grad, transposed weight copy", lambda: G.gemm(dy, wt), fl, it)
+    _sustained("ours weight grad dy^T @ x, fp32 out", lambda: G.gemm(dy.t(), x.t(), out_dtype=torch.float32, out=dw32), fl, it)
+    _sustained("ours weight grad, bf16 out", lambda: G.gemm(dy.t(), x.t(), out=dw16), fl, it)
+    import os
+    for gm in (2, 4, 16, 32):  # tile walk: row tiles per group (default 8)
+        os.environ["LB_GEMM_GROUP_M"] = str(gm)
+        _sustained(f"ours forward, row tiles per group {gm}", lambda: G.gemm(x, w), fl, it)
+        _sustained(f"ours input grad, row tiles per group {gm}", lambda: G.gemm(dy, w.t()), fl, it)
+    os.environ.pop("LB_GEMM_GROUP_M")
+    _sustained("cuBLAS forward", lambda: torch.matmul(x, w.t()), fl, it)
+    _sustained("cuBLAS input grad", lambda: torch.matmul(dy, w), fl, it)
+    _sustained("cuBLAS weight grad (bf16 out)", lambda: torch.matmul(dy.t(), x), fl, it)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("op")
@@ -64,6 +121,8 @@ def main(argv=None):
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     flops = bytes_ = 0.0
     M, N, K = a.m, a.n, a.k
+    if a.op == "gemm_sustained":
+        return _gemm_sustained(a)
     if a.op == "gemm":
         x, w = torch.randn(M, K, device=dev, dtype=bf), torch.randn(N, K, device=dev, dtype=bf)
         fn = lambda: G.gemm(x, w, force_bn=a.bn)

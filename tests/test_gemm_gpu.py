@@ -18,7 +18,10 @@ def _check(out, ref, k):
     assert err / scale < tol, f"rel err {err / scale:.4g} (abs {err:.4g})"
 
 
-SHAPES = [(128, 256, 64), (256, 512, 512), (384, 128, 192), (200, 136, 72), (1024, 2048, 1024), (130, 72, 1032)]
+# the last three leave 14, 34 and 0 tiles of 256 x 256 for the final wave of 74 SM pairs: split into half-width
+# tiles, split, and not split
+SHAPES = [(128, 256, 64), (256, 512, 512), (384, 128, 192), (200, 136, 72), (1024, 2048, 1024), (130, 72, 1032),
+          (2048, 2816, 256), (4096, 4352, 128), (4096, 4736, 128)]
 
 
 @pytest.mark.parametrize("M,N,K", SHAPES)
