@@ -154,6 +154,32 @@ def test_indexed_matmul_matches_gather_oracle():
     assert (idx.flatten()[plan.order].diff() >= 0).all()
 
 
+def test_grouped_plan_layout_is_consistent():
+    """The device-side layout of the single-launch grouped products, computed here on CPU tensors: every row gets
+    its own slot inside its group's 256-row tiles, tiles name their group, contraction ranges cover the tiles."""
+    torch.manual_seed(1)
+    n, R = 7, 256
+    idx = torch.randint(0, n, (3, 1000))
+    idx[idx == 4] = 1  # a group without rows
+    plan = plan_groups(idx, n, grouped=True)
+    flat = idx.flatten()
+    T = flat.numel()
+    assert plan.grouped and plan._counts is None and plan.padded_rows % R == 0
+    assert plan.padded_rows >= int(((plan.counts_dev + R - 1) // R * R).sum())
+    assert plan.prow.unique().numel() == T and int(plan.prow.max()) < plan.padded_rows  # one slot per row
+    assert torch.equal(plan.pos[plan.order], plan.prow)
+    tile_group = plan.sel[plan.pos // R].long()
+    assert torch.equal(tile_group, flat)  # the tile a row lands in belongs to the row's group
+    k0, kb = plan.k_range[:, 0].long(), plan.k_range[:, 1].long()
+    assert kb[4] == 0 and (k0 % R == 0).all()
+    for g in range(n):
+        rows = plan.pos[flat == g]
+        if rows.numel():
+            assert int(rows.min()) == int(k0[g]) and int(rows.max()) < int(k0[g] + 64 * kb[g])
+    used = int((k0 + 64 * kb).max())
+    assert (plan.sel[used // R:] == -1).all() and (plan.sel[:used // R] >= 0).all()  # tiles past the end are skipped
+
+
 @pytest.mark.parametrize("kind", ["simple_indexed_matmul", "simple", "simple_repeat",
                                   "simple_non_param_indexed_matmul", "simple_non_param"])
 def test_model_every_pooling_type(kind):
