@@ -57,6 +57,8 @@ def _shard_param(mod: nn.Module, dim: int, tp: int, rank: int) -> None:
     else:
         new = w.data.chunk(tp, dim=dim)[rank].clone()
     mod.weight = nn.Parameter(new, requires_grad=w.requires_grad)
+    if getattr(w, "lb_fp8", False) and shape[0] % 16 == 0 and shape[1] % 16 == 0:
+        mod.weight.lb_fp8 = True  # float8 products were requested for this layer: the mark lives on the parameter
     mod.tp_shard = (dim, tp, rank)
     if dim == 0:
         mod.out_features = shape[0]

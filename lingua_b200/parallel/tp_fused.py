@@ -178,6 +178,7 @@ class SymmetricPeers:
         assert self.world <= MAX_PEERS
         self._bufs: Dict[str, torch.Tensor] = {}
         self._ptrs: Dict[str, List[int]] = {}
+        self._peer_views: Dict[str, List[torch.Tensor]] = {}
         self._epoch = 0
         self.alloc("__pad", (MAX_PEERS,), torch.int32).zero_()
         torch.cuda.synchronize(device)
@@ -189,6 +190,7 @@ class SymmetricPeers:
             hdl = self._sm.rendezvous(t, group=self.group)
             self._bufs[name] = t
             self._ptrs[name] = [int(p) for p in hdl.buffer_ptrs]
+            self._peer_views[name] = [hdl.get_buffer(r, tuple(shape), dtype) for r in range(self.world)]
         t = self._bufs[name]
         assert tuple(t.shape) == tuple(shape) and t.dtype == dtype, f"buffer {name} re-allocated with another shape"
         return t
@@ -198,6 +200,11 @@ class SymmetricPeers:
 
     def local(self, name: str) -> torch.Tensor:
         return self._bufs[name]
+
+    def peer(self, name: str, rank: int) -> torch.Tensor:
+        """Rank ``rank``'s buffer as a tensor of this device (peer mapping): for copies, never as a kernel operand
+        of a library product."""
+        return self._peer_views[name][rank]
 
     def barrier(self) -> None:
         self._epoch += 1

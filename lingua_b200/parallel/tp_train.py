@@ -28,6 +28,7 @@ from typing import Optional
 import torch
 import torch.distributed as dist
 
+from ..float8 import fp8_dgrad_mm, fp8_forward_mm, wants_fp8
 from ..ops import functional as F
 from ..ops.attention import flash_bwd, flash_fwd
 from ..ops.fused import _emit_vec_grad, _emit_wgrad, _weights
@@ -63,23 +64,58 @@ class SPContext:
     def barrier(self) -> None:
         self.peers.barrier()
 
-    def gathered(self, own_rows: torch.Tensor, w_view: torch.Tensor):
-        """(all rows @ w_view^T, all rows): publish ``own_rows`` ([Tl, D]), multiply every rank's rows with ``w_view``
-        ([N, D] view, either operand order in memory) and keep the gathered rows for the weight gradient."""
+    def gathered(self, own_rows: torch.Tensor, w: torch.Tensor, transposed: bool = False):
+        """(all rows @ w^T, all rows) -- with ``transposed``: all rows @ w. Publishes ``own_rows`` ([Tl, D]),
+        multiplies every rank's rows with the weight (read in place in either orientation) and keeps the gathered
+        rows for the weight gradient.
+
+        bf16 weights: one kernel gathers and multiplies (``ag_gemm``). Weights marked for float8: the peers' rows are
+        copied over NVLink into the local buffer first and the product is the row-wise scaled e4m3 one of
+        ``lingua_b200.float8`` on local memory; every rank quantises what it holds, so operands that TP splits
+        along the reduction dim get one scale per row and rank (the sub-row scaling of lingua/float8.py:14-21)."""
         self.y.copy_(own_rows)
         self.barrier()  # every rank's rows are in place (and nobody still reads the previous contents)
         full = torch.empty(self.T, self.D, dtype=torch.bfloat16, device=self.device)
-        out = ag_gemm(self.peers.ptrs("sp_y"), self.rank, self.Tl, w_view, full, self.flags)
-        full[self.rank * self.Tl:(self.rank + 1) * self.Tl].copy_(own_rows)  # the kernel reads the own slab in place
-        return out, full
+        if not wants_fp8(w):
+            out = ag_gemm(self.peers.ptrs("sp_y"), self.rank, self.Tl, w.t() if transposed else w, full, self.flags)
+            full[self.rank * self.Tl:(self.rank + 1) * self.Tl].copy_(own_rows)  # the kernel reads the own slab in place
+            return out, full
+        for r in range(self.world):
+            src = own_rows if r == self.rank else self.peers.peer("sp_y", r)
+            full[r * self.Tl:(r + 1) * self.Tl].copy_(src, non_blocking=True)
+        return (fp8_dgrad_mm(full, w) if transposed else fp8_forward_mm(full, w)), full
 
-    def scattered_sum(self, x: torch.Tensor, w_view: torch.Tensor, resid: Optional[torch.Tensor]) -> torch.Tensor:
-        """Own rows of sum_ranks(x_r @ w_view_r^T) (+ resid): the partial product of every rank is stored into the
-        owners' slots by the GEMM epilogue, then the slots are summed."""
-        gemm_scatter(x, w_view, self.peers.ptrs("sp_stage"), self.rank, self.Tl * self.D)
+    def scattered_sum(self, x: torch.Tensor, w: torch.Tensor, resid: Optional[torch.Tensor],
+                      transposed: bool = False) -> torch.Tensor:
+        """Own rows of sum_ranks(x_r @ w_r^T) (+ resid) -- with ``transposed``: x_r @ w_r. bf16: the partial product
+        of every rank is stored into the owners' slots by the GEMM epilogue; float8: the local e4m3 product is
+        copied slab by slab into the owners' slots. Then the slots are summed."""
+        if not wants_fp8(w):
+            gemm_scatter(x, w.t() if transposed else w, self.peers.ptrs("sp_stage"), self.rank, self.Tl * self.D)
+        else:
+            part = fp8_dgrad_mm(x, w) if transposed else fp8_forward_mm(x, w)
+            for k in range(self.world):
+                r = (self.rank + k) % self.world  # own slab first, then the neighbours in ring order
+                self.peers.peer("sp_stage", r)[self.rank].copy_(part[r * self.Tl:(r + 1) * self.Tl], non_blocking=True)
         self.barrier()  # every rank's partials have landed
         h, _ = reduce_norm(self.stage, resid, None, 0.0)
         return h
+
+
+def _out_weight(w: torch.Tensor) -> torch.Tensor:
+    """The row-parallel weight without its autograd history; ``detach`` drops the float8 mark, so it is put back."""
+    d = w.detach()
+    if wants_fp8(w):
+        d.lb_fp8 = True
+    return d
+
+
+def _in_weight(ws_in) -> torch.Tensor:
+    """The stacked column-parallel weight (wq|wk|wv or w1|w3) as one matrix, carrying the float8 mark of its parts."""
+    w = _weights(ws_in)
+    if wants_fp8(ws_in[0]) and not wants_fp8(w):
+        w.lb_fp8 = True
+    return w
 
 
 class SPHalfBlockFn(torch.autograd.Function):
@@ -90,7 +126,7 @@ class SPHalfBlockFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, h, g, eps, sp: SPContext, cfg, cs, doc_start, doc_end, pos, w_out, *ws_in):
         y, _, rstd = F.rmsnorm_fwd(h, g.detach(), eps, None)
-        pre, y_full = sp.gathered(y, _weights(ws_in))
+        pre, y_full = sp.gathered(y, _in_weight(ws_in))
         del y
         lse = o = None
         if cfg[0] == "attn":
@@ -103,7 +139,7 @@ class SPHalfBlockFn(torch.autograd.Function):
             core = F.glu_fwd(pre, cfg[1])
         else:
             core = F.act_fwd(pre, cfg[1])
-        h_out = sp.scattered_sum(core, w_out.detach(), h)
+        h_out = sp.scattered_sum(core, _out_weight(w_out), h)
         ctx.save_for_backward(h, rstd, y_full, pre, o, lse, cs, doc_start, doc_end, pos)
         ctx.g, ctx.eps, ctx.sp, ctx.cfg, ctx.w_out, ctx.ws_in = g, eps, sp, cfg, w_out, ws_in
         return h_out
@@ -114,7 +150,7 @@ class SPHalfBlockFn(torch.autograd.Function):
         g, sp, cfg, w_out, ws_in = ctx.g, ctx.sp, ctx.cfg, ctx.w_out, ctx.ws_in
         dh_out = dh_out.contiguous()
         # d(core) = gather(dh_out) @ W_out  (W_out [D, K_local] read as the [K_local, D] operand it is the transpose of)
-        dcore, dp_full = sp.gathered(dh_out, w_out.detach().t())
+        dcore, dp_full = sp.gathered(dh_out, _out_weight(w_out), transposed=True)
         if cfg[0] == "attn":
             _, B, S, H, Hkv, Dh, causal, window = cfg
             core = o.view(B * S, H * Dh)
@@ -138,7 +174,7 @@ class SPHalfBlockFn(torch.autograd.Function):
         del core, dcore
         dws_in = _emit_wgrad(ws_in, dpre, y_full) if ws_in[0].requires_grad else [None] * len(ws_in)
         # d(y) for the own rows = sum over ranks of dpre_r @ W_in_r
-        dy = sp.scattered_sum(dpre, _weights(ws_in).t(), None)
+        dy = sp.scattered_sum(dpre, _in_weight(ws_in), None, transposed=True)
         holder = {}
 
         def run(dw_buf):

@@ -74,3 +74,26 @@ def test_checkpoint_round_trip_keeps_every_ranks_shard(tmp_path, nproc, dp_shard
     proc = _run(nproc, dp_shard, tp, steps=2, port=29637, ckpt=str(tmp_path / "ckpt"))
     assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-3000:]
     assert proc.stdout.count("CKPT_OK") == nproc
+
+
+def test_tp_sharding_keeps_the_float8_mark():
+    """Sharding a layer over the TP group replaces its parameter; the request for float8 products has to survive."""
+    import torch.nn as nn
+
+    from lingua_b200.float8 import convert_linears_to_fp8, wants_fp8
+    from lingua_b200.parallel.tensor_parallel import _shard_param
+
+    class Blk(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.layers = nn.ModuleList([nn.Linear(64, 128, bias=False), nn.Linear(64, 24, bias=False)])
+
+    m = Blk()
+    convert_linears_to_fp8(m, "rowwise", r"layers\.[0-9]+")
+    assert wants_fp8(m.layers[0].weight) and not wants_fp8(m.layers[1].weight)  # 24 is not a multiple of 16
+    _shard_param(m.layers[0], 0, 2, 1)
+    assert m.layers[0].weight.shape == (64, 64) and wants_fp8(m.layers[0].weight)
+    _shard_param(m.layers[0], 1, 4, 0)  # 16 columns left: still a float8 shape
+    assert wants_fp8(m.layers[0].weight)
+    _shard_param(m.layers[0], 1, 2, 0)  # 8 columns: the kernels do not take it, the layer falls back to bf16
+    assert not wants_fp8(m.layers[0].weight)

@@ -72,3 +72,30 @@ def test_fp8_model_trains_on_cpu():
         losses.append(loss.item())
     assert abs(losses[0] - ref_loss) < 0.05 * ref_loss
     assert losses[-1] < losses[0] - 0.3
+
+
+def test_row_parallel_split_equals_sub_row_scaling():
+    """Under tensor parallelism a row-parallel product splits the reduction dim over the ranks and every rank
+    quantises its own slice with its own per-row scales. That is the sub-row scaling the reference switches to
+    for operands sharded along the reduction dim (lingua/float8.py:14-21, 86-88): one scale per row and K-chunk."""
+    from lingua_b200 import float8 as F8
+
+    torch.manual_seed(0)
+    M, N, K, tp = 24, 40, 128, 2
+    x = torch.randn(M, K) * torch.logspace(-2, 1, K)  # very different magnitudes in the two halves of K
+    w = torch.randn(N, K) * 0.05
+    ours = sum(F8.fp8_forward_mm(xc.contiguous(), wc.contiguous()) for xc, wc in zip(x.chunk(tp, 1), w.chunk(tp, 1)))
+
+    def sub_row(t):  # the reference's formula, restated: amax over (rows, tp chunks)
+        amax = t.abs().unflatten(-1, (tp, -1)).amax(dim=-1)
+        scale = amax.float().clamp(min=1e-12) / torch.finfo(torch.float8_e4m3fn).max
+        q = (t.unflatten(-1, (tp, -1)) / scale[..., None]).to(torch.float8_e4m3fn)
+        return q, scale
+
+    x8, sx = sub_row(x)
+    w8, sw = sub_row(w)
+    want = sum((x8[:, c].float() @ w8[:, c].float().t()) * sx[:, c, None] * sw[None, :, c] for c in range(tp))
+    assert torch.allclose(ours, want, rtol=1e-5, atol=1e-6)
+    one_scale = F8.fp8_forward_mm(x, w)  # a single scale per row loses the small half of K
+    exact = x @ w.t()
+    assert (ours - exact).abs().max() < (one_scale - exact).abs().max()

@@ -17,12 +17,13 @@ from lingua_b200.ops import _lib  # noqa: E402
 from lingua_b200.optim import OptimArgs  # noqa: E402
 
 
-def run(sp: bool, world: int, dev, act: str):
+def run(sp: bool, world: int, dev, act: str, fp8: bool = False):
     tp = 2
     args = LMTransformerArgs(dim=512, n_layers=2, n_heads=4, n_kv_heads=2, vocab_size=1024, max_seqlen=256,
                              ffn_activation=act)
     tr = Trainer(args, DistributedArgs(dp_shard=world // tp, tp_size=tp, fsdp_type="full_shard",
-                                       tp_sequence_parallel=sp, fused_tp_forward=False),
+                                       tp_sequence_parallel=sp, fused_tp_forward=False,
+                                       float8_recipe="rowwise" if fp8 else None),
                  OptimArgs(lr=3e-3, warmup=1, clip=1.0), total_steps=100, device=dev)
     assert (getattr(tr.model, "tp_sp", None) is not None) == sp
     dp_rank = tr.mesh.local_rank("dp")
@@ -57,6 +58,29 @@ def main():
             print(f"TP_TRAIN_MISMATCH rank {rank} {act} losses {l_sp} vs {l_ar} norms {n_sp} vs {n_ar}", flush=True)
             raise SystemExit(1)
         assert l_sp[-1] < l_sp[0]
+    # float8 products in the blocks: the sequence-parallel path gathers / scatters around the e4m3 products, the
+    # all-reduce formulation runs the same products on the same operands
+    from lingua_b200.parallel import tp_train
+
+    calls = {"n": 0}
+    orig = tp_train.fp8_forward_mm
+
+    def counted(*a, **k):
+        calls["n"] += 1
+        return orig(*a, **k)
+
+    tp_train.fp8_forward_mm = counted
+    l_sp, n_sp = run(True, world, dev, "swiglu", fp8=True)
+    tp_train.fp8_forward_mm = orig
+    assert calls["n"] == 6 * 2 * 4, calls  # 6 steps x 2 layers x (two products per half-block)
+    l_ar, n_ar = run(False, world, dev, "swiglu", fp8=True)
+    # later steps overfit one batch down to a loss of 0.06, where two float8 trajectories differ by their own noise
+    ok = all(abs(a - b) <= (1e-2 * abs(b) if i < 3 else 6e-2 * abs(b) + 2e-2) for i, (a, b) in enumerate(zip(l_sp, l_ar)))
+    ok = ok and all(abs(a - b) <= (4e-2 if i < 3 else 1.5e-1) * abs(b) for i, (a, b) in enumerate(zip(n_sp, n_ar)))
+    if not ok:
+        print(f"TP_TRAIN_MISMATCH rank {rank} float8 losses {l_sp} vs {l_ar} norms {n_sp} vs {n_ar}", flush=True)
+        raise SystemExit(1)
+    assert l_sp[-1] < l_sp[0]
     dist.barrier()
     if rank == 0:
         print("TP_TRAIN_OK", l_sp, n_sp)
